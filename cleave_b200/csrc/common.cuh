@@ -1,0 +1,83 @@
+// Shared internals of libcleave_cuda: context, handle table, error channel, launch helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "../../include/cleave_cuda.h"
+
+namespace cleave {
+
+// One device tensor: dense row-major f32, `len` elements at `ptr`.
+struct Buf {
+  uint32_t magic;   // kMagic while live
+  float* ptr;
+  int64_t len;
+  int64_t cap_bytes;  // pool block size; 0 for a non-owning view
+};
+constexpr uint32_t kMagic = 0xC1EA7E5Bu;
+
+// Device-visible status word: kernels with bounded waits record a non-zero code here
+// (pinned, mapped host memory), the host checks it at every synchronisation point.
+struct DeviceStatus {
+  int code;       // 0 = fine
+  int where;      // kernel-specific location id
+  int block;      // blockIdx.x of the reporter
+  int detail;
+};
+
+struct Context {
+  bool ready = false;
+  int device = -1;
+  int sm_count = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;      // stream in use (own or caller's)
+  DeviceStatus* status_host = nullptr;
+  DeviceStatus* status_dev = nullptr;
+  float* scalar_host = nullptr;       // pinned landing area for scalar results (64 floats)
+};
+
+Context& ctx();
+
+// ---- error channel -------------------------------------------------------------------
+int set_error(int code, const char* fmt, ...);   // records and returns `code`
+bool ensure_init();                              // lazily initialises device 0 (or CLEAVE_CUDA_DEVICE)
+bool cuda_ok(cudaError_t e, const char* what);   // records CLEAVE_CUDA_ERR_CUDA on failure
+int check_device_status();                       // after a sync: translate the status word
+
+// Every extern "C" entry point holds this lock for its whole body.
+std::recursive_mutex& api_mutex();
+struct ApiLock {
+  std::lock_guard<std::recursive_mutex> g;
+  ApiLock() : g(api_mutex()) {}
+};
+
+// ---- handles and memory ---------------------------------------------------------------
+Buf* new_buf(int64_t len);             // pooled device allocation; nullptr + error on failure
+Buf* as_buf(cleave_buf h, const char* what);   // validates; nullptr + error on failure
+void release_buf(Buf* b);
+float* scratch_alloc(int64_t bytes);   // pooled scratch (stream-ordered reuse); pair with scratch_free
+void scratch_free(float* p);
+void count_launch(int n = 1);
+
+// Reads one f32 produced on the device at `dev_scalar`: copies to pinned memory, syncs,
+// checks the status word.  Returns NaN on failure.
+float read_scalar(const float* dev_scalar);
+
+// ---- launch geometry -------------------------------------------------------------------
+inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+// Grid for a grid-stride streaming kernel: enough CTAs for the work, capped at a multiple
+// of the SM count so every SM holds the same number of resident CTAs.
+inline int stream_grid(int64_t work_items, int threads, int ctas_per_sm) {
+  int64_t need = (work_items + threads - 1) / threads;
+  int64_t cap = (int64_t)ctx().sm_count * ctas_per_sm;
+  if (need < 1) need = 1;
+  return (int)(need < cap ? need : cap);
+}
+
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+}  // namespace cleave

@@ -1,0 +1,98 @@
+// C-ABI entry points of the MatMul family and the choice between the two GEMM paths.
+#include <cstdlib>
+
+#include "common.cuh"
+#include "gemm.cuh"
+
+namespace cleave {
+
+// Below this many multiply-adds the exact CUDA-core kernel is used: the pre-pass and pipeline
+// fill of the tensor-core path cost more than they save, and the result is bit-identical to
+// the reference's loop.
+constexpr int64_t kTensorCoreMinMacs = 1ll << 24;
+
+static bool run_gemm(const GemmArgs& g, int algo) {
+  if (algo == CLEAVE_GEMM_AUTO) {
+    const int64_t macs = (int64_t)g.batch * g.m * g.n * g.k;
+    algo = (macs >= kTensorCoreMinMacs && g.m >= 64 && g.n >= 64 && gemm_3xtf32_supported(g)) ? CLEAVE_GEMM_3XTF32
+                                                                                              : CLEAVE_GEMM_EXACT;
+  }
+  if (algo == CLEAVE_GEMM_EXACT) return launch_gemm_exact(g);
+  if (algo == CLEAVE_GEMM_3XTF32) return launch_gemm_3xtf32(g);
+  set_error(CLEAVE_CUDA_ERR_ARG, "gemm: unknown algorithm code %d", algo);
+  return false;
+}
+
+static int gemm_into(Buf* C, Buf* A, Buf* B, int batch, int m, int n, int k, int ta, int tb, int algo, Buf* bias,
+                     int act) {
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0)
+    return set_error(CLEAVE_CUDA_ERR_ARG, "gemm: batch, m, n, k must be positive (got %d, %d, %d, %d)", batch, m, n, k);
+  if (A->len != (int64_t)batch * m * k || B->len != (int64_t)batch * k * n || C->len != (int64_t)batch * m * n)
+    return set_error(CLEAVE_CUDA_ERR_SHAPE,
+                     "gemm: operand lengths %lld, %lld, %lld do not match batch %d of [%d x %d] * [%d x %d]",
+                     (long long)A->len, (long long)B->len, (long long)C->len, batch, m, k, k, n);
+  if (bias && bias->len != n)
+    return set_error(CLEAVE_CUDA_ERR_SHAPE, "gemm: bias has %lld elements, n is %d", (long long)bias->len, n);
+  if (act < CLEAVE_ACT_IDENTITY || act > CLEAVE_ACT_TANH)
+    return set_error(CLEAVE_CUDA_ERR_ARG, "gemm: unknown activation code %d", act);
+  if (C->ptr == A->ptr || C->ptr == B->ptr)
+    return set_error(CLEAVE_CUDA_ERR_ARG, "gemm: the output must not alias an operand");
+  GemmArgs g{A->ptr, B->ptr, C->ptr, batch, m, n, k, ta ? 1 : 0, tb ? 1 : 0, bias ? bias->ptr : nullptr, act};
+  return run_gemm(g, algo) ? CLEAVE_CUDA_OK : cleave_cuda_last_error();
+}
+
+static cleave_buf gemm_new(cleave_buf a, cleave_buf b, int batch, int m, int n, int k, int ta, int tb) {
+  ApiLock lock;
+  Buf* A = as_buf(a, "gemm");
+  Buf* B = as_buf(b, "gemm");
+  if (!A || !B) return nullptr;
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "gemm: batch, m, n, k must be positive (got %d, %d, %d, %d)", batch, m, n, k);
+    return nullptr;
+  }
+  Buf* C = new_buf((int64_t)batch * m * n);
+  if (!C) return nullptr;
+  if (gemm_into(C, A, B, batch, m, n, k, ta, tb, CLEAVE_GEMM_AUTO, nullptr, CLEAVE_ACT_IDENTITY) != CLEAVE_CUDA_OK) {
+    release_buf(C);
+    return nullptr;
+  }
+  return (cleave_buf)C;
+}
+
+}  // namespace cleave
+
+using namespace cleave;
+
+extern "C" {
+
+cleave_buf cleave_cuda_gemm_f32(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k) {
+  return gemm_new(a, b, 1, m, n, k, 0, 0);
+}
+cleave_buf cleave_cuda_gemm_nt_f32(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k) {
+  return gemm_new(a, b, 1, m, n, k, 0, 1);
+}
+cleave_buf cleave_cuda_gemm_tn_f32(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k) {
+  return gemm_new(a, b, 1, m, n, k, 1, 0);
+}
+cleave_buf cleave_cuda_gemm_batched_f32(cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n, int32_t k) {
+  return gemm_new(a, b, batch, m, n, k, 0, 0);
+}
+
+int32_t cleave_cuda_gemm_ex_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n,
+                                int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo, cleave_buf bias,
+                                int32_t act) {
+  ApiLock lock;
+  Buf* C = as_buf(c, "gemm_ex");
+  Buf* A = as_buf(a, "gemm_ex");
+  Buf* B = as_buf(b, "gemm_ex");
+  if (!C || !A || !B) return -cleave_cuda_last_error();
+  Buf* bi = nullptr;
+  if (bias) {
+    bi = as_buf(bias, "gemm_ex");
+    if (!bi) return -cleave_cuda_last_error();
+  }
+  int r = gemm_into(C, A, B, batch, m, n, k, trans_a, trans_b, algo, bi, act);
+  return r == CLEAVE_CUDA_OK ? CLEAVE_CUDA_OK : -r;
+}
+
+}  // extern "C"

@@ -1,0 +1,622 @@
+// Tensor-core f32 GEMM for sm_100a: tcgen05.mma (kind::tf32) with TMEM accumulators, operands
+// staged by TMA into a multi-stage shared-memory ring guarded by mbarriers, and a 3xTF32
+// split so that the f32 result stays within rounding distance of the reference's f32 loop.
+//
+// Split precision.  Every f32 operand value x is written as hi + lo with
+//   hi = tf32(x)  (round to nearest, 10 explicit mantissa bits),  lo = tf32(x - hi),
+// and a*b is accumulated as  a_lo*b_hi + a_hi*b_lo + a_hi*b_hi  in the f32 TMEM accumulator.
+// The dropped a_lo*b_lo term and the rounding of lo are each <= 2^-22 |a b|.
+//
+// Data path.  A pre-pass writes both operands K-major (the contraction index contiguous) as two
+// planes [hi | lo] of shape [rows_padded, K_padded], transposing where the caller's layout has
+// the other index contiguous; this makes NN / NT / TN one kernel.  Padding (rows to the tile
+// height, K to the K-block) is zero-filled so every TMA box is fully in bounds.
+//
+// Kernel.  Persistent, one CTA per SM, 192 threads:
+//   warp 0      TMA producer (one elected lane): per K-block one 3-D box per operand
+//               {BK, rows, 2 planes} -> shared memory, completion on the stage's "full" mbarrier
+//   warp 1      MMA issuer (one elected lane): 3 x (BK/8) tcgen05.mma per K-block into one of two
+//               128x256 f32 accumulators in TMEM; tcgen05.commit releases the stage ("empty")
+//               and, after the last K-block, publishes the accumulator ("tmem_full")
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, optional bias + activation,
+//               128-bit stores to C; then hand the accumulator back ("tmem_empty")
+// The second accumulator lets the epilogue of tile i overlap the main loop of tile i+1.
+// Tiles are visited in groups of 16 tile-rows so that the ~148 tiles in flight share operand
+// panels through L2.
+//
+// Every mbarrier wait is bounded (wall-clock limit on %globaltimer).  A wait that gives up sets a
+// CTA-wide abort flag and a status word the host reads; the CTA then drains its own TMA copies
+// (bounded), frees its TMEM and returns, so the context stays usable.
+#include <cuda.h>
+
+#include <cstdio>
+
+#include "common.cuh"
+#include "gemm.cuh"
+
+namespace cleave {
+
+constexpr int BM = 128;          // tile rows  (UMMA M)
+constexpr int BN = 256;          // tile cols  (UMMA N)
+constexpr int UMMA_K = 8;        // tf32 MMA K (32 bytes)
+constexpr int kGemmThreads = 192;
+constexpr int kAccStages = 2;
+constexpr int kTmemCols = kAccStages * BN;   // 512: all of TMEM
+constexpr int kGroupM = 16;      // tile-rows per rasterisation group
+constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s per wait
+
+template <int BK>
+struct Cfg {
+  static_assert(BK == 16 || BK == 32, "BK must give a 64- or 128-byte row");
+  static constexpr int kRowBytes = BK * 4;
+  static constexpr int kStages = BK == 32 ? 2 : 4;
+  static constexpr int kABytes = BM * kRowBytes;          // one plane of A
+  static constexpr int kBBytes = BN * kRowBytes;          // one plane of B
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;   // + alignment slack
+  static constexpr uint32_t kLayoutType = BK == 32 ? 2u : 4u;       // SWIZZLE_128B : SWIZZLE_64B
+  static constexpr uint32_t kSBO = 8 * kRowBytes;                   // bytes between 8-row groups
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false if the CTA is aborting or the wall-clock limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0xFFu) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], tf32 inputs, f32 accumulate.
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, swizzled rows of `kRowBytes`:
+//   bits  0-13 start address >> 4     bits 16-29 leading byte offset >> 4 (1: unused when swizzled)
+//   bits 32-45 stride byte offset >> 4 (8-row group pitch)   bits 46-47 descriptor version (1)
+//   bits 61-63 swizzle mode (2 = 128 B, 4 = 64 B)
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t sbo_bytes, uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(sbo_bytes >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+
+// Instruction descriptor: f32 accumulator (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2),
+// both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float act_apply(float v, int act) {
+  switch (act) {
+    case CLEAVE_ACT_RELU: return v != v ? v : (v > 0.0f ? v : 0.0f);
+    case CLEAVE_ACT_SIGMOID: return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v)));
+    case CLEAVE_ACT_TANH: return tanhf(v);
+    default: return v;
+  }
+}
+
+struct TcParams {
+  float* c;             // [batch][m][n]
+  const float* bias;    // [n] or null
+  int m, n;
+  int num_kb;           // K_padded / BK
+  int batch, mblks, nblks;
+  int act;
+  DeviceStatus* status;
+};
+
+// Tile index -> (batch, tile-row, tile-col); tile-rows are walked in groups of kGroupM with the
+// row index fastest inside a group, so consecutive tiles share a B panel and nearby A panels.
+__device__ __forceinline__ void decode_tile(int t, const TcParams& p, int& b, int& mb, int& nb) {
+  const int per_batch = p.mblks * p.nblks;
+  b = t / per_batch;
+  int r = t - b * per_batch;
+  const int group_span = kGroupM * p.nblks;
+  const int gid = r / group_span;
+  const int first_m = gid * kGroupM;
+  const int rows_here = (p.mblks - first_m) < kGroupM ? (p.mblks - first_m) : kGroupM;
+  r -= gid * group_span;
+  mb = first_m + r % rows_here;
+  nb = r / rows_here;
+}
+
+__device__ __forceinline__ void report(DeviceStatus* st, int code, int where, int detail) {
+  // Plain stores to mapped host memory (several CTAs may report; any one record will do).
+  volatile DeviceStatus* v = st;
+  v->where = where;
+  v->block = blockIdx.x;
+  v->detail = detail;
+  v->code = code;
+  __threadfence_system();
+}
+
+template <int BK>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+  using C = Cfg<BK>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[C::kStages];
+  __shared__ __align__(8) uint64_t bar_empty[C::kStages];
+  __shared__ __align__(8) uint64_t bar_tmem_full[kAccStages];
+  __shared__ __align__(8) uint64_t bar_tmem_empty[kAccStages];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // Operand ring, 1024-byte aligned (the swizzle pattern is a function of address bits 4-9).
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int total_tiles = p.batch * p.mblks * p.nblks;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < kAccStages; ++a) {
+      mbar_init(smem_u32(&bar_tmem_full[a]), 1);
+      mbar_init(smem_u32(&bar_tmem_empty[a]), 4);   // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed[C::kStages];
+#pragma unroll
+      for (int s = 0; s < C::kStages; ++s) armed[s] = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        int b, mb, nb;
+        decode_tile(t, p, b, mb, nb);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
+            report(p.status, 1, 100 + stage, kb);
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          const uint32_t sa = ring + stage * C::kStageBytes;
+          mbar_arrive_expect_tx(full, C::kStageBytes);
+          tma_load_3d(sa, &map_a, full, kb * BK, mb * BM, b * 2);
+          tma_load_3d(sa + 2 * C::kABytes, &map_b, full, kb * BK, nb * BN, b * 2);
+#pragma unroll
+          for (int s = 0; s < C::kStages; ++s)
+            if (s == stage) armed[s]++;
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Leaving early: give this CTA's copies in flight a bounded chance to land before the
+        // shared memory they target is released.
+#pragma unroll
+        for (int s = 0; s < C::kStages; ++s) {
+          if (armed[s] == 0) continue;
+          const uint32_t par = (armed[s] - 1u) & 1u;
+          for (int spin = 0; spin < (1 << 20); ++spin)
+            if (mbar_try_wait(smem_u32(&bar_full[s]), par)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
+          report(p.status, 2, 200 + acc, t);
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
+            report(p.status, 3, 300 + stage, kb);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_hi = ring + stage * C::kStageBytes;
+          const uint32_t a_lo = a_hi + C::kABytes;
+          const uint32_t b_hi = a_hi + 2 * C::kABytes;
+          const uint32_t b_lo = b_hi + C::kBBytes;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint32_t off = kk * UMMA_K * 4;   // 32 bytes along K inside the swizzled row
+            const uint64_t da_hi = make_smem_desc(a_hi + off, C::kSBO, C::kLayoutType);
+            const uint64_t da_lo = make_smem_desc(a_lo + off, C::kSBO, C::kLayoutType);
+            const uint64_t db_hi = make_smem_desc(b_hi + off, C::kSBO, C::kLayoutType);
+            const uint64_t db_lo = make_smem_desc(b_lo + off, C::kSBO, C::kLayoutType);
+            // small terms first, then the leading product
+            umma_tf32(d_tmem, da_lo, db_hi, kInstrDesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_tf32(d_tmem, da_hi, db_lo, kInstrDesc, 1u);
+            umma_tf32(d_tmem, da_hi, db_hi, kInstrDesc, 1u);
+          }
+          tcgen05_commit(smem_u32(&bar_empty[stage]));   // stage reusable once these MMAs retire
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tcgen05_commit(smem_u32(&bar_tmem_full[acc]));   // accumulator complete
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;   // TMEM lane quarter this warp may read: lanes 32q .. 32q+31
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = (p.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0);
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      int b, mb, nb;
+      decode_tile(t, p, b, mb, nb);
+      bool ok = mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, 4, 400 + acc, t);
+        break;
+      }
+      tcgen05_fence_after();
+      const int row = mb * BM + q * 32 + lane;
+      const int col0 = nb * BN;
+      float* crow = p.c + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; ++cb) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + cb * 32, r);
+        tmem_ld_wait();
+        const int cbase = col0 + cb * 32;
+        if (row < p.m && cbase < p.n) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (p.bias != nullptr || p.act != CLEAVE_ACT_IDENTITY) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int cj = cbase + j;
+              float x = v[j];
+              if (p.bias != nullptr && cj < p.n) x = __fadd_rn(x, __ldg(p.bias + cj));
+              v[j] = act_apply(x, p.act);
+            }
+          }
+          if (vec_ok && cbase + 32 <= p.n) {
+            float4* dst = reinterpret_cast<float4*>(crow + cb * 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cbase + j < p.n) crow[cb * 32 + j] = v[j];
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
+      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---- operand pre-pass: split into tf32 hi / lo planes, K-major, zero padded ----------------------
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  hi = tf32_round(x);
+  lo = tf32_round(__fsub_rn(x, hi));
+}
+
+// Source already K-major: src[b][r][k] (r < rows, k < K).  dst planes [b][2][rows_p][Kp].
+__global__ void __launch_bounds__(256) split_copy_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                         int rows, int K, int rows_p, int Kp, int vec) {
+  const int b = blockIdx.z;
+  const float* s = src + (int64_t)b * rows * K;
+  float* hi_p = dst + (int64_t)b * 2 * rows_p * Kp;
+  float* lo_p = hi_p + (int64_t)rows_p * Kp;
+  const int kq = Kp >> 2;   // Kp is a multiple of 16
+  const int64_t total = (int64_t)rows_p * kq;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / kq);
+    const int k = (int)(i - (int64_t)r * kq) * 4;
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    if (r < rows) {
+      if (vec && k + 3 < K) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(s + (int64_t)r * K + k));
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (k + j < K) x[j] = s[(int64_t)r * K + k + j];
+      }
+    }
+    float h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) split_tf32(x[j], h[j], l[j]);
+    const int64_t o = (int64_t)r * Kp + k;
+    *reinterpret_cast<float4*>(hi_p + o) = make_float4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<float4*>(lo_p + o) = make_float4(l[0], l[1], l[2], l[3]);
+  }
+}
+
+// Source has the row index contiguous: src[b][k][r].  32x32 tiles through shared memory so both
+// the read (along r) and the writes (along k) are coalesced.  grid = (Kp/32, rows_p/32, batch).
+__global__ void __launch_bounds__(256) split_transpose_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                              int rows, int K, int rows_p, int Kp) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z;
+  const float* s = src + (int64_t)b * rows * K;
+  float* hi_p = dst + (int64_t)b * 2 * rows_p * Kp;
+  float* lo_p = hi_p + (int64_t)rows_p * Kp;
+  const int k0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int k = k0 + ty + j * 8, r = r0 + tx;
+    tile[ty + j * 8][tx] = (k < K && r < rows) ? __ldcs(s + (int64_t)k * rows + r) : 0.0f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int r = r0 + ty + j * 8, k = k0 + tx;
+    if (r < rows_p && k < Kp) {
+      float h, l;
+      split_tf32(tile[tx][ty + j * 8], h, l);
+      hi_p[(int64_t)r * Kp + k] = h;
+      lo_p[(int64_t)r * Kp + k] = l;
+    }
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// 3-D map over the split planes of one operand: dims {Kp, rows_p, 2*batch}, box {BK, box_rows, 2}.
+static bool make_operand_map(CUtensorMap* map, float* planes, int rows_p, int Kp, int batch, int bk, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)rows_p, (cuuint64_t)(2 * batch)};
+  cuuint64_t strides[2] = {(cuuint64_t)Kp * 4, (cuuint64_t)rows_p * Kp * 4};
+  cuuint32_t box[3] = {(cuuint32_t)bk, (cuuint32_t)box_rows, 2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, planes, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (rows %d, K %d, batch %d)", (int)r,
+              rows_p, Kp, batch);
+    return false;
+  }
+  return true;
+}
+
+static int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+static int g_bk = 0;   // K-block: 16 (64-byte rows, 4 stages) or 32 (128-byte rows, 2 stages)
+static int choose_bk() {
+  if (g_bk == 0) {
+    const char* e = getenv("CLEAVE_CUDA_GEMM_BK");
+    g_bk = (e && atoi(e) == 32) ? 32 : 16;
+  }
+  return g_bk;
+}
+
+bool gemm_3xtf32_supported(const GemmArgs& g) {
+  // Problem dimensions must fit the 32-bit coordinates of the tensor map and the tile counters.
+  return g.m > 0 && g.n > 0 && g.k > 0 && g.batch > 0 && (int64_t)g.m * g.n < (1ll << 40) &&
+         (int64_t)g.batch * ceil_div(g.m, BM) * ceil_div(g.n, BN) < (1ll << 30);
+}
+
+static bool split_operand(const float* src, float* dst, int batch, int rows, int K, int rows_p, int Kp,
+                          bool k_contiguous) {
+  cudaStream_t s = ctx().stream;
+  if (k_contiguous) {
+    int vec = (aligned16(src) && K % 4 == 0) ? 1 : 0;
+    int64_t items = (int64_t)rows_p * (Kp / 4);
+    int grid = stream_grid(items, 256, 8);
+    split_copy_kernel<<<dim3(grid, 1, batch), 256, 0, s>>>(src, dst, rows, K, rows_p, Kp, vec);
+  } else {
+    split_transpose_kernel<<<dim3(ceil_div(Kp, 32), ceil_div(rows_p, 32), batch), 256, 0, s>>>(src, dst, rows, K,
+                                                                                               rows_p, Kp);
+  }
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "operand split launch");
+}
+
+template <int BK>
+static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
+  using C = Cfg<BK>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_kernel<BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      C::kSmemBytes),
+                 "cudaFuncSetAttribute(gemm)"))
+      return false;
+    attr_set = true;
+  }
+  const int tiles = p.batch * p.mblks * p.nblks;
+  const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
+  gemm_3xtf32_kernel<BK><<<grid, kGemmThreads, C::kSmemBytes, ctx().stream>>>(ma, mb, p);
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch");
+}
+
+bool launch_gemm_3xtf32(const GemmArgs& g) {
+  if (!gemm_3xtf32_supported(g)) {
+    set_error(CLEAVE_CUDA_ERR_UNSUPPORTED, "3xTF32 GEMM: problem %d x %d x %d (batch %d) is out of range", g.m, g.n,
+              g.k, g.batch);
+    return false;
+  }
+  const int bk = choose_bk();
+  const int Kp = round_up(g.k, 32);        // multiple of both K-block sizes
+  const int Mp = round_up(g.m, BM);
+  const int Np = round_up(g.n, BN);
+  // Bound the split workspace: process the batch in chunks of at most ~4 GiB of planes.
+  const int64_t per_batch_bytes = 2ll * ((int64_t)Mp + Np) * Kp * 4;
+  int chunk = (int)((4ll << 30) / per_batch_bytes);
+  if (chunk < 1) chunk = 1;
+  if (chunk > g.batch) chunk = g.batch;
+
+  float* wa = scratch_alloc((int64_t)chunk * 2 * Mp * Kp * 4);
+  if (!wa) return false;
+  float* wb = scratch_alloc((int64_t)chunk * 2 * Np * Kp * 4);
+  if (!wb) { scratch_free(wa); return false; }
+
+  bool ok = true;
+  for (int b0 = 0; ok && b0 < g.batch; b0 += chunk) {
+    const int nb = (g.batch - b0) < chunk ? (g.batch - b0) : chunk;
+    const float* a = g.a + (int64_t)b0 * g.m * g.k;
+    const float* b = g.b + (int64_t)b0 * g.k * g.n;
+    // A is K-contiguous when stored [m,k]; B is K-contiguous when stored [n,k].
+    ok = split_operand(a, wa, nb, g.m, g.k, Mp, Kp, g.trans_a == 0) &&
+         split_operand(b, wb, nb, g.n, g.k, Np, Kp, g.trans_b != 0);
+    if (!ok) break;
+    CUtensorMap ma, mb;
+    ok = make_operand_map(&ma, wa, Mp, Kp, nb, bk, BM) && make_operand_map(&mb, wb, Np, Kp, nb, bk, BN);
+    if (!ok) break;
+    TcParams p;
+    p.c = g.c + (int64_t)b0 * g.m * g.n;
+    p.bias = g.bias;
+    p.m = g.m;
+    p.n = g.n;
+    p.num_kb = Kp / bk;
+    p.batch = nb;
+    p.mblks = Mp / BM;
+    p.nblks = Np / BN;
+    p.act = g.act;
+    p.status = ctx().status_dev;
+    ok = bk == 32 ? run_tc<32>(ma, mb, p) : run_tc<16>(ma, mb, p);
+  }
+  scratch_free(wa);
+  scratch_free(wb);
+  return ok;
+}
+
+}  // namespace cleave

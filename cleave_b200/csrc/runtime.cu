@@ -1,0 +1,425 @@
+// Runtime half of libcleave_cuda: device context, pooled allocator, handle table, transfers,
+// error channel.  Plays the part cleave_alloc / cleave_realloc / dynarray_* play in the
+// reference runtime (cleave-rt/src/lib.rs:56-71, :146-213), for device memory.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#include "common.cuh"
+
+namespace cleave {
+
+static std::recursive_mutex g_mu;
+static Context g_ctx;
+static std::unordered_set<Buf*> g_live;
+static std::unordered_map<int64_t, std::vector<void*>> g_free_blocks;   // block size -> cached blocks
+static std::unordered_map<void*, int64_t> g_scratch_sizes;
+static int64_t g_live_bytes = 0;
+static int64_t g_cached_bytes = 0;
+static int64_t g_launches = 0;
+
+static thread_local int t_err_code = 0;
+static thread_local char t_err_msg[512] = "";
+
+Context& ctx() { return g_ctx; }
+std::recursive_mutex& api_mutex() { return g_mu; }
+
+int set_error(int code, const char* fmt, ...) {
+  t_err_code = code;
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_err_msg, sizeof(t_err_msg), fmt, ap);
+  va_end(ap);
+  const char* abort_env = getenv("CLEAVE_CUDA_ABORT_ON_ERROR");
+  if (abort_env && abort_env[0] == '1') {
+    fprintf(stderr, "libcleave_cuda: fatal: %s\n", t_err_msg);
+    abort();
+  }
+  return code;
+}
+
+bool cuda_ok(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return true;
+  set_error(CLEAVE_CUDA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return false;
+}
+
+static bool init_device(int device) {
+  if (g_ctx.ready && (device < 0 || device == g_ctx.device)) return true;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    set_error(CLEAVE_CUDA_ERR_NO_DEVICE, "no CUDA device available (%s); this library has no CPU fallback",
+              e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    return false;
+  }
+  if (device < 0) {
+    const char* env = getenv("CLEAVE_CUDA_DEVICE");
+    device = env ? atoi(env) : 0;
+  }
+  if (device >= count) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "device %d requested but only %d present", device, count);
+    return false;
+  }
+  if (g_ctx.ready) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "already initialised on device %d; one device per process", g_ctx.device);
+    return false;
+  }
+  if (!cuda_ok(cudaSetDevice(device), "cudaSetDevice")) return false;
+  cudaDeviceProp prop;
+  if (!cuda_ok(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties")) return false;
+  if (prop.major != 10) {
+    set_error(CLEAVE_CUDA_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+              prop.major, prop.minor);
+    return false;
+  }
+  g_ctx.device = device;
+  g_ctx.sm_count = prop.multiProcessorCount;
+  if (!cuda_ok(cudaStreamCreateWithFlags(&g_ctx.own_stream, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
+  g_ctx.stream = g_ctx.own_stream;
+  if (!cuda_ok(cudaHostAlloc((void**)&g_ctx.status_host, sizeof(DeviceStatus), cudaHostAllocMapped), "cudaHostAlloc"))
+    return false;
+  memset(g_ctx.status_host, 0, sizeof(DeviceStatus));
+  if (!cuda_ok(cudaHostGetDevicePointer((void**)&g_ctx.status_dev, g_ctx.status_host, 0), "cudaHostGetDevicePointer"))
+    return false;
+  if (!cuda_ok(cudaHostAlloc((void**)&g_ctx.scalar_host, 64 * sizeof(float), cudaHostAllocDefault), "cudaHostAlloc"))
+    return false;
+  g_ctx.ready = true;
+  return true;
+}
+
+bool ensure_init() {
+  if (g_ctx.ready) {
+    // Calls may arrive on a host thread that never selected the device.
+    int cur = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur != g_ctx.device) cudaSetDevice(g_ctx.device);
+    return true;
+  }
+  return init_device(-1);
+}
+
+int check_device_status() {
+  if (!g_ctx.status_host) return CLEAVE_CUDA_OK;
+  DeviceStatus s = *g_ctx.status_host;
+  if (s.code == 0) return CLEAVE_CUDA_OK;
+  memset(g_ctx.status_host, 0, sizeof(DeviceStatus));
+  return set_error(CLEAVE_CUDA_ERR_DEVICE_TIMEOUT,
+                   "a kernel gave up a bounded wait (code %d, location %d, block %d, detail %d); "
+                   "results of the queued work are invalid",
+                   s.code, s.where, s.block, s.detail);
+}
+
+void count_launch(int n) { g_launches += n; }
+
+// ---- pool ----------------------------------------------------------------------------
+static int64_t block_size_for(int64_t bytes) {
+  if (bytes < 512) bytes = 512;
+  if (bytes <= (1 << 20)) {
+    int64_t b = 512;
+    while (b < bytes) b <<= 1;
+    return b;
+  }
+  const int64_t g = 2 << 20;
+  return (bytes + g - 1) / g * g;
+}
+
+static void* pool_alloc(int64_t bytes, int64_t* block_bytes) {
+  int64_t bs = block_size_for(bytes);
+  *block_bytes = bs;
+  auto it = g_free_blocks.find(bs);
+  if (it != g_free_blocks.end() && !it->second.empty()) {
+    void* p = it->second.back();
+    it->second.pop_back();
+    g_cached_bytes -= bs;
+    return p;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bs);
+  if (e != cudaSuccess) {
+    // Give cached blocks back to the driver and retry once.
+    cudaGetLastError();
+    cudaStreamSynchronize(g_ctx.stream);
+    for (auto& kv : g_free_blocks) {
+      for (void* q : kv.second) cudaFree(q);
+      kv.second.clear();
+    }
+    g_cached_bytes = 0;
+    e = cudaMalloc(&p, (size_t)bs);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error(CLEAVE_CUDA_ERR_OOM, "device allocation of %lld bytes failed: %s", (long long)bs, cudaGetErrorString(e));
+    return nullptr;
+  }
+  return p;
+}
+
+// Blocks go straight back to the free list: all work of this library runs on one stream,
+// so a later user of the block is ordered after every kernel that touched it.
+static void pool_free(void* p, int64_t block_bytes) {
+  g_free_blocks[block_bytes].push_back(p);
+  g_cached_bytes += block_bytes;
+}
+
+Buf* new_buf(int64_t len) {
+  if (len <= 0) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "tensor length must be positive, got %lld", (long long)len);
+    return nullptr;
+  }
+  if (!ensure_init()) return nullptr;
+  int64_t bs = 0;
+  void* p = pool_alloc(len * (int64_t)sizeof(float), &bs);
+  if (!p) return nullptr;
+  Buf* b = new Buf{kMagic, (float*)p, len, bs};
+  g_live.insert(b);
+  g_live_bytes += bs;
+  return b;
+}
+
+Buf* as_buf(cleave_buf h, const char* what) {
+  Buf* b = (Buf*)h;
+  if (!b || g_live.find(b) == g_live.end() || b->magic != kMagic) {
+    set_error(CLEAVE_CUDA_ERR_BAD_HANDLE, "%s: not a live tensor handle (%p)", what, (void*)h);
+    return nullptr;
+  }
+  return b;
+}
+
+void release_buf(Buf* b) {
+  g_live.erase(b);
+  if (b->cap_bytes) {
+    pool_free(b->ptr, b->cap_bytes);
+    g_live_bytes -= b->cap_bytes;
+  }
+  b->magic = 0;
+  delete b;
+}
+
+float* scratch_alloc(int64_t bytes) {
+  if (!ensure_init()) return nullptr;
+  int64_t bs = 0;
+  void* p = pool_alloc(bytes, &bs);
+  if (p) g_scratch_sizes[p] = bs;
+  return (float*)p;
+}
+
+void scratch_free(float* p) {
+  if (!p) return;
+  auto it = g_scratch_sizes.find(p);
+  if (it == g_scratch_sizes.end()) return;
+  pool_free(p, it->second);
+  g_scratch_sizes.erase(it);
+}
+
+float read_scalar(const float* dev_scalar) {
+  Context& c = g_ctx;
+  if (!cuda_ok(cudaMemcpyAsync(c.scalar_host, dev_scalar, sizeof(float), cudaMemcpyDeviceToHost, c.stream),
+               "cudaMemcpyAsync(scalar)"))
+    return NAN;
+  if (!cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize")) return NAN;
+  if (check_device_status() != CLEAVE_CUDA_OK) return NAN;
+  return c.scalar_host[0];
+}
+
+}  // namespace cleave
+
+using namespace cleave;
+
+extern "C" {
+
+int32_t cleave_cuda_init(int32_t device) {
+  ApiLock lock;
+  return init_device(device) ? CLEAVE_CUDA_OK : t_err_code;
+}
+
+int32_t cleave_cuda_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int32_t cleave_cuda_last_error(void) { return t_err_code; }
+const char* cleave_cuda_last_error_message(void) { return t_err_msg; }
+void cleave_cuda_clear_error(void) {
+  t_err_code = 0;
+  t_err_msg[0] = 0;
+}
+
+int32_t cleave_cuda_sync(void) {
+  ApiLock lock;
+  if (!ensure_init()) return t_err_code;
+  if (!cuda_ok(cudaStreamSynchronize(g_ctx.stream), "cudaStreamSynchronize")) return t_err_code;
+  return check_device_status();
+}
+
+void cleave_cuda_set_stream(void* s) {
+  ApiLock lock;
+  if (!ensure_init()) return;
+  // Order the new stream after everything queued so far, so pooled blocks stay safe to reuse.
+  cudaStreamSynchronize(g_ctx.stream);
+  g_ctx.stream = s ? (cudaStream_t)s : g_ctx.own_stream;
+}
+
+void* cleave_cuda_get_stream(void) {
+  ApiLock lock;
+  if (!ensure_init()) return nullptr;
+  return (void*)g_ctx.stream;
+}
+
+void cleave_cuda_reset(void) {
+  ApiLock lock;
+  std::vector<Buf*> all(g_live.begin(), g_live.end());
+  for (Buf* b : all) release_buf(b);
+}
+
+void cleave_cuda_trim(void) {
+  ApiLock lock;
+  if (!g_ctx.ready) return;
+  cudaStreamSynchronize(g_ctx.stream);
+  for (auto& kv : g_free_blocks) {
+    for (void* q : kv.second) cudaFree(q);
+    kv.second.clear();
+  }
+  g_cached_bytes = 0;
+}
+
+int64_t cleave_cuda_live_bytes(void) {
+  ApiLock lock;
+  return g_live_bytes;
+}
+
+int64_t cleave_cuda_kernel_launches(void) {
+  ApiLock lock;
+  return g_launches;
+}
+
+void* cleave_cuda_host_alloc(int64_t bytes) {
+  ApiLock lock;
+  if (bytes <= 0) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "host_alloc: bytes must be positive");
+    return nullptr;
+  }
+  if (!ensure_init()) return nullptr;
+  void* p = nullptr;
+  cudaError_t e = cudaHostAlloc(&p, (size_t)bytes, cudaHostAllocDefault);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error(CLEAVE_CUDA_ERR_OOM, "pinned host allocation of %lld bytes failed: %s", (long long)bytes,
+              cudaGetErrorString(e));
+    return nullptr;
+  }
+  return p;
+}
+
+void cleave_cuda_host_free(void* p) {
+  ApiLock lock;
+  if (p && g_ctx.ready) cudaFreeHost(p);
+}
+
+cleave_buf cleave_cuda_alloc_f32(int64_t len) {
+  ApiLock lock;
+  return (cleave_buf)new_buf(len);
+}
+
+int32_t cleave_cuda_upload_into_f32(cleave_buf t, const float* host, int64_t len) {
+  ApiLock lock;
+  Buf* b = as_buf(t, "upload_into");
+  if (!b) return -t_err_code;
+  if (!host || len != b->len) return -set_error(CLEAVE_CUDA_ERR_SHAPE, "upload_into: %lld elements given, tensor has %lld",
+                                                (long long)len, (long long)b->len);
+  if (!cuda_ok(cudaMemcpyAsync(b->ptr, host, (size_t)len * sizeof(float), cudaMemcpyHostToDevice, g_ctx.stream),
+               "cudaMemcpyAsync(H2D)"))
+    return -t_err_code;
+  return CLEAVE_CUDA_OK;
+}
+
+cleave_buf cleave_cuda_upload_f32(const float* host, int64_t len) {
+  ApiLock lock;
+  if (!host) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "upload: NULL host pointer");
+    return nullptr;
+  }
+  Buf* b = new_buf(len);
+  if (!b) return nullptr;
+  if (!cuda_ok(cudaMemcpyAsync(b->ptr, host, (size_t)len * sizeof(float), cudaMemcpyHostToDevice, g_ctx.stream),
+               "cudaMemcpyAsync(H2D)")) {
+    release_buf(b);
+    return nullptr;
+  }
+  // The caller's array may be a temporary (cleave passes a stack array): finish the copy
+  // before returning unless the source is pinned memory, which this call cannot know, so
+  // always wait.  Pinned sources still get the full-bandwidth DMA path.
+  if (!cuda_ok(cudaStreamSynchronize(g_ctx.stream), "cudaStreamSynchronize")) {
+    release_buf(b);
+    return nullptr;
+  }
+  return (cleave_buf)b;
+}
+
+int64_t cleave_cuda_download_f32(cleave_buf t, float* host, int64_t len) {
+  ApiLock lock;
+  Buf* b = as_buf(t, "download");
+  if (!b) return -t_err_code;
+  if (!host || len != b->len)
+    return -set_error(CLEAVE_CUDA_ERR_SHAPE, "download: room for %lld elements, tensor has %lld", (long long)len,
+                      (long long)b->len);
+  if (!cuda_ok(cudaMemcpyAsync(host, b->ptr, (size_t)len * sizeof(float), cudaMemcpyDeviceToHost, g_ctx.stream),
+               "cudaMemcpyAsync(D2H)"))
+    return -t_err_code;
+  if (!cuda_ok(cudaStreamSynchronize(g_ctx.stream), "cudaStreamSynchronize")) return -t_err_code;
+  if (check_device_status() != CLEAVE_CUDA_OK) return -t_err_code;
+  return len;
+}
+
+float cleave_cuda_get_f32(cleave_buf t, int64_t i) {
+  ApiLock lock;
+  Buf* b = as_buf(t, "get");
+  if (!b) return NAN;
+  if (i < 0 || i >= b->len) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "get: index %lld outside [0, %lld)", (long long)i, (long long)b->len);
+    return NAN;
+  }
+  return read_scalar(b->ptr + i);
+}
+
+int64_t cleave_cuda_len(cleave_buf t) {
+  ApiLock lock;
+  Buf* b = as_buf(t, "len");
+  return b ? b->len : -t_err_code;
+}
+
+void cleave_cuda_free(cleave_buf t) {
+  ApiLock lock;
+  Buf* b = as_buf(t, "free");
+  if (b) release_buf(b);
+}
+
+cleave_buf cleave_cuda_wrap_f32(void* device_ptr, int64_t len) {
+  ApiLock lock;
+  if (!device_ptr || len <= 0 || ((uintptr_t)device_ptr & 3u)) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "wrap: need a 4-byte aligned device pointer and a positive length");
+    return nullptr;
+  }
+  if (!ensure_init()) return nullptr;
+  Buf* b = new Buf{kMagic, (float*)device_ptr, len, 0};
+  g_live.insert(b);
+  return (cleave_buf)b;
+}
+
+void* cleave_cuda_data_ptr(cleave_buf t) {
+  ApiLock lock;
+  Buf* b = as_buf(t, "data_ptr");
+  return b ? (void*)b->ptr : nullptr;
+}
+
+}  // extern "C"

@@ -1,0 +1,195 @@
+"""Host-side mirror of cleave's ``stdlib/linalg`` over device tensors.
+
+``Tensor`` corresponds to ``struct Tensor<T: Float, const Dims...: i32>``
+(stdlib/linalg/tensor.cleave:40): dense, row-major, static shape, immutable value.  Its
+operators are the ``Ring<Tensor<T, Dims...>>`` impl (tensor.cleave:66-80) -- ``+ - * /`` and unary
+``-`` are elementwise on same-shape operands, ``zero`` is the zero tensor -- ``t[i, j]`` is
+``Index::index`` (tensor.cleave:129-133) and ``matmul`` is ``MatMul::matmul``
+(stdlib/linalg/matrix.cleave:22-62).  Each method is one call into ``libcleave_cuda`` with
+exactly the arguments the matching ``extern(cleave_cuda_*) fn`` would pass.
+
+Where cleave rejects a program at compile time (shape mismatch, wrong index rank) these
+functions raise ``TypeError``; a failing library call raises ``CleaveCudaError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import numpy as np
+
+from ._lib import c_f32p, lib, raise_last_error
+
+
+def _prod(dims) -> int:
+    return int(math.prod(dims))
+
+
+class Tensor:
+    """``Tensor<f32, Dims...>``: a device-resident f32 array with a static shape."""
+
+    __slots__ = ("_h", "dims", "_owner")
+
+    def __init__(self, data=None, *, dims=None, _handle=None):
+        """``Tensor(data)`` uploads a nested list / array, like ``Tensor::<f32, ...>(data: [...])``."""
+        if _handle is not None:
+            self._h, self.dims = _handle, tuple(int(d) for d in dims)
+            return
+        a = np.ascontiguousarray(data, dtype=np.float32)
+        if dims is not None and tuple(dims) != a.shape:
+            raise TypeError(f"data has shape {a.shape}, declared dims are {tuple(dims)}")
+        if a.ndim < 1 or a.size == 0:
+            raise TypeError("a Tensor needs rank >= 1 and at least one element")
+        h = lib().cleave_cuda_upload_f32(a.ctypes.data_as(c_f32p), a.size)
+        if not h:
+            raise_last_error("Tensor upload")
+        self._h, self.dims = h, a.shape
+
+    # ---- construction -------------------------------------------------------------------
+    @classmethod
+    def _wrap(cls, handle, dims, what="op"):
+        if not handle:
+            raise_last_error(what)
+        return cls(dims=dims, _handle=handle)
+
+    @classmethod
+    def zero(cls, *dims) -> "Tensor":
+        """``Ring::zero()`` for ``Tensor<f32, dims...>`` (tensor.cleave:79)."""
+        return cls._wrap(lib().cleave_cuda_zeros_f32(_prod(dims)), dims, "zero")
+
+    @classmethod
+    def filled(cls, value: float, *dims) -> "Tensor":
+        """``Tensor::<T, Dims...>(data: [value; Dims...])``."""
+        return cls._wrap(lib().cleave_cuda_fill_f32(float(value), _prod(dims)), dims, "fill")
+
+    @classmethod
+    def empty(cls, *dims) -> "Tensor":
+        return cls._wrap(lib().cleave_cuda_alloc_f32(_prod(dims)), dims, "alloc")
+
+    @classmethod
+    def from_device_ptr(cls, ptr: int, *dims) -> "Tensor":
+        """Non-owning view of caller-owned device memory (e.g. a torch CUDA tensor's data_ptr)."""
+        return cls._wrap(lib().cleave_cuda_wrap_f32(ctypes.c_void_p(ptr), _prod(dims)), dims, "wrap")
+
+    # ---- readback -----------------------------------------------------------------------
+    @property
+    def numel(self) -> int:
+        return _prod(self.dims)
+
+    @property
+    def data_ptr(self) -> int:
+        return int(lib().cleave_cuda_data_ptr(self._h) or 0)
+
+    def numpy(self, out: np.ndarray | None = None) -> np.ndarray:
+        if out is None:
+            out = np.empty(self.dims, np.float32)
+        assert out.dtype == np.float32 and out.size == self.numel and out.flags.c_contiguous
+        if lib().cleave_cuda_download_f32(self._h, out.ctypes.data_as(c_f32p), out.size) < 0:
+            raise_last_error("download")
+        return out
+
+    def reshape(self, *dims) -> "Tensor":
+        """Same storage, new static shape (row-major flattening is the identity on memory)."""
+        if _prod(dims) != self.numel:
+            raise TypeError(f"cannot view {self.dims} as {dims}")
+        t = Tensor.from_device_ptr(self.data_ptr, *dims)
+        t._owner = self   # keep the storage alive
+        return t
+
+    def __getitem__(self, idx) -> float:
+        """``t[i, j, ...]`` -> scalar; the index count must equal the rank (tensor.cleave:129-133)."""
+        idx = idx if isinstance(idx, tuple) else (idx,)
+        if len(idx) != len(self.dims):
+            raise TypeError(f"tensor of rank {len(self.dims)} indexed with {len(idx)} indices")
+        flat = 0
+        for i, d in zip(idx, self.dims):
+            if not 0 <= int(i) < d:
+                raise IndexError(f"index {idx} out of bounds for dims {self.dims}")
+            flat = flat * d + int(i)
+        v = lib().cleave_cuda_get_f32(self._h, flat)
+        if math.isnan(v) and lib().cleave_cuda_last_error():
+            raise_last_error("index")
+        return float(np.float32(v))
+
+    # ---- Ring<Tensor> -------------------------------------------------------------------
+    def _binary(self, other, fn, name):
+        if not isinstance(other, Tensor):
+            raise TypeError(f"{name}: operand is not a Tensor (a bare scalar is not broadcast)")
+        if other.dims != self.dims:
+            raise TypeError(f"{name}: mismatched types Tensor<f32,{self.dims}> and Tensor<f32,{other.dims}>")
+        return Tensor._wrap(fn(self._h, other._h), self.dims, name)
+
+    def __add__(self, o): return self._binary(o, lib().cleave_cuda_add_f32, "add")
+    def __sub__(self, o): return self._binary(o, lib().cleave_cuda_sub_f32, "sub")
+    def __mul__(self, o): return self._binary(o, lib().cleave_cuda_mul_f32, "mul")
+    def __truediv__(self, o): return self._binary(o, lib().cleave_cuda_div_f32, "div")
+    def __neg__(self): return Tensor._wrap(lib().cleave_cuda_neg_f32(self._h), self.dims, "neg")
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                lib().cleave_cuda_free(h)
+            except Exception:  # interpreter shutdown
+                pass
+
+    def __repr__(self):
+        return f"Tensor<f32, {', '.join(map(str, self.dims))}>"
+
+
+def matmul(a: Tensor, b: Tensor) -> Tensor:
+    """``MatMul<Tensor<T,N,M>, Tensor<T,M,K>, Tensor<T,N,K>>::matmul`` (matrix.cleave:27-62)."""
+    if len(a.dims) != 2 or len(b.dims) != 2 or a.dims[1] != b.dims[0]:
+        raise TypeError(f"matmul: no impl for Tensor<f32,{a.dims}> x Tensor<f32,{b.dims}>")
+    (m, k), n = a.dims, b.dims[1]
+    return Tensor._wrap(lib().cleave_cuda_gemm_f32(a._h, b._h, m, n, k), (m, n), "matmul")
+
+
+def matmul_nt(a: Tensor, b: Tensor) -> Tensor:
+    """``a @ b^T`` with b stored [n, k]: the ``matmul(d(a), b)`` half of the derivative rule
+    (matrix.cleave:24) pulled back to the first operand."""
+    if len(a.dims) != 2 or len(b.dims) != 2 or a.dims[1] != b.dims[1]:
+        raise TypeError(f"matmul_nt: no impl for Tensor<f32,{a.dims}> x Tensor<f32,{b.dims}>^T")
+    (m, k), n = a.dims, b.dims[0]
+    return Tensor._wrap(lib().cleave_cuda_gemm_nt_f32(a._h, b._h, m, n, k), (m, n), "matmul_nt")
+
+
+def matmul_tn(a: Tensor, b: Tensor) -> Tensor:
+    """``a^T @ b`` with a stored [k, m]: the ``matmul(a, d(b))`` half pulled back to the second operand."""
+    if len(a.dims) != 2 or len(b.dims) != 2 or a.dims[0] != b.dims[0]:
+        raise TypeError(f"matmul_tn: no impl for Tensor<f32,{a.dims}>^T x Tensor<f32,{b.dims}>")
+    (k, m), n = a.dims, b.dims[1]
+    return Tensor._wrap(lib().cleave_cuda_gemm_tn_f32(a._h, b._h, m, n, k), (m, n), "matmul_tn")
+
+
+def batched_matmul(a: Tensor, b: Tensor) -> Tensor:
+    """``batch`` independent products: a is [batch, m, k], b is [batch, k, n]."""
+    if len(a.dims) != 3 or len(b.dims) != 3 or a.dims[0] != b.dims[0] or a.dims[2] != b.dims[1]:
+        raise TypeError(f"batched_matmul: no impl for Tensor<f32,{a.dims}> x Tensor<f32,{b.dims}>")
+    batch, m, k = a.dims
+    n = b.dims[2]
+    return Tensor._wrap(lib().cleave_cuda_gemm_batched_f32(a._h, b._h, batch, m, n, k), (batch, m, n),
+                        "batched_matmul")
+
+
+GEMM_AUTO, GEMM_EXACT, GEMM_3XTF32 = 0, 1, 2
+ACT = {"identity": 0, "relu": 1, "sigmoid": 2, "tanh": 3}
+
+
+def gemm_into(c: Tensor, a: Tensor, b: Tensor, *, trans_a=False, trans_b=False, algo=GEMM_AUTO,
+              bias: Tensor | None = None, act: str = "identity") -> Tensor:
+    """General product written into ``c`` (``cleave_cuda_gemm_ex_f32``).  Shapes follow the stored
+    layouts: a is [m,k] ([k,m] if trans_a), b is [k,n] ([n,k] if trans_b); a leading batch
+    dimension on all three runs independent products."""
+    batched = len(c.dims) == 3
+    batch = c.dims[0] if batched else 1
+    ad, bd, cd = (t.dims[1:] if batched else t.dims for t in (a, b, c))
+    m, k = (ad[1], ad[0]) if trans_a else ad
+    k2, n = (bd[1], bd[0]) if trans_b else bd
+    if k != k2 or tuple(cd) != (m, n) or (batched and not (a.dims[0] == b.dims[0] == batch)):
+        raise TypeError(f"gemm_into: shapes {a.dims}, {b.dims} -> {c.dims} do not agree")
+    r = lib().cleave_cuda_gemm_ex_f32(c._h, a._h, b._h, batch, m, n, k, int(trans_a), int(trans_b), algo,
+                                      bias._h if bias is not None else None, ACT[act])
+    if r != 0:
+        raise_last_error("gemm_into")
+    return c

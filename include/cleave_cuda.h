@@ -1,0 +1,173 @@
+/* libcleave_cuda -- C ABI of the B200 (sm_100a) tensor backend for cleave.
+ *
+ * Every entry point uses only what cleave's extern-call lowering can pass
+ * (cleave/src/mlir_lower.rs:1061-1130, :1720-1751, :2127-2160 in the reference):
+ *   - scalars i32 / i64 / f32 by value,
+ *   - an opaque struct handle as ONE pointer (mlir_lower.rs:145), here `cleave_buf`,
+ *   - an array `[T; ...]` as the pair (T* ptr, int64_t total_len),
+ *   - one scalar / handle result, or void.
+ * A `cleave_buf` plays the role `RawBuf` plays for DynArray
+ * (stdlib/dynarray/dynarray.cleave:29, cleave-rt/src/lib.rs:169-213): it is produced by an
+ * extern function, only ever passed back to extern functions, and owns a dense, row-major,
+ * contiguous f32 device array -- the layout of `Tensor<T, Dims...>`
+ * (stdlib/linalg/tensor.cleave:40, mlir_lower.rs:276-295).  Shapes stay in the cleave type
+ * system (const generics are i32) and are passed as i32 scalars where an op needs them.
+ *
+ * Value semantics: tensor values in cleave are immutable SSA values, so every op returns a
+ * NEW handle; the `_into` forms write into a handle the caller already owns.
+ *
+ * Errors: the reference runtime has no error channel (it panics: cleave-rt/src/lib.rs:69).
+ * Here a failing call returns NULL (handle), NaN (f32 scalar) or a negative code (i32/i64)
+ * and records a thread-local code + message readable with cleave_cuda_last_error*().
+ * With CLEAVE_CUDA_ABORT_ON_ERROR=1 in the environment a failing call aborts the process
+ * instead, which is the reference's behaviour.  There is no CPU fallback: without a CUDA
+ * device every compute call fails with CLEAVE_CUDA_ERR_NO_DEVICE.
+ *
+ * Threads: calls may come from several host threads; they are serialised on one device
+ * stream per process.  Work is asynchronous until a scalar-returning op, a download or
+ * cleave_cuda_sync().
+ */
+#ifndef CLEAVE_CUDA_H
+#define CLEAVE_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cleave_buf_s* cleave_buf; /* opaque device tensor handle ("DevBuf") */
+
+enum {
+  CLEAVE_CUDA_OK = 0,
+  CLEAVE_CUDA_ERR_NO_DEVICE = 1,   /* no usable CUDA device / driver */
+  CLEAVE_CUDA_ERR_BAD_HANDLE = 2,  /* NULL, freed or foreign handle */
+  CLEAVE_CUDA_ERR_SHAPE = 3,       /* lengths / dims inconsistent with the operands */
+  CLEAVE_CUDA_ERR_ARG = 4,         /* other invalid argument */
+  CLEAVE_CUDA_ERR_OOM = 5,         /* device or pinned-host allocation failed */
+  CLEAVE_CUDA_ERR_CUDA = 6,        /* a CUDA runtime call failed (message has the text) */
+  CLEAVE_CUDA_ERR_DEVICE_TIMEOUT = 7, /* a bounded in-kernel wait gave up; results invalid */
+  CLEAVE_CUDA_ERR_UNSUPPORTED = 8
+};
+
+/* activation codes for the fused entry points */
+enum { CLEAVE_ACT_IDENTITY = 0, CLEAVE_ACT_RELU = 1, CLEAVE_ACT_SIGMOID = 2, CLEAVE_ACT_TANH = 3 };
+
+/* GEMM algorithm selector for cleave_cuda_gemm_ex_f32 */
+enum {
+  CLEAVE_GEMM_AUTO = 0,   /* tensor-core path for large problems, exact path for small ones */
+  CLEAVE_GEMM_EXACT = 1,  /* SIMT f32, k-ascending multiply-then-add: bit-identical to the CPU path */
+  CLEAVE_GEMM_3XTF32 = 2  /* tcgen05 + TMEM + TMA, split-precision TF32 (3 MMAs per product) */
+};
+
+/* ------------------------------------------------------------------ runtime
+ * No counterpart in cleave-rt (it has no device); modelled on its allocation pair
+ * cleave_alloc / cleave_realloc (cleave-rt/src/lib.rs:56-71, :146-155). */
+int32_t cleave_cuda_init(int32_t device);            /* select device, create the stream; idempotent */
+int32_t cleave_cuda_device_count(void);
+int32_t cleave_cuda_last_error(void);                /* code of this thread's last failing call */
+const char* cleave_cuda_last_error_message(void);    /* its message (thread-local storage) */
+void cleave_cuda_clear_error(void);
+int32_t cleave_cuda_sync(void);                      /* wait for all queued work; returns a code */
+void cleave_cuda_set_stream(void* cuda_stream);      /* run on a caller-owned cudaStream_t (NULL: own stream) */
+void* cleave_cuda_get_stream(void);
+void cleave_cuda_reset(void);                        /* invalidate every handle, keep memory cached */
+void cleave_cuda_trim(void);                         /* return cached device memory to the driver */
+int64_t cleave_cuda_live_bytes(void);                /* bytes held by live handles */
+int64_t cleave_cuda_kernel_launches(void);           /* kernels launched by this library so far */
+void* cleave_cuda_host_alloc(int64_t bytes);         /* pinned host memory for fast transfers */
+void cleave_cuda_host_free(void* p);
+
+/* ------------------------------------------------------------------ construction / readback
+ * Replaces tensor.from_elements (mlir_lower.rs:1447-1476), the array-repeat fill behind
+ * Ring::zero (stdlib/linalg/tensor.cleave:79, mlir_lower.rs:1176-1272) and tensor.extract
+ * (stdlib/linalg/tensor.cleave:129-133, mlir_lower.rs:1972-2002). */
+cleave_buf cleave_cuda_alloc_f32(int64_t len);                              /* uninitialised */
+cleave_buf cleave_cuda_upload_f32(const float* host, int64_t len);          /* [f32; len] -> device */
+int64_t cleave_cuda_download_f32(cleave_buf t, float* host, int64_t len);   /* returns len or <0 */
+int32_t cleave_cuda_upload_into_f32(cleave_buf t, const float* host, int64_t len);
+cleave_buf cleave_cuda_fill_f32(float value, int64_t len);
+cleave_buf cleave_cuda_zeros_f32(int64_t len);
+float cleave_cuda_get_f32(cleave_buf t, int64_t flat_index);                /* row-major flat index */
+int64_t cleave_cuda_len(cleave_buf t);
+void cleave_cuda_free(cleave_buf t);
+cleave_buf cleave_cuda_wrap_f32(void* device_ptr, int64_t len);             /* non-owning view of caller memory */
+void* cleave_cuda_data_ptr(cleave_buf t);
+
+/* ------------------------------------------------------------------ Ring<Tensor<T, Dims...>>
+ * stdlib/linalg/tensor.cleave:66-80: add/sub/mul/div/neg = arith.addf/subf/mulf/divf/negf on
+ * same-shape tensors (no broadcasting).  One IEEE-754 operation per element. */
+cleave_buf cleave_cuda_add_f32(cleave_buf a, cleave_buf b);
+cleave_buf cleave_cuda_sub_f32(cleave_buf a, cleave_buf b);
+cleave_buf cleave_cuda_mul_f32(cleave_buf a, cleave_buf b);
+cleave_buf cleave_cuda_div_f32(cleave_buf a, cleave_buf b);
+cleave_buf cleave_cuda_neg_f32(cleave_buf a);
+
+/* ------------------------------------------------------------------ Activation / Transcendental
+ * stdlib/nn/nn.cleave:82-95 (tensor) and :54-64 (scalar); stdlib/num/num.cleave:227-233.
+ * relu = NaN-propagating max(x, 0); sigmoid = 1/(1+exp(-x)) in ONE pass instead of the
+ * reference's four; tanh, exp. */
+cleave_buf cleave_cuda_relu_f32(cleave_buf x);
+cleave_buf cleave_cuda_sigmoid_f32(cleave_buf x);
+cleave_buf cleave_cuda_tanh_f32(cleave_buf x);
+cleave_buf cleave_cuda_exp_f32(cleave_buf x);
+/* Derivative rules applied to a whole tensor, fused with the upstream factor
+ * (stdlib/num/num.cleave:222-223; sigmoid through the chain of :123-136).
+ * y = forward OUTPUT for tanh/sigmoid, x = forward INPUT for relu, g = upstream gradient. */
+cleave_buf cleave_cuda_tanh_bwd_f32(cleave_buf y, cleave_buf g);     /* (1 - y*y) * g */
+cleave_buf cleave_cuda_sigmoid_bwd_f32(cleave_buf y, cleave_buf g);  /* y*(1 - y) * g */
+cleave_buf cleave_cuda_relu_bwd_f32(cleave_buf x, cleave_buf g);     /* x > 0 ? g : 0 */
+
+/* ------------------------------------------------------------------ Sum / Mean / Max
+ * stdlib/nn/nn.cleave:111-149.  sum is a deterministic tree (fixed grid, fixed order), not
+ * the reference's left-to-right chain: equal within rounding, reproducible run to run.
+ * max_of keeps the reference's strict-> scan semantics for NaN (NaN in v[0] wins, later
+ * NaNs are skipped). */
+float cleave_cuda_sum_f32(cleave_buf v);
+float cleave_cuda_mean_f32(cleave_buf v);
+float cleave_cuda_max_f32(cleave_buf v);
+/* Sum applied to each column of a rows x cols matrix (bias gradients). */
+cleave_buf cleave_cuda_colsum_f32(cleave_buf x, int32_t rows, int32_t cols);
+int32_t cleave_cuda_colsum_into_f32(cleave_buf out, cleave_buf x, int32_t rows, int32_t cols);
+
+/* ------------------------------------------------------------------ MatMul
+ * stdlib/linalg/matrix.cleave:22-62: MatMul<Tensor<T,N,M>, Tensor<T,M,K>, Tensor<T,N,K>>,
+ * linalg.matmul into a zero tensor (region mlir_lower.rs:2089-2120).  Here the dims are named
+ * BLAS-style: C[m,n] = A[m,k] * B[k,n]  (cleave's N,M,K are m,k,n). */
+cleave_buf cleave_cuda_gemm_f32(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k);
+/* Transposed-operand forms needed by the derivative rule matmul(da,b) + matmul(a,db)
+ * (stdlib/linalg/matrix.cleave:24) evaluated in reverse mode:
+ *   nt: C[m,n] = A[m,k] * B[n,k]^T        tn: C[m,n] = A[k,m]^T * B[k,n] */
+cleave_buf cleave_cuda_gemm_nt_f32(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k);
+cleave_buf cleave_cuda_gemm_tn_f32(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k);
+/* `batch` independent products, operands stacked along a leading batch dimension.
+ * (Named in the reference only as a comment, mlir_lower.rs:2078.) */
+cleave_buf cleave_cuda_gemm_batched_f32(cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n,
+                                        int32_t k);
+/* General form: writes C (caller-owned, batch*m*n elements).  trans_a / trans_b select the
+ * stored layout of the operands as above; algo is a CLEAVE_GEMM_* value; bias (may be NULL,
+ * n elements) is added to every row and act (CLEAVE_ACT_*) applied before the store. */
+int32_t cleave_cuda_gemm_ex_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m,
+                                int32_t n, int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo,
+                                cleave_buf bias, int32_t act);
+
+/* ------------------------------------------------------------------ compositions the programs spell out
+ * bias add: a rows x cols tensor plus a tensor whose rows all equal `bias`
+ * (arith.addf does not broadcast: stdlib/nn/nn.cleave:72-74), then an activation. */
+cleave_buf cleave_cuda_bias_act_f32(cleave_buf x, cleave_buf bias, int32_t rows, int32_t cols, int32_t act);
+/* mean((p - t)^2) (examples/linear_regression.cleave:20-30 with Mean, nn.cleave:119-139).
+ * If dp is non-NULL it receives 2*(p - t)/len, the gradient with respect to p. */
+float cleave_cuda_mse_f32(cleave_buf p, cleave_buf t, cleave_buf dp);
+/* w = w - lr * (gscale * g) in place (examples/xor.cleave:67-70); gscale folds the 1/G of a
+ * gradient mean over G data-parallel ranks into the same pass. */
+int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale);
+/* One linear-regression batch-gradient step in a single sweep over X[rows, feat]:
+ * pred = X w, loss = mean((pred - y)^2), grad = dloss/dw.  pred_out (rows) and grad_out
+ * (feat) are caller-owned handles; pred_out may be NULL.  feat <= 32.  Returns the loss. */
+float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out,
+                                  cleave_buf grad_out, int32_t rows, int32_t feat);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLEAVE_CUDA_H */

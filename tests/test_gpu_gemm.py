@@ -1,0 +1,148 @@
+"""Parity of the MatMul family with the CPU oracle: the exact CUDA-core path bit for bit, the
+tcgen05 3xTF32 path within 1e-5 (componentwise against sum|a||b|, and normwise)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import cleave_b200 as cb
+from cleave_b200 import linalg, workloads
+from cleave_b200.linalg import GEMM_3XTF32, GEMM_EXACT
+from oracle import ref
+
+from _util import TOL, assert_gemm_close, gemm_errors, rel_err
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+def gemm(a, b, algo, trans_a=False, trans_b=False, bias=None, act="identity", batch=None):
+    ta, tb = linalg.Tensor(a), linalg.Tensor(b)
+    if batch is None:
+        m = a.shape[1] if trans_a else a.shape[0]
+        n = b.shape[0] if trans_b else b.shape[1]
+        c = linalg.Tensor.empty(m, n)
+    else:
+        c = linalg.Tensor.empty(batch, a.shape[1], b.shape[2])
+    linalg.gemm_into(c, ta, tb, trans_a=trans_a, trans_b=trans_b, algo=algo,
+                     bias=linalg.Tensor(bias) if bias is not None else None, act=act)
+    cb.sync()
+    return c.numpy()
+
+
+def test_reference_known_answers_exact():
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_kats.json")) as f:
+        kats = json.load(f)
+    for case in kats["matmul"]:
+        c = linalg.matmul(linalg.Tensor(case["a"]), linalg.Tensor(case["b"]))
+        assert np.array_equal(c.numpy(), np.array(case["c"], f32)), case["cite"]
+    c = linalg.matmul(linalg.Tensor([[1, 2, 3], [4, 5, 6]]), linalg.Tensor([[7, 8], [9, 10], [11, 12]]))
+    assert (c[0, 0], c[0, 1], c[1, 0], c[1, 1]) == (58.0, 64.0, 139.0, 154.0)
+    z = linalg.matmul(linalg.Tensor([[1, 2], [3, 4]]), linalg.Tensor.zero(2, 2))
+    assert not z.numpy().any()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (2, 2, 3), (7, 5, 3), (33, 65, 17), (64, 64, 16), (100, 130, 77),
+                                   (128, 256, 64), (512, 512, 512)])
+def test_exact_path_is_bit_identical_to_the_reference_loop(m, n, k):
+    a, b = workloads.gemm_inputs(m, n, k)
+    assert np.array_equal(gemm(a, b, GEMM_EXACT), ref.matmul(a, b))
+
+
+def test_exact_path_transposed_and_batched():
+    a, b = workloads.gemm_inputs(70, 50, 90)
+    want = ref.matmul(a, b)
+    assert np.array_equal(gemm(np.ascontiguousarray(a.T), b, GEMM_EXACT, trans_a=True), want)
+    assert np.array_equal(gemm(a, np.ascontiguousarray(b.T), GEMM_EXACT, trans_b=True), want)
+    A = workloads.uniform_pm1(11, 3, 20, 30)
+    B = workloads.uniform_pm1(12, 3, 30, 10)
+    got = gemm(A, B, GEMM_EXACT, batch=3)
+    for i in range(3):
+        assert np.array_equal(got[i], ref.matmul(A[i], B[i]))
+
+
+# Shapes for the tensor-core path: one tile, one K-block; ragged in every dimension; several
+# tiles per CTA; more tiles than SMs; K not a multiple of the K-block; tall / wide.
+TC_SHAPES = [(128, 256, 16), (128, 256, 32), (128, 256, 64), (128, 256, 512), (256, 512, 128),
+             (100, 200, 50), (129, 257, 33), (1, 1, 1), (5, 300, 7), (300, 5, 1000),
+             (512, 512, 512), (1024, 1024, 1024), (2048, 4096, 256), (640, 768, 2048)]
+
+
+@pytest.mark.parametrize("m,n,k", TC_SHAPES)
+def test_3xtf32_path_within_tolerance(m, n, k):
+    a, b = workloads.gemm_inputs(m, n, k)
+    got = gemm(a, b, GEMM_3XTF32)
+    assert_gemm_close(got, a, b, what=(m, n, k))
+
+
+def test_3xtf32_matches_exact_path_on_exactly_representable_data():
+    # Small integers: every product and partial sum is exact in tf32 x tf32 -> f32.
+    rng = np.random.default_rng(0)
+    a = rng.integers(-8, 9, (256, 384)).astype(f32)
+    b = rng.integers(-8, 9, (384, 512)).astype(f32)
+    assert np.array_equal(gemm(a, b, GEMM_3XTF32), ref.matmul(a, b))
+
+
+def test_3xtf32_identity_and_layout():
+    # A = I picks out rows of B: any descriptor / swizzle / tile-decoding mistake shows as a permutation.
+    n = 512
+    b = workloads.uniform_pm1(5, n, n)
+    got = gemm(np.eye(n, dtype=f32), b, GEMM_3XTF32)
+    assert rel_err(got, b) <= 2e-6 and np.array_equal(np.argmax(got, axis=1), np.argmax(b, axis=1))
+    a = workloads.uniform_pm1(6, n, n)
+    got = gemm(a, np.eye(n, dtype=f32), GEMM_3XTF32)
+    assert rel_err(got, a) <= 2e-6
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 384), (130, 70, 200)])
+def test_3xtf32_transposed_operands(m, n, k):
+    a, b = workloads.gemm_inputs(m, n, k)
+    want = ref.matmul(a, b)
+    assert_gemm_close(gemm(np.ascontiguousarray(a.T), b, GEMM_3XTF32, trans_a=True), a, b, want, "tn")
+    assert_gemm_close(gemm(a, np.ascontiguousarray(b.T), GEMM_3XTF32, trans_b=True), a, b, want, "nt")
+
+
+def test_3xtf32_batched():
+    A = workloads.uniform_pm1(21, 5, 256, 128)
+    B = workloads.uniform_pm1(22, 5, 128, 512)
+    got = gemm(A, B, GEMM_3XTF32, batch=5)
+    for i in range(5):
+        assert_gemm_close(got[i], A[i], B[i], what=f"batch {i}")
+
+
+@pytest.mark.parametrize("act", ["identity", "tanh", "sigmoid", "relu"])
+def test_3xtf32_fused_bias_activation(act):
+    a, b = workloads.gemm_inputs(256, 512, 256)
+    a *= f32(0.1)
+    bias = workloads.uniform_pm1(7, 512)
+    z = ref.bias_add(ref.matmul(a, b), bias)
+    want = z if act == "identity" else getattr(ref, act)(z)
+    got = gemm(a, b, GEMM_3XTF32, bias=bias, act=act)
+    # activations are 1-Lipschitz here; compare on the scale of the pre-activation error bound
+    s = ref.matmul_absdot(a, b) + np.abs(bias)
+    assert np.max(np.abs(got.astype(np.float64) - want) / np.maximum(s, 1e-30)) <= TOL
+
+
+def test_cleave_matmul_dispatch_at_512_cubed():
+    # Benchmark configuration 0: C = A B, M = N = K = 512, uniform[-1,1).
+    a, b = workloads.gemm_inputs(512, 512, 512)
+    got = linalg.matmul(linalg.Tensor(a), linalg.Tensor(b)).numpy()
+    e = assert_gemm_close(got, a, b, what="512^3 auto")
+    print("512^3 errors:", e)
+
+
+def test_large_gemm_sampled_rows():
+    # 4096^3 is too slow for a full oracle pass in a test; check 64 sampled rows exactly as the
+    # reference loop computes them, plus a checksum-of-rows identity on the whole result.
+    m = n = k = 4096
+    a, b = workloads.gemm_inputs(m, n, k)
+    got = gemm(a, b, GEMM_3XTF32)
+    rows = np.random.default_rng(0).choice(m, 64, replace=False)
+    a_s = np.ascontiguousarray(a[rows])
+    assert_gemm_close(np.ascontiguousarray(got[rows]), a_s, b, what="4096^3 sampled rows")
+    # linearity: (1^T A) B == 1^T (A B)
+    lhs = (a.astype(np.float64).sum(axis=0) @ b.astype(np.float64))
+    rhs = got.astype(np.float64).sum(axis=0)
+    scale = np.abs(a).astype(np.float64).sum(axis=0) @ np.abs(b).astype(np.float64)
+    assert np.max(np.abs(lhs - rhs) / scale) <= TOL
