@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the cleave tensor hot path on B200.
+
+Headline metric: f32 GEMM TFLOP/s at M = N = K = 8192 (algorithmic flops 2*M*N*K, not counting the
+3x of the TF32 split), one problem per GPU per step.  With N GPUs every rank multiplies its own
+8192^3 problem (independent units, no collective: weak scaling), launched as
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+Rank 0 prints ONE JSON line.
+
+  value     whole-job TFLOP/s, operands resident in HBM when the timed region starts
+            (each step = operand split pre-pass + tcgen05 GEMM kernel)
+  e2e       the same metric through the C ABI with HOST buffers: per step both operands are
+            copied from pinned host memory, multiplied, and C is copied back
+  roofline  the tcgen05 kernel alone (CUDA events around each launch on the launching stream)
+            against the 3xTF32-effective tensor peak
+  cpu_baseline  the CPU oracle (restatement of the reference's loop) on a bounded row slice of the
+            same problem, all host threads
+  secondary the other two single-GPU configurations: MLP forward+backward samples/s and the
+            linear-regression step in GB/s (not part of the headline)
+
+`--impl reference` times the reference's CPU arithmetic (the oracle; the reference itself is Rust +
+MLIR and cannot be built here) on the same workload, each step a bounded row slice.
+Inputs are seeded synthetic data (the workload is defined by shapes and distributions).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+FLOPS = 2.0 * M * N * K
+# DRAM traffic of one tcgen05 GEMM kernel launch at 8192^3, from the ncu capture summarised in
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}",
+                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        self.p.wait()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        self.f.close()
+        os.unlink(self.f.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_gemm_sample(a: np.ndarray, b: np.ndarray, target_s: float = 12.0):
+    """Times the oracle GEMM on a row slice of the problem sized for ~target_s of CPU work."""
+    from oracle import ref
+    rows = 32
+    t0 = time.perf_counter()
+    ref.matmul_rows(a, b, 0, rows)
+    dt = time.perf_counter() - t0
+    rows = int(max(32, min(a.shape[0], rows * target_s / max(dt, 1e-3))))
+    rows -= rows % 8
+    t0 = time.perf_counter()
+    ref.matmul_rows(a, b, 0, rows)
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows * b.shape[0] * b.shape[1] / dt / 1e12
+    return tflops, rows, dt, ref.num_threads()
+
+
+def run_reference(args):
+    """Reference arm: the CPU restatement of cleave's matmul loop, all host threads, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from cleave_b200 import workloads
+    from oracle import ref
+    a, b = workloads.gemm_inputs(M, N, K)
+    rows = 64
+    for _ in range(max(args.warmup, 1)):
+        ref.matmul_rows(a, b, 0, rows)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        ref.matmul_rows(a, b, (i * rows) % (M - rows), rows)
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows * N * K * args.steps / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "f32 GEMM TFLOP/s (8192^3)", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "f32 GEMM C=A*B, M=N=K=8192, uniform[-1,1), row-major",
+                   "note": "reference CPU arithmetic (oracle restatement; the Rust+MLIR reference cannot be "
+                           "built here); each step = a 64-row slice of the 8192^3 product"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": ref.num_threads(), "kind": "port",
+                         "sample": f"{rows} of {M} rows per step, {args.steps} steps"},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def secondary_configs(cb, torch, peaks):
+    """MLP forward+backward (configuration 2) and linear-regression step (configuration 1)."""
+    from cleave_b200 import autodiff, linalg, workloads
+    out = {}
+    L = cb.lib()
+    # --- MLP 4096 x (1024 -> 4096 tanh -> 1024 sigmoid), MSE, all grads
+    X, W1, b1, W2, b2, T = workloads.mlp_inputs()
+    net = autodiff.MLP2(1024, 4096, 1024)
+    net.load(W1, b1, W2, b2)
+    tX, tT = linalg.Tensor(X), linalg.Tensor(T)
+    for _ in range(3):
+        net.forward_backward(tX, tT)
+    cb.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = 10
+    e0.record()
+    for _ in range(steps):
+        loss = net.forward_backward(tX, tT)
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    gemm_flops = 5 * 2.0 * 4096 * 4096 * 1024
+    out["mlp_fwd_bwd"] = {"samples_per_s": 4096 / (ms * 1e-3), "ms_per_step": ms, "loss": loss,
+                          "gemm_tflops": gemm_flops / (ms * 1e-3) / 1e12,
+                          "config": "batch 4096, 1024->4096 tanh->1024 sigmoid, MSE, f32"}
+    del net, tX, tT
+    # --- linear regression 1,048,576 x 16
+    X, y, _w = workloads.linreg_inputs()
+    tX, ty, tw = linalg.Tensor(X), linalg.Tensor(y), linalg.Tensor(np.zeros(16, np.float32))
+    for _ in range(3):
+        autodiff.linreg_step(tX, ty, tw)
+    e0.record()
+    for _ in range(steps):
+        loss, _g, _p = autodiff.linreg_step(tX, ty, tw)
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    nbytes = 4.0 * (X.size + 2 * y.size)
+    out["linreg_step"] = {"gb_per_s": nbytes / (ms * 1e-3) / 1e9, "ms_per_step": ms, "loss": loss,
+                          "hbm_frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                          "note": "includes the scalar read-back of the loss each step",
+                          "config": "X 1048576x16 N(0,1), loss + dL/dw in one sweep"}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cleave_b200", choices=["cleave_b200", "reference"])
+    ap.add_argument("--no-secondary", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import cleave_b200 as cb
+    from cleave_b200 import linalg, workloads
+    from cleave_b200._lib import c_f32p
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = cb.lib()
+    if L.cleave_cuda_init(local) != 0:
+        cb._lib.raise_last_error("init")
+    # Run the library on torch's current stream so torch CUDA events bracket its kernels.
+    L.cleave_cuda_set_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    peaks, peaks_kind = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # Operands: seeded per rank (independent problems), generated on the host, resident in HBM.
+    a_host, b_host = workloads.gemm_inputs(M, N, K, seed_a=1 + 2 * rank, seed_b=2 + 2 * rank)
+    ta, tb = linalg.Tensor(a_host), linalg.Tensor(b_host)
+    tc = linalg.Tensor.empty(M, N)
+
+    def step():
+        linalg.gemm_into(tc, ta, tb, algo=linalg.GEMM_3XTF32)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches0 = L.cleave_cuda_kernel_launches()
+    sampler = ClockSampler(local) if rank == 0 else None
+    L.cleave_cuda_profile_begin()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    n_prof = ctypes.c_int32(0)
+    kernel_ms_total = L.cleave_cuda_profile_end(ctypes.byref(n_prof))
+    clocks = sampler.stop() if sampler else None
+    launches = L.cleave_cuda_kernel_launches() - launches0
+    if L.cleave_cuda_sync() != 0:
+        cb._lib.raise_last_error("timed region")
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    value = world * FLOPS / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
+    nbytes = M * K * 4
+    pin = [L.cleave_cuda_host_alloc(nbytes) for _ in range(3)]
+    if not all(pin):
+        cb._lib.raise_last_error("pinned host allocation")
+    ha, hb, hc = (np.ctypeslib.as_array(ctypes.cast(p, c_f32p), shape=(M * K,)) for p in pin)
+    ha[:] = a_host.ravel()
+    hb[:] = b_host.ravel()
+
+    def e2e_step():
+        L.cleave_cuda_upload_into_f32(ta._h, ha.ctypes.data_as(c_f32p), ha.size)
+        L.cleave_cuda_upload_into_f32(tb._h, hb.ctypes.data_as(c_f32p), hb.size)
+        step()
+        if L.cleave_cuda_download_f32(tc._h, hc.ctypes.data_as(c_f32p), hc.size) < 0:
+            cb._lib.raise_last_error("download")
+
+    e2e_steps = max(3, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / e2e_steps
+    e2e_value = world * FLOPS / (e2e_ms * 1e-3) / 1e12
+    checksum = float(hc[:4096].astype(np.float64).sum())
+    for p in pin:
+        L.cleave_cuda_host_free(p)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel (tcgen05 GEMM), this rank
+    kernel_ms = kernel_ms_total / max(n_prof.value, 1)
+    achieved = FLOPS / (kernel_ms * 1e-3) / 1e12
+    # 3xTF32-effective tensor peak: dense TF32 runs at half the bf16 rate, and the split issues
+    # three MMAs per product.  The bf16 figure is the measured sustained cuBLAS number.
+    peak = peaks["bf16_tflops_sustained"] / 2.0 / 3.0
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "kernel": "gemm_3xtf32_kernel", "kernel_ms": kernel_ms, "launches_timed": n_prof.value,
+                "peak_basis": f"{peaks_kind} bf16_tflops_sustained / 2 (tf32) / 3 (split); "
+                              f"burst basis {peaks['bf16_tflops'] / 6.0:.1f}"}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        v, rows, dt, cores = cpu_gemm_sample(a_host, b_host)
+        cpu = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+               "sample": f"rows 0..{rows} of the 8192^3 product ({dt:.1f} s), bit-identical restatement of the "
+                         "reference loop, OpenMP over rows"}
+
+    line = {
+        "metric": "f32 GEMM TFLOP/s (8192^3)", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "f32 GEMM C=A*B, M=N=K=8192, uniform[-1,1), row-major; one problem per GPU per step",
+                   "arithmetic": "3xTF32 split on tcgen05, f32 accumulate, K chunks of 256 summed in f32",
+                   "l2": "operands 256 MiB each, larger than the 126 MB L2", "parallelism": f"replicas x{world}"},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 2 * nbytes,
+                "d2h_bytes_per_step": nbytes, "steps": e2e_steps, "checksum": checksum},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+    }
+    if not args.no_secondary and world == 1:
+        del ta, tb, tc
+        line["secondary"] = secondary_configs(cb, torch, peaks)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

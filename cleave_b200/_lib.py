@@ -30,6 +30,8 @@ SIGNATURES = {
     "cleave_cuda_trim": (None, []),
     "cleave_cuda_live_bytes": (i64, []),
     "cleave_cuda_kernel_launches": (i64, []),
+    "cleave_cuda_profile_begin": (None, []),
+    "cleave_cuda_profile_end": (ctypes.c_double, [ctypes.POINTER(i32)]),
     "cleave_cuda_host_alloc": (ctypes.c_void_p, [i64]),
     "cleave_cuda_host_free": (None, [ctypes.c_void_p]),
     "cleave_cuda_alloc_f32": (c_buf, [i64]),

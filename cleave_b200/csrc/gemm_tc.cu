@@ -17,10 +17,19 @@
 //               {BK, rows, 2 planes} -> shared memory, completion on the stage's "full" mbarrier
 //   warp 1      MMA issuer (one elected lane): 3 x (BK/8) tcgen05.mma per K-block into one of two
 //               128x256 f32 accumulators in TMEM; tcgen05.commit releases the stage ("empty")
-//               and, after the last K-block, publishes the accumulator ("tmem_full")
-//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, optional bias + activation,
-//               128-bit stores to C; then hand the accumulator back ("tmem_empty")
-// The second accumulator lets the epilogue of tile i overlap the main loop of tile i+1.
+//               and, after each K-chunk, publishes the accumulator ("tmem_full")
+//   warps 2-9   drain + epilogue: after every K-chunk (256 values of k) tcgen05.ld the chunk's
+//               partial sums and add them, round-to-nearest, to 128 running sums per thread in
+//               registers; hand the accumulator back ("tmem_empty"); after the last chunk apply
+//               bias + activation and store C with 128-bit stores
+// The two TMEM accumulators alternate per chunk, so draining chunk i overlaps the MMAs of
+// chunk i+1 (and the stores of one tile overlap the first chunk of the next).
+//
+// Why chunks.  The tensor pipe adds into its f32 accumulator with truncation, not round to
+// nearest (measured: at K = 8192 a single accumulation chain ends ~1e-3 too close to zero, a bias
+// linear in K and 14x the error of the reference's f32 loop).  Restarting the chain every 256 k
+// and summing the chunks in registers with round-to-nearest keeps each chain short and its
+// partial sums small, which brings the error below that of the reference loop itself.
 // Tiles are visited in groups of 16 tile-rows so that the ~148 tiles in flight share operand
 // panels through L2.
 //
@@ -30,6 +39,8 @@
 #include <cuda.h>
 
 #include <cstdio>
+#include <utility>
+#include <vector>
 
 #include "common.cuh"
 #include "gemm.cuh"
@@ -39,7 +50,9 @@ namespace cleave {
 constexpr int BM = 128;          // tile rows  (UMMA M)
 constexpr int BN = 256;          // tile cols  (UMMA N)
 constexpr int UMMA_K = 8;        // tf32 MMA K (32 bytes)
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;     // two per TMEM lane quarter, 128 columns each
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
+constexpr int kChunkK = 256;     // k values accumulated in TMEM before a drain into registers
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = kAccStages * BN;   // 512: all of TMEM
 constexpr int kGroupM = 16;      // tile-rows per rasterisation group
@@ -175,6 +188,7 @@ struct TcParams {
   const float* bias;    // [n] or null
   int m, n;
   int num_kb;           // K_padded / BK
+  int chunk_kb;         // K-blocks per accumulation chunk (kChunkK / BK)
   int batch, mblks, nblks;
   int act;
   DeviceStatus* status;
@@ -231,7 +245,7 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     for (int a = 0; a < kAccStages; ++a) {
       mbar_init(smem_u32(&bar_tmem_full[a]), 1);
-      mbar_init(smem_u32(&bar_tmem_empty[a]), 4);   // one arrival per epilogue warp
+      mbar_init(smem_u32(&bar_tmem_empty[a]), kEpiWarps);   // one arrival per drain warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -299,97 +313,106 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
-          report(p.status, 2, 200 + acc, t);
-          break;
-        }
-        tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
-            report(p.status, 3, 300 + stage, kb);
+        for (int kb0 = 0; ok && kb0 < p.num_kb; kb0 += p.chunk_kb) {
+          if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
+            report(p.status, 2, 200 + acc, t);
             ok = false;
             break;
           }
           tcgen05_fence_after();
-          const uint32_t a_hi = ring + stage * C::kStageBytes;
-          const uint32_t a_lo = a_hi + C::kABytes;
-          const uint32_t b_hi = a_hi + 2 * C::kABytes;
-          const uint32_t b_lo = b_hi + C::kBBytes;
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+          const int kb_end = (kb0 + p.chunk_kb) < p.num_kb ? (kb0 + p.chunk_kb) : p.num_kb;
+          for (int kb = kb0; kb < kb_end; ++kb) {
+            if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
+              report(p.status, 3, 300 + stage, kb);
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+            const uint32_t a_hi = ring + stage * C::kStageBytes;
+            const uint32_t a_lo = a_hi + C::kABytes;
+            const uint32_t b_hi = a_hi + 2 * C::kABytes;
+            const uint32_t b_lo = b_hi + C::kBBytes;
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            const uint32_t off = kk * UMMA_K * 4;   // 32 bytes along K inside the swizzled row
-            const uint64_t da_hi = make_smem_desc(a_hi + off, C::kSBO, C::kLayoutType);
-            const uint64_t da_lo = make_smem_desc(a_lo + off, C::kSBO, C::kLayoutType);
-            const uint64_t db_hi = make_smem_desc(b_hi + off, C::kSBO, C::kLayoutType);
-            const uint64_t db_lo = make_smem_desc(b_lo + off, C::kSBO, C::kLayoutType);
-            // small terms first, then the leading product
-            umma_tf32(d_tmem, da_lo, db_hi, kInstrDesc, (kb | kk) != 0 ? 1u : 0u);
-            umma_tf32(d_tmem, da_hi, db_lo, kInstrDesc, 1u);
-            umma_tf32(d_tmem, da_hi, db_hi, kInstrDesc, 1u);
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              const uint32_t off = kk * UMMA_K * 4;   // 32 bytes along K inside the swizzled row
+              const uint64_t da_hi = make_smem_desc(a_hi + off, C::kSBO, C::kLayoutType);
+              const uint64_t da_lo = make_smem_desc(a_lo + off, C::kSBO, C::kLayoutType);
+              const uint64_t db_hi = make_smem_desc(b_hi + off, C::kSBO, C::kLayoutType);
+              const uint64_t db_lo = make_smem_desc(b_lo + off, C::kSBO, C::kLayoutType);
+              // the first MMA of a chunk overwrites the accumulator; small terms go first
+              umma_tf32(d_tmem, da_lo, db_hi, kInstrDesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+              umma_tf32(d_tmem, da_hi, db_lo, kInstrDesc, 1u);
+              umma_tf32(d_tmem, da_hi, db_hi, kInstrDesc, 1u);
+            }
+            tcgen05_commit(smem_u32(&bar_empty[stage]));   // stage reusable once these MMAs retire
+            if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
           }
-          tcgen05_commit(smem_u32(&bar_empty[stage]));   // stage reusable once these MMAs retire
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+          if (!ok) break;
+          tcgen05_commit(smem_u32(&bar_tmem_full[acc]));   // chunk complete
+          if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
         }
-        if (!ok) break;
-        tcgen05_commit(smem_u32(&bar_tmem_full[acc]));   // accumulator complete
-        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int q = warp & 3;   // TMEM lane quarter this warp may read: lanes 32q .. 32q+31
+    // ------------------------------------------------------------------ drain + epilogue (warps 2..9)
+    const int q = warp & 3;             // TMEM lane quarter this warp may read: lanes 32q .. 32q+31
+    const int half = (warp - 2) >> 2;   // which 128 of the tile's 256 columns
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = (p.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0);
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
       int b, mb, nb;
       decode_tile(t, p, b, mb, nb);
-      bool ok = mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        if (lane == 0) report(p.status, 4, 400 + acc, t);
-        break;
+      float sum[BN / 2];
+#pragma unroll
+      for (int j = 0; j < BN / 2; ++j) sum[j] = 0.0f;
+      for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.chunk_kb) {
+        ok = mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, 4, 400 + acc, t);
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * (BN / 2));
+#pragma unroll
+        for (int cb = 0; cb < BN / 64; ++cb) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + cb * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[cb * 32 + j] = __fadd_rn(sum[cb * 32 + j], __uint_as_float(r[j]));
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
       }
-      tcgen05_fence_after();
+      if (!ok) break;
       const int row = mb * BM + q * 32 + lane;
-      const int col0 = nb * BN;
-      float* crow = p.c + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-      for (int cb = 0; cb < BN / 32; ++cb) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + cb * 32, r);
-        tmem_ld_wait();
-        const int cbase = col0 + cb * 32;
-        if (row < p.m && cbase < p.n) {
-          float v[32];
+      const int col0 = nb * BN + half * (BN / 2);
+      if (row < p.m) {
+        float* crow = p.c + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
+        if (p.bias != nullptr || p.act != CLEAVE_ACT_IDENTITY) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (p.bias != nullptr || p.act != CLEAVE_ACT_IDENTITY) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int cj = cbase + j;
-              float x = v[j];
-              if (p.bias != nullptr && cj < p.n) x = __fadd_rn(x, __ldg(p.bias + cj));
-              v[j] = act_apply(x, p.act);
-            }
-          }
-          if (vec_ok && cbase + 32 <= p.n) {
-            float4* dst = reinterpret_cast<float4*>(crow + cb * 32);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cbase + j < p.n) crow[cb * 32 + j] = v[j];
+          for (int j = 0; j < BN / 2; ++j) {
+            float x = sum[j];
+            if (p.bias != nullptr && col0 + j < p.n) x = __fadd_rn(x, __ldg(p.bias + col0 + j));
+            sum[j] = act_apply(x, p.act);
           }
         }
+        if (vec_ok && col0 + BN / 2 <= p.n) {
+          float4* dst = reinterpret_cast<float4*>(crow);
+#pragma unroll
+          for (int j = 0; j < BN / 8; ++j) dst[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN / 2; ++j)
+            if (col0 + j < p.n) crow[j] = sum[j];
+        }
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
-      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
     }
   }
 
@@ -550,6 +573,48 @@ static bool split_operand(const float* src, float* dst, int batch, int rows, int
   return cuda_ok(cudaGetLastError(), "operand split launch");
 }
 
+// Optional timing of the tensor-core kernel alone (pre-pass excluded): an event pair around each
+// launch on the launching stream, summed by cleave_cuda_profile_end().
+static bool g_profiling = false;
+static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_prof_events;
+static size_t g_prof_used = 0;
+
+static void prof_mark(bool begin) {
+  if (!g_profiling) return;
+  if (begin) {
+    if (g_prof_used == g_prof_events.size()) {
+      cudaEvent_t a, b;
+      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) { cudaGetLastError(); return; }
+      g_prof_events.emplace_back(a, b);
+    }
+    cudaEventRecord(g_prof_events[g_prof_used].first, ctx().stream);
+  } else if (g_prof_used < g_prof_events.size()) {
+    cudaEventRecord(g_prof_events[g_prof_used].second, ctx().stream);
+    ++g_prof_used;
+  }
+}
+
+void gemm_profile_begin() {
+  g_profiling = true;
+  g_prof_used = 0;
+}
+
+double gemm_profile_end(int* launches) {
+  double total = 0.0;
+  g_profiling = false;
+  for (size_t i = 0; i < g_prof_used; ++i) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(g_prof_events[i].second) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, g_prof_events[i].first, g_prof_events[i].second) == cudaSuccess)
+      total += ms;
+    else
+      cudaGetLastError();
+  }
+  if (launches) *launches = (int)g_prof_used;
+  g_prof_used = 0;
+  return total;
+}
+
 template <int BK>
 static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
   using C = Cfg<BK>;
@@ -563,7 +628,9 @@ static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams&
   }
   const int tiles = p.batch * p.mblks * p.nblks;
   const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
+  prof_mark(true);
   gemm_3xtf32_kernel<BK><<<grid, kGemmThreads, C::kSmemBytes, ctx().stream>>>(ma, mb, p);
+  prof_mark(false);
   count_launch();
   return cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch");
 }
@@ -607,6 +674,7 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.m = g.m;
     p.n = g.n;
     p.num_kb = Kp / bk;
+    p.chunk_kb = kChunkK / bk;
     p.batch = nb;
     p.mblks = Mp / BM;
     p.nblks = Np / BN;

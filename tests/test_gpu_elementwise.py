@@ -40,7 +40,8 @@ def test_ring_ops_on_rank_2_and_3_and_special_values():
                           ((linalg.Tensor(a) * linalg.Tensor(b)).numpy(), ref.mul(a, b)),
                           ((linalg.Tensor(a) / linalg.Tensor(b)).numpy(), ref.div(a, b))):
             assert np.array_equal(got, want, equal_nan=True)
-            assert np.array_equal(np.signbit(got), np.signbit(want))
+            ok = ~np.isnan(want)   # the sign of a generated NaN is not specified by IEEE 754
+            assert np.array_equal(np.signbit(got[ok]), np.signbit(want[ok]))
     t3 = linalg.Tensor(np.arange(8, dtype=f32).reshape(2, 2, 2) + 1)
     assert t3[0, 1, 0] == 3.0 and t3[1, 1, 1] == 8.0
 

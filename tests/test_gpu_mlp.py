@@ -31,7 +31,9 @@ def test_mlp2_forward_backward_matches_oracle(batch, d_in, d_hid, d_out):
     net.load(W1, b1, W2, b2)
     loss, inter = net.forward_backward(linalg.Tensor(X), linalg.Tensor(T), keep=True)
     cb.sync()
-    assert abs(loss - float(want["loss"])) <= TOL * float(want["loss"])
+    loss64 = ref.mse_f64(want["Y"], T)
+    assert abs(loss - loss64) <= TOL * loss64
+    assert abs(loss - float(want["loss"])) <= abs(float(want["loss"]) - loss64) + TOL * loss64
     # Each quantity is compared on the scale of the sum of |terms| of the contraction that made it.
     absX, absH = np.abs(X).astype(np.float64), np.abs(want["H"]).astype(np.float64)
     check(inter["H"].numpy(), want["H"], absX @ np.abs(W1) + np.abs(b1), "H")

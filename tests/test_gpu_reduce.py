@@ -60,8 +60,11 @@ def test_mse_loss_and_gradient(n):
     loss, dp = nn.mse(linalg.Tensor(p), linalg.Tensor(t))
     want_loss, want_dp = ref.mse(p, t)
     assert np.array_equal(dp.numpy(), want_dp)                 # elementwise: bit-exact
-    assert abs(loss - float(want_loss)) <= TOL * float(want_loss)
-    assert abs(loss - ref.mse_f64(p, t)) <= TOL * ref.mse_f64(p, t)
+    loss64 = ref.mse_f64(p, t)
+    assert abs(loss - loss64) <= TOL * loss64
+    # The reference's left-to-right float32 chain drifts from the exact sum as n grows (4e-3
+    # relative at n = 4M); the device tree may differ from it by that drift, not by more.
+    assert abs(loss - float(want_loss)) <= abs(float(want_loss) - loss64) + TOL * loss64
 
 
 @pytest.mark.parametrize("rows,feat", [(1, 1), (1000, 16), (5000, 7), (4096, 32), (100003, 16), (1 << 20, 16)])
@@ -75,7 +78,7 @@ def test_linreg_step(rows, feat):
         assert np.array_equal(pred.numpy(), want_pred)          # f ascending, mul then add: bit-exact
         loss64, grad64 = ref.linreg_step_f64(X, y, w)
         assert abs(loss - loss64) <= TOL * loss64
-        assert abs(loss - float(want_loss)) <= TOL * float(want_loss)
+        assert abs(loss - float(want_loss)) <= abs(float(want_loss) - loss64) + TOL * loss64
         # gradient terms X[i,f] * 2e_i/N: error scales with the sum of |terms|
         e = np.abs(want_pred.astype(np.float64) - y) * 2 / rows
         scale = np.abs(X).astype(np.float64).T @ e
