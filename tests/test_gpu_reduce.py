@@ -84,5 +84,8 @@ def test_linreg_step(rows, feat):
         scale = np.abs(X).astype(np.float64).T @ e
         scale = np.maximum(scale, 1e-30)
         g = grad.numpy().astype(np.float64)
-        assert np.max(np.abs(g - want_grad) / scale) <= TOL
         assert np.max(np.abs(g - grad64) / scale) <= TOL
+        # against the reference's float32 chain: allowed to differ by that chain's own drift
+        # from the exact sum (3e-5 of the scale at a million rows), not by more
+        drift = np.abs(want_grad - grad64) / scale
+        assert np.all(np.abs(g - want_grad) / scale <= drift + TOL)
