@@ -60,6 +60,7 @@ SIGNATURES = {
     "cleave_cuda_sum_f32": (f32, [c_buf]),
     "cleave_cuda_mean_f32": (f32, [c_buf]),
     "cleave_cuda_max_f32": (f32, [c_buf]),
+    "cleave_cuda_sum_noalloc_f32": (i32, [ctypes.c_void_p, i64, ctypes.c_void_p, ctypes.c_void_p]),
     "cleave_cuda_colsum_f32": (c_buf, [c_buf, i32, i32]),
     "cleave_cuda_colsum_into_f32": (i32, [c_buf, c_buf, i32, i32]),
     "cleave_cuda_gemm_f32": (c_buf, [c_buf, c_buf, i32, i32, i32]),

@@ -492,3 +492,73 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free sum.
+//
+// Some callers may not allocate device memory at the moment they need a reduction: code that runs
+// while another framework owns the device heap and forbids side allocations, latency-critical loops
+// where a cudaMalloc (which can synchronise the whole device) is unacceptable, or processes that
+// are already at their memory budget.  cleave_cuda_sum_f32 takes its partial-sum buffer from the
+// library's pool, which may call cudaMalloc; the variant below keeps that buffer in a fixed
+// device-resident array instead and touches neither the pool, the handle table nor the library
+// context.  The cost is that every GPU that loads the library carries the array until exit.
+// ------------------------------------------------------------------------------------------------
+namespace cleave {
+
+constexpr int kNoAllocScratchFloats = kMaxPartials + 4;     // 1188 floats, 4752 bytes
+constexpr int64_t kNoAllocMaxLen = 2147483647ll;             // largest tensor an i32 shape can describe
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+// Device address of the array above, per device.  The symbol name is only a host-side stand-in;
+// the address a kernel can use has to be asked for, once per device, with that device current.
+static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+
+static float* noalloc_scratch_for_current_device() {
+  int dev = -1;
+  if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return nullptr;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) {
+    set_error(CLEAVE_CUDA_ERR_UNSUPPORTED, "sum_noalloc: device ordinal %d is outside the supported range [0, %d)", dev,
+              kNoAllocMaxDevices);
+    return nullptr;
+  }
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    if (!cuda_ok(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)")) return nullptr;
+    g_noalloc_ptr[dev] = p;
+  }
+  return g_noalloc_ptr[dev];
+}
+
+}  // namespace cleave
+
+extern "C" int32_t cleave_cuda_sum_noalloc_f32(const float* x_dev, int64_t len, float* out_dev, void* cuda_stream) {
+  ApiLock lock;
+  if (!x_dev || !out_dev)
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "sum_noalloc: input and output must be non-NULL device pointers");
+  if (len <= 0)
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "sum_noalloc: length must be positive, got %lld", (long long)len);
+  if (len > kNoAllocMaxLen)
+    return -set_error(CLEAVE_CUDA_ERR_UNSUPPORTED,
+                      "sum_noalloc: %lld elements exceed the maximum of %lld this entry point accepts",
+                      (long long)len, (long long)kNoAllocMaxLen);
+  if ((reinterpret_cast<uintptr_t>(x_dev) & 3u) || (reinterpret_cast<uintptr_t>(out_dev) & 3u))
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "sum_noalloc: pointers must be 4-byte aligned");
+  float* scratch = noalloc_scratch_for_current_device();
+  if (!scratch) return -cleave_cuda_last_error();
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  // Same slab rule and the same two kernels as cleave_cuda_sum_f32, so the summation tree and
+  // therefore the result are identical.  Stage 1 writes partials [0, ctas) and stage 2 reads
+  // exactly those, so nothing left in the array by an earlier call is ever read and nothing has
+  // to be cleared first.
+  int64_t slab;
+  int ctas;
+  slab_for(len, &slab, &ctas);
+  reduce_stage1<SumRed><<<ctas, kRThreads, 0, s>>>(x_dev, len, slab, scratch, aligned16(x_dev) ? 1 : 0);
+  reduce_stage2<SumRed><<<1, kRThreads, 0, s>>>(scratch, ctas, out_dev, 1.0f, 0, nullptr);
+  count_launch(2);
+  if (!cuda_ok(cudaGetLastError(), "sum_noalloc launch")) return -cleave_cuda_last_error();
+  return CLEAVE_CUDA_OK;
+}

@@ -131,6 +131,20 @@ cleave_buf cleave_cuda_relu_bwd_f32(cleave_buf x, cleave_buf g);     /* x > 0 ? 
 float cleave_cuda_sum_f32(cleave_buf v);
 float cleave_cuda_mean_f32(cleave_buf v);
 float cleave_cuda_max_f32(cleave_buf v);
+/* Sum without any allocation.  No counterpart in the reference (its runtime only ever
+ * allocates, cleave-rt/src/lib.rs:56-71); added for callers that cannot allocate device memory
+ * when they need the reduction: hosts where another framework owns the device heap, loops
+ * where a cudaMalloc stall is not acceptable, processes already at their memory budget.
+ * x_dev (len f32 values) and out_dev (one f32) are raw device pointers owned by the caller; the
+ * two kernels are queued on cuda_stream (NULL = the default stream) of the CURRENT device and the
+ * call returns without waiting.  The partial sums live in a 4752-byte array that is part of the
+ * library image on every GPU; len may be at most 2^31 - 1 (larger is rejected with
+ * CLEAVE_CUDA_ERR_UNSUPPORTED).  The first call on each device looks up the array's device
+ * address, so make that first call outside any stream capture.  All calls on one device share
+ * the array: calls whose kernels may overlap on the GPU (different streams) race on it; calls
+ * on one stream do not.  The value equals cleave_cuda_sum_f32 of the same data bit for bit.
+ * It uses no handle, no pool and no library context, and never calls cudaMalloc or cudaFree. */
+int32_t cleave_cuda_sum_noalloc_f32(const float* x_dev, int64_t len, float* out_dev, void* cuda_stream);
 /* Sum applied to each column of a rows x cols matrix (bias gradients). */
 cleave_buf cleave_cuda_colsum_f32(cleave_buf x, int32_t rows, int32_t cols);
 int32_t cleave_cuda_colsum_into_f32(cleave_buf out, cleave_buf x, int32_t rows, int32_t cols);
