@@ -190,6 +190,76 @@ def secondary_configs(cb, torch, peaks):
     return out
 
 
+def run_dp_mlp(args):
+    """Configuration 4b: the 2-layer MLP trained data-parallel, global batch 32768 split evenly over
+    the ranks, SGD lr 1e-3, gradients all-reduced (mean) with NCCL each step.  Strong scaling."""
+    import torch
+    import torch.distributed as dist
+
+    import cleave_b200 as cb
+    from cleave_b200 import autodiff, dp, linalg, workloads
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = cb.lib()
+    if L.cleave_cuda_init(local) != 0:
+        cb._lib.raise_last_error("init")
+    dp.use_torch_stream()
+    global_batch, d_in, d_hid, d_out = args.global_batch, 1024, 4096, 1024
+    _, W1, b1, W2, b2, _ = workloads.mlp_inputs(1, d_in, d_hid, d_out)
+    net = autodiff.MLP2(d_in, d_hid, d_out)
+    net.load(W1, b1, W2, b2)
+    trainer = dp.DataParallel(dp.MLP2Replica(net), overlap=not args.no_overlap)
+    X, T = dp.dp_batch_inputs(global_batch, rank, world, d_in, d_out)
+    tX, tT = linalg.Tensor(X), linalg.Tensor(T)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        trainer.step(tX, tT, 1e-3)
+    barrier()
+    launches0 = L.cleave_cuda_kernel_launches()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = trainer.step(tX, tT, 1e-3)
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    launches = L.cleave_cuda_kernel_launches() - launches0
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    psum = torch.tensor([float(dp.as_torch(net.params).double().sum())], device="cuda", dtype=torch.float64)
+    pmin, pmax = psum.clone(), psum.clone()
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(pmin, op=dist.ReduceOp.MIN)
+        dist.all_reduce(pmax, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    if rank == 0:
+        nparams = net.n_params
+        print(json.dumps({
+            "metric": "MLP data-parallel training samples/s", "value": global_batch / (ms * 1e-3), "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"2-layer MLP 1024->4096 tanh->1024 sigmoid, MSE, SGD lr 1e-3, global batch "
+                                   f"{global_batch} split over {world} rank(s), gradient all-reduce (mean) every step",
+                       "allreduce_bytes_per_step": 4 * nparams, "overlap": not args.no_overlap},
+            "gpu_launches": int(launches), "clocks": clocks, "loss": loss,
+            "replicas_identical": bool(pmin.item() == pmax.item()),
+            "gemm_tflops_per_gpu": 5 * 2.0 * (global_batch / world) * d_hid * d_in / (ms * 1e-3) / 1e12,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -199,6 +269,10 @@ def main():
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "dp_mlp"],
+                    help="gemm = the headline; dp_mlp = data-parallel MLP training (secondary, strong scaling)")
+    ap.add_argument("--global-batch", type=int, default=32768)
+    ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--size", type=int, default=8192,
                     help="M=N=K; anything but 8192 is a profiling case, not the headline workload")
     args = ap.parse_args()
@@ -209,6 +283,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "dp_mlp":
+        run_dp_mlp(args)
         return
 
     import torch

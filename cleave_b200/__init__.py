@@ -8,11 +8,11 @@ a hand-written sm_100a (B200) implementation behind a C ABI.
 There is no CPU fallback: the shared library must be built (``python -m cleave_b200.build``)
 and a CUDA device must be present for any compute call to succeed.
 """
-from . import _lib, autodiff, linalg, nn, workloads  # noqa: F401
+from . import _lib, autodiff, dp, linalg, nn, workloads  # noqa: F401
 from ._lib import CleaveCudaError, lib  # noqa: F401
 from .linalg import Tensor, matmul  # noqa: F401
 
-__all__ = ["linalg", "nn", "autodiff", "workloads", "Tensor", "matmul", "CleaveCudaError", "lib"]
+__all__ = ["linalg", "nn", "autodiff", "dp", "workloads", "Tensor", "matmul", "CleaveCudaError", "lib"]
 
 
 def sync() -> None:

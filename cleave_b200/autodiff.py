@@ -71,18 +71,23 @@ class MLP2:
         Y = gemm_into(Tensor.empty(batch, self.d_out), H, self.W2, bias=self.b2, act=self.act2)
         return H, Y
 
-    def forward_backward(self, X: Tensor, T: Tensor, keep: bool = False):
+    def forward_backward(self, X: Tensor, T: Tensor, keep: bool = False, on_grads_ready=None):
         """One forward + backward pass; gradients land in ``self.grads``.  Returns the loss
-        (and, with ``keep``, the intermediates for inspection)."""
+        (and, with ``keep``, the intermediates for inspection).  ``on_grads_ready(i)`` is called
+        when a gradient bucket is final: 0 = [dW2 | db2], 1 = [dW1 | db1]."""
         H, Y = self.forward(X)
         loss, dY = nn.mse(Y, T)
         dZ2 = _ACT_BWD[self.act2](Y, dY)
         gemm_into(self.dW2, H, dZ2, trans_a=True)            # H^T dZ2
         self._colsum_into(self.db2, dZ2)
+        if on_grads_ready:
+            on_grads_ready(0)
         dH = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True)   # dZ2 W2^T
         dZ1 = _ACT_BWD[self.act1](H, dH)
         gemm_into(self.dW1, X, dZ1, trans_a=True)            # X^T dZ1
         self._colsum_into(self.db1, dZ1)
+        if on_grads_ready:
+            on_grads_ready(1)
         if keep:
             return loss, dict(H=H, Y=Y, dZ2=dZ2, dH=dH, dZ1=dZ1)
         return loss

@@ -1,0 +1,148 @@
+"""Sharding of the tensor path across the GPUs of one box: one process per GPU.
+
+The reference has no distribution at all ("named as a goal but not designed", doc/hld.md:250);
+what shards here is what the benchmark configurations partition naturally:
+
+* batched GEMM by batch index and large GEMM by row blocks of A / C -- independent units, no
+  collective in the data path (``batch_shard``, ``row_block``, ``row_block_matmul``);
+* data-parallel training of the two-layer perceptron -- the one real exchange step: after the local
+  backward pass the contiguous gradient buffer is summed over ranks with one NCCL all-reduce
+  (``torch.distributed``, over NVLink / NVSwitch) and the 1/G of the mean is folded into the SGD pass.
+
+``torch`` is used for process-group plumbing and as a zero-copy view of the library's device
+memory; all arithmetic stays in libcleave_cuda kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+
+def shard(n: int, rank: int, world: int) -> tuple[int, int]:
+    """Half-open range of the ``n`` units owned by ``rank``: contiguous, sizes differ by at most one."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def batch_shard(batch: int, rank: int, world: int) -> range:
+    """Batch indices of a batched GEMM owned by ``rank`` (b -> rank b mod G, so work stays even
+    when the batch is not a multiple of the world size)."""
+    return range(rank, batch, world)
+
+
+def row_block(m: int, rank: int, world: int, tile: int = 128) -> tuple[int, int]:
+    """Rows of A and C owned by ``rank`` for a row-block sharded GEMM; block edges fall on
+    multiples of the GEMM tile height so no tile straddles two ranks."""
+    tiles = (m + tile - 1) // tile
+    lo, hi = shard(tiles, rank, world)
+    return min(lo * tile, m), min(hi * tile, m)
+
+
+class _CudaArrayView:
+    """Exposes a libcleave_cuda buffer through ``__cuda_array_interface__`` (no copy)."""
+
+    def __init__(self, ptr: int, shape: tuple[int, ...]):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def as_torch(t, offset: int = 0, numel: int | None = None):
+    """Zero-copy torch view of (a slice of) a device ``Tensor``; the Tensor must outlive the view."""
+    import torch
+    n = t.numel - offset if numel is None else numel
+    view = torch.as_tensor(_CudaArrayView(t.data_ptr + 4 * offset, (n,)), device="cuda")
+    view._cleave_owner = t
+    return view
+
+
+def use_torch_stream():
+    """Creates a torch stream, makes it current and points the library at it, so library kernels,
+    NCCL collectives and torch CUDA events are all ordered on one stream.  Returns the stream."""
+    import torch
+
+    from ._lib import lib
+    s = torch.cuda.Stream()
+    torch.cuda.set_stream(s)
+    lib().cleave_cuda_set_stream(ctypes.c_void_p(s.cuda_stream))
+    return s
+
+
+class DataParallel:
+    """Synchronous data-parallel SGD over a replica that keeps its gradients in one flat buffer.
+
+    ``replica`` provides ``forward_backward(X, T, on_grads_ready=...) -> loss``, ``grad_buckets()``
+    (list of flat torch views over its gradient buffer, in the order the backward pass completes
+    them) and ``sgd(lr, gscale)``.  Every rank sees a different shard of the global batch; after
+    ``step`` all replicas hold identical parameters.
+    """
+
+    def __init__(self, replica, group=None, overlap: bool = True):
+        import torch.distributed as dist
+        self.replica, self.group, self.overlap = replica, group, overlap
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self._dist = dist
+        self._buckets = replica.grad_buckets()
+
+    def step(self, X, T, lr: float):
+        dist, pending = self._dist, []
+
+        def on_ready(i: int) -> None:
+            # bucket i is final: start summing it while the rest of the backward pass runs
+            if self.world > 1 and self.overlap:
+                pending.append(dist.all_reduce(self._buckets[i], op=dist.ReduceOp.SUM, group=self.group,
+                                               async_op=True))
+
+        loss = self.replica.forward_backward(X, T, on_grads_ready=on_ready)
+        if self.world > 1 and not self.overlap:
+            for b in self._buckets:
+                dist.all_reduce(b, op=dist.ReduceOp.SUM, group=self.group)
+        for w in pending:
+            w.wait()     # orders the current stream after the collective; does not block the host
+        # mean of the per-rank gradients: the 1/G is applied inside the SGD kernel
+        self.replica.sgd(lr, 1.0 / self.world)
+        return loss
+
+
+class MLP2Replica:
+    """Adapter of ``autodiff.MLP2`` to the ``DataParallel`` interface."""
+
+    def __init__(self, net):
+        self.net = net
+        o = [int(x) for x in net._offsets]
+        # backward completes [W2 | b2] first, then [W1 | b1]
+        self._buckets = [as_torch(net.grads, o[2], o[4] - o[2]), as_torch(net.grads, o[0], o[2] - o[0])]
+
+    def grad_buckets(self):
+        return self._buckets
+
+    def forward_backward(self, X, T, on_grads_ready=None):
+        return self.net.forward_backward(X, T, on_grads_ready=on_grads_ready)
+
+    def sgd(self, lr, gscale):
+        self.net.sgd(lr, gscale)
+
+
+def row_block_matmul(a_rows, b_full, group=None, src: int = 0):
+    """C rows of this rank for a row-block sharded GEMM.  ``a_rows`` is this rank's [rows, k] block
+    of A; ``b_full`` is a [k, n] device Tensor whose contents are valid on rank ``src`` and are
+    replicated into every rank's own HBM first (an NCCL broadcast), so the GEMM only ever reads
+    local memory."""
+    import torch.distributed as dist
+
+    from .linalg import matmul
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.broadcast(as_torch(b_full), src=src, group=group)
+    return matmul(a_rows, b_full)
+
+
+def dp_batch_inputs(global_batch: int, rank: int, world: int, d_in: int, d_out: int, step: int = 0):
+    """This rank's shard of a seeded global batch: every rank draws from the same generator
+    stream and keeps its own contiguous rows, so the union over ranks is independent of G."""
+    from . import workloads
+    lo, hi = shard(global_batch, rank, world)
+    X = workloads.normal(1000 + step, global_batch, d_in)[lo:hi]
+    T = workloads.uniform01(2000 + step, global_batch, d_out)[lo:hi]
+    return np.ascontiguousarray(X), np.ascontiguousarray(T)
