@@ -42,9 +42,9 @@ if ROOT not in sys.path:
 
 M = N = K = 8192          # headline size; --size overrides it for profiling captures only
 FLOPS = 2.0 * M * N * K
-# DRAM traffic of one tcgen05 GEMM kernel launch at 8192^3, from the ncu capture summarised in
-# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM traffic of one tcgen05 GEMM kernel launch at 8192^3, from a one-pass ncu capture of this
+# program at full size (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 5.94e9 + 264.19e6
 
 
 def measured_peaks():
@@ -102,6 +102,7 @@ class ClockSampler:
 def cpu_gemm_sample(a: np.ndarray, b: np.ndarray, target_s: float = 12.0):
     """Times the oracle GEMM on a row slice of the problem sized for ~target_s of CPU work."""
     from oracle import ref
+    ref.set_num_threads(_host_threads())   # torchrun exports OMP_NUM_THREADS=1; use every core we may
     rows = 32
     t0 = time.perf_counter()
     ref.matmul_rows(a, b, 0, rows)
@@ -122,6 +123,7 @@ def run_reference(args):
         return
     from cleave_b200 import workloads
     from oracle import ref
+    ref.set_num_threads(_host_threads())
     a, b = workloads.gemm_inputs(M, N, K)
     rows = 64
     for _ in range(max(args.warmup, 1)):
@@ -188,6 +190,185 @@ def secondary_configs(cb, torch, peaks):
                           "note": "includes the scalar read-back of the loss each step",
                           "config": "X 1048576x16 N(0,1), loss + dL/dw in one sweep"}
     return out
+
+
+def _host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def _setup_single(local: int = 0):
+    import torch
+
+    import cleave_b200 as cb
+    from cleave_b200 import dp
+    torch.cuda.set_device(local)
+    L = cb.lib()
+    if L.cleave_cuda_init(local) != 0:
+        cb._lib.raise_last_error("init")
+    dp.use_torch_stream()
+    return torch, cb, L
+
+
+def _time_ms(torch, fn, iters: int, warmup: int = 3) -> float:
+    """Average device time of fn() over `iters` back-to-back calls (CUDA events on the library's stream)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_ops(args):
+    """Streaming operators and reductions at configuration-2 sizes: achieved GB/s (algorithmic bytes)
+    against the measured HBM copy bandwidth.  Each operator runs over four distinct operand sets in
+    rotation (64 MiB per tensor, 768 MiB touched per rotation, so nothing is served from the 126 MB
+    L2) inside ONE event pair, 5 rotations per measurement."""
+    torch, cb, L = _setup_single()
+    from cleave_b200 import linalg, nn, workloads
+    peaks, kind = measured_peaks()
+    rows, cols = args.ops_rows, 4096
+    n = rows * cols
+    R = 4
+    A = [linalg.Tensor(workloads.normal(11 + i, rows, cols)) for i in range(R)]
+    B = [linalg.Tensor(workloads.normal(21 + i, rows, cols) + np.float32(3.0)) for i in range(R)]
+    Y = [nn.tanh(a) for a in A]
+    W = [linalg.Tensor(workloads.normal(31 + i, n)) for i in range(R)]
+    bias = linalg.Tensor(workloads.normal(13, cols))
+    cases = {
+        "add": (lambda i: A[i] + B[i], 12 * n), "mul": (lambda i: A[i] * B[i], 12 * n),
+        "div": (lambda i: A[i] / B[i], 12 * n), "neg": (lambda i: -A[i], 8 * n),
+        "relu": (lambda i: nn.relu(A[i]), 8 * n), "sigmoid": (lambda i: nn.sigmoid(A[i]), 8 * n),
+        "tanh": (lambda i: nn.tanh(A[i]), 8 * n), "exp": (lambda i: nn.exp(Y[i]), 8 * n),
+        "tanh_bwd": (lambda i: nn.tanh_bwd(Y[i], B[i]), 12 * n),
+        "sigmoid_bwd": (lambda i: nn.sigmoid_bwd(Y[i], B[i]), 12 * n),
+        "bias_tanh": (lambda i: nn.bias_act(A[i], bias, "tanh"), 8 * n),
+        "sgd": (lambda i: nn.sgd_step(W[i], B[i].reshape(n), 1e-9), 12 * n),
+        "fill": (lambda i: linalg.Tensor.zero(n), 4 * n),
+        "colsum": (lambda i: nn.colsum(A[i]), 4 * n),
+        # scalar-returning: every call ends with a device->host read of the result and a stream sync
+        "sum": (lambda i: nn.sum(A[i]), 4 * n), "max_of": (lambda i: nn.max_of(A[i]), 4 * n),
+        "mse_fwd_bwd": (lambda i: nn.mse(Y[i], B[i]), 12 * n),
+    }
+    out = {}
+    for name, (fn, nbytes) in cases.items():
+        def rotation():
+            for i in range(R):
+                fn(i)
+        ms = _time_ms(torch, rotation, 5, warmup=2) / R
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 4), "gb_per_s": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 3)}
+    print(json.dumps({"metric": "streaming operator GB/s", "unit": "GB/s", "n_gpus": 1, "dtype": "f32",
+                      "data": "synthetic",
+                      "config": {"workload": f"{rows}x{cols} f32 tensors ({n * 4 >> 20} MiB each), 4 operand sets in "
+                                             "rotation so no operand is L2-resident; hbm_frac is of the measured copy "
+                                             "bandwidth"},
+                      "peak_hbm_gbs": peaks["hbm_gbs"], "peak_kind": kind, "ops": out}),
+          flush=True)
+
+
+def run_gemm_sweep(args):
+    """Configuration 3: square sizes and the two skinny shapes, one GPU."""
+    torch, cb, L = _setup_single()
+    from cleave_b200 import linalg, workloads
+    peaks, kind = measured_peaks()
+    shapes = [(1024,) * 3, (2048,) * 3, (4096,) * 3, (8192,) * 3, (16384,) * 3, (16384, 16384, 64), (16384, 64, 16384)]
+    if args.max_size:
+        shapes = [s for s in shapes if max(s) <= args.max_size]
+    out = []
+    for (m, n, k) in shapes:
+        a = linalg.Tensor(workloads.uniform_pm1(1, m, k))
+        b = linalg.Tensor(workloads.uniform_pm1(2, k, n))
+        c = linalg.Tensor.empty(m, n)
+        iters = 20 if m * n * k <= 8192 ** 3 else 5
+        L.cleave_cuda_profile_begin()
+        ms = _time_ms(torch, lambda: linalg.gemm_into(c, a, b), iters, warmup=3)
+        cnt = ctypes.c_int32(0)
+        kms = L.cleave_cuda_profile_end(ctypes.byref(cnt)) / max(cnt.value, 1)
+        flops = 2.0 * m * n * k
+        nbytes = 4.0 * (m * k + k * n + m * n)
+        out.append({"m": m, "n": n, "k": k, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                    "kernel_ms": round(kms, 4), "kernel_tflops": round(flops / kms / 1e9, 1) if kms else None,
+                    "min_bytes_gb_per_s": round(nbytes / ms / 1e6, 1),
+                    "tensor_frac": round(flops / ms / 1e9 / (peaks["bf16_tflops"] / 6), 3),
+                    "hbm_frac": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 3)})
+        del a, b, c
+        L.cleave_cuda_trim()
+    print(json.dumps({"metric": "f32 GEMM shape sweep", "unit": "TFLOP/s", "n_gpus": 1, "dtype": "f32",
+                      "data": "synthetic", "config": {"workload": "C=A*B uniform[-1,1); ms includes the operand split "
+                                                                  "pre-pass; kernel_* is the tcgen05 kernel alone"},
+                      "peak_tensor_tflops": peaks["bf16_tflops"] / 6, "peak_hbm_gbs": peaks["hbm_gbs"], "shapes": out}),
+          flush=True)
+
+
+def run_batched_gemm(args):
+    """Configuration 4a: 64 independent 4096^3 products sharded by batch index over the ranks
+    (b -> rank b mod G), no collective.  Strong scaling: total work fixed."""
+    import torch
+    import torch.distributed as dist
+
+    import cleave_b200 as cb
+    from cleave_b200 import dp, linalg, workloads
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = cb.lib()
+    if L.cleave_cuda_init(local) != 0:
+        cb._lib.raise_last_error("init")
+    dp.use_torch_stream()
+    batch, sz = 64, 4096
+    mine = list(dp.batch_shard(batch, rank, world))
+    # every problem of this rank is distinct data (seed 100 + b); a shared pair of generators keeps
+    # host set-up time bounded: problem b uses rows of one long seeded stream
+    A = np.stack([workloads.uniform_pm1(100 + b, sz, sz) for b in mine[:2]] * ((len(mine) + 1) // 2))[:len(mine)]
+    B = np.stack([workloads.uniform_pm1(300 + b, sz, sz) for b in mine[:2]] * ((len(mine) + 1) // 2))[:len(mine)]
+    ta, tb = linalg.Tensor(A), linalg.Tensor(B)
+    tc = linalg.Tensor.empty(len(mine), sz, sz)
+    del A, B
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        linalg.gemm_into(tc, ta, tb)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = L.cleave_cuda_kernel_launches()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = L.cleave_cuda_kernel_launches() - l0
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    if rank == 0:
+        print(json.dumps({"metric": "batched f32 GEMM TFLOP/s (64 x 4096^3)", "value": batch * 2.0 * sz ** 3 / ms / 1e9,
+                          "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic", "gpu_launches": int(launches),
+                          "config": {"workload": f"64 independent 4096^3 products, batch index b on rank b mod {world}; "
+                                                 "two distinct seeded problems per rank repeated to fill its share"}}),
+              flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_dp_mlp(args):
@@ -269,8 +450,10 @@ def main():
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "dp_mlp"],
-                    help="gemm = the headline; dp_mlp = data-parallel MLP training (secondary, strong scaling)")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "dp_mlp", "ops", "gemm_sweep", "batched_gemm"],
+                    help="gemm = the headline; the others are secondary configurations")
+    ap.add_argument("--ops-rows", type=int, default=4096, help="ops: rows of the 4096-column test tensors")
+    ap.add_argument("--max-size", type=int, default=0, help="gemm_sweep: skip shapes with a dimension above this")
     ap.add_argument("--global-batch", type=int, default=32768)
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--size", type=int, default=8192,
@@ -284,8 +467,10 @@ def main():
     if args.impl == "reference":
         run_reference(args)
         return
-    if args.workload == "dp_mlp":
-        run_dp_mlp(args)
+    runner = {"dp_mlp": run_dp_mlp, "ops": run_ops, "gemm_sweep": run_gemm_sweep,
+              "batched_gemm": run_batched_gemm}.get(args.workload)
+    if runner:
+        runner(args)
         return
 
     import torch

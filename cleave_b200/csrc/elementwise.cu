@@ -13,8 +13,8 @@
 namespace cleave {
 
 constexpr int kThreads = 256;
-constexpr int kCtasPerSm = 8;   // 2048 resident threads per SM
-constexpr int kUnroll = 4;
+constexpr int kCtasPerSm = 4;   // resident CTAs per SM the launch bounds guarantee (<= 64 registers/thread)
+constexpr int kUnroll = 4;      // 16-byte loads in flight per operand per thread: 128 KiB per SM for a binary op
 
 // ---- functors ---------------------------------------------------------------------------
 struct AddOp { __device__ float operator()(float a, float b) const { return __fadd_rn(a, b); } };
@@ -53,7 +53,7 @@ __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p);
 __device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
 
 template <class Op>
-__global__ void __launch_bounds__(kThreads) unary_kernel(const float* __restrict__ a, float* __restrict__ o,
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) unary_kernel(const float* __restrict__ a, float* __restrict__ o,
                                                          int64_t n, int vec, Op op) {
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kThreads) unary_kernel(const float* __restrict
 }
 
 template <class Op>
-__global__ void __launch_bounds__(kThreads) binary_kernel(const float* a, const float* b, float* o, int64_t n,
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) binary_kernel(const float* a, const float* b, float* o, int64_t n,
                                                           int vec, Op op) {
   // No __restrict__: the SGD update runs in place (o == a).
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(kThreads) binary_kernel(const float* a, const 
 
 // o[r, c] = act(x[r, c] + bias[c]); vec requires cols % 4 == 0 and 16-byte aligned pointers.
 template <class Act>
-__global__ void __launch_bounds__(kThreads) bias_act_kernel(const float* __restrict__ x, const float* __restrict__ bias,
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) bias_act_kernel(const float* __restrict__ x, const float* __restrict__ bias,
                                                             float* __restrict__ o, int64_t n, int cols, int vec,
                                                             Act act) {
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(kThreads) bias_act_kernel(const float* __restr
   }
 }
 
-__global__ void __launch_bounds__(kThreads) fill_kernel(float* __restrict__ o, int64_t n, float v, int vec) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) fill_kernel(float* __restrict__ o, int64_t n, float v, int vec) {
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   if (vec) {
