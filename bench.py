@@ -392,9 +392,18 @@ def run_dp_mlp(args):
     dp.use_torch_stream()
     global_batch, d_in, d_hid, d_out = args.global_batch, 1024, 4096, 1024
     _, W1, b1, W2, b2, _ = workloads.mlp_inputs(1, d_in, d_hid, d_out)
-    net = autodiff.MLP2(d_in, d_hid, d_out)
+    if args.dp_mode == "nccl" or world == 1:
+        net = autodiff.MLP2(d_in, d_hid, d_out)
+        trainer = dp.DataParallel(dp.MLP2Replica(net), overlap=not args.no_overlap)
+        mode = "nccl all-reduce + fused 1/G SGD pass" if world > 1 else "single rank"
+    else:
+        n_params = d_in * d_hid + d_hid + d_hid * d_out + d_out
+        trainer = dp.FusedDataParallel(n_params, lambda p, g: autodiff.MLP2(d_in, d_hid, d_out, params=p, grads=g),
+                                       multimem=args.dp_mode == "fused")
+        net = trainer.net
+        mode = "one kernel: " + ("multimem.ld_reduce in NVSwitch" if trainer.multimem else "peer loads") + \
+               " + SGD + replication of the new weights"
     net.load(W1, b1, W2, b2)
-    trainer = dp.DataParallel(dp.MLP2Replica(net), overlap=not args.no_overlap)
     X, T = dp.dp_batch_inputs(global_batch, rank, world, d_in, d_out)
     tX, tT = linalg.Tensor(X), linalg.Tensor(T)
 
@@ -432,7 +441,8 @@ def run_dp_mlp(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"2-layer MLP 1024->4096 tanh->1024 sigmoid, MSE, SGD lr 1e-3, global batch "
                                    f"{global_batch} split over {world} rank(s), gradient all-reduce (mean) every step",
-                       "allreduce_bytes_per_step": 4 * nparams, "overlap": not args.no_overlap},
+                       "allreduce_bytes_per_step": 4 * nparams, "exchange": mode,
+                       "overlap": not args.no_overlap},
             "gpu_launches": int(launches), "clocks": clocks, "loss": loss,
             "replicas_identical": bool(pmin.item() == pmax.item()),
             "gemm_tflops_per_gpu": 5 * 2.0 * (global_batch / world) * d_hid * d_in / (ms * 1e-3) / 1e12,
@@ -456,6 +466,8 @@ def main():
     ap.add_argument("--max-size", type=int, default=0, help="gemm_sweep: skip shapes with a dimension above this")
     ap.add_argument("--global-batch", type=int, default=32768)
     ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--dp-mode", default="fused", choices=["fused", "fused_p2p", "nccl"],
+                    help="dp_mlp: gradient exchange as one multimem kernel, one peer-load kernel, or NCCL + SGD")
     ap.add_argument("--size", type=int, default=8192,
                     help="M=N=K; anything but 8192 is a profiling case, not the headline workload")
     args = ap.parse_args()

@@ -34,15 +34,21 @@ class MLP2:
     in a buffer ``grads`` with the same layout; ``W1`` ... ``db2`` are views into them.
     """
 
-    def __init__(self, d_in: int, d_hid: int, d_out: int, act1: str = "tanh", act2: str = "sigmoid"):
+    def __init__(self, d_in: int, d_hid: int, d_out: int, act1: str = "tanh", act2: str = "sigmoid",
+                 params: Tensor | None = None, grads: Tensor | None = None):
+        """``params`` / ``grads``: optional caller-provided flat buffers (e.g. views of symmetric
+        memory shared with the other data-parallel ranks); allocated here when omitted."""
         if act1 not in _ACT_BWD or act2 not in _ACT_BWD:
             raise ValueError("activations with a declared derivative rule: tanh, sigmoid")
         self.d_in, self.d_hid, self.d_out, self.act1, self.act2 = d_in, d_hid, d_out, act1, act2
         sizes = [d_in * d_hid, d_hid, d_hid * d_out, d_out]
         shapes = [(d_in, d_hid), (d_hid,), (d_hid, d_out), (d_out,)]
         self.n_params = sum(sizes)
-        self.params = Tensor.zero(self.n_params)
-        self.grads = Tensor.zero(self.n_params)
+        for given in (params, grads):
+            if given is not None and given.numel != self.n_params:
+                raise TypeError(f"flat buffer has {given.numel} elements, the network has {self.n_params}")
+        self.params = params if params is not None else Tensor.zero(self.n_params)
+        self.grads = grads if grads is not None else Tensor.zero(self.n_params)
         offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
         self._offsets = offs
 
@@ -76,8 +82,7 @@ class MLP2:
         (and, with ``keep``, the intermediates for inspection).  ``on_grads_ready(i)`` is called
         when a gradient bucket is final: 0 = [dW2 | db2], 1 = [dW1 | db1]."""
         H, Y = self.forward(X)
-        loss, dY = nn.mse(Y, T)
-        dZ2 = _ACT_BWD[self.act2](Y, dY)
+        loss, dZ2 = nn.mse_act_bwd(Y, T, self.act2)   # dY and act2'(Y) * dY in one pass
         gemm_into(self.dW2, H, dZ2, trans_a=True)            # H^T dZ2
         self._colsum_into(self.db2, dZ2)
         if on_grads_ready:

@@ -36,7 +36,8 @@ struct Context {
   cudaStream_t stream = nullptr;      // stream in use (own or caller's)
   DeviceStatus* status_host = nullptr;
   DeviceStatus* status_dev = nullptr;
-  float* scalar_host = nullptr;       // pinned landing area for scalar results (64 floats)
+  float* scalar_host = nullptr;       // pinned, mapped landing area for scalar results (64 floats)
+  float* scalar_dev = nullptr;        // device alias of scalar_host: kernels write results straight to the host
 };
 
 Context& ctx();
@@ -65,6 +66,10 @@ void count_launch(int n = 1);
 // Reads one f32 produced on the device at `dev_scalar`: copies to pinned memory, syncs,
 // checks the status word.  Returns NaN on failure.
 float read_scalar(const float* dev_scalar);
+// Scalar results without a copy: a kernel writes the value to scalar_slot() (mapped host memory),
+// wait_scalar() synchronises the stream, checks the status word and returns it (NaN on failure).
+float* scalar_slot();
+float wait_scalar();
 
 // ---- launch geometry -------------------------------------------------------------------
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }

@@ -395,13 +395,34 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const int col0 = nb * BN + half * (BN / 2);
       if (row < p.m) {
         float* crow = p.c + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
-        if (p.bias != nullptr || p.act != CLEAVE_ACT_IDENTITY) {
+        if (p.bias != nullptr) {
+          if (vec_ok && col0 + BN / 2 <= p.n && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) {
+            const float4* b4 = reinterpret_cast<const float4*>(p.bias + col0);
 #pragma unroll
-          for (int j = 0; j < BN / 2; ++j) {
-            float x = sum[j];
-            if (p.bias != nullptr && col0 + j < p.n) x = __fadd_rn(x, __ldg(p.bias + col0 + j));
-            sum[j] = act_apply(x, p.act);
+            for (int j = 0; j < BN / 8; ++j) {
+              const float4 bv = __ldg(b4 + j);
+              sum[4 * j] = __fadd_rn(sum[4 * j], bv.x);
+              sum[4 * j + 1] = __fadd_rn(sum[4 * j + 1], bv.y);
+              sum[4 * j + 2] = __fadd_rn(sum[4 * j + 2], bv.z);
+              sum[4 * j + 3] = __fadd_rn(sum[4 * j + 3], bv.w);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 2; ++j)
+              if (col0 + j < p.n) sum[j] = __fadd_rn(sum[j], __ldg(p.bias + col0 + j));
           }
+        }
+        // One loop per activation (the choice is uniform for the launch), so each is a straight
+        // unrolled sequence over independent elements.
+        if (p.act == CLEAVE_ACT_TANH) {
+#pragma unroll
+          for (int j = 0; j < BN / 2; ++j) sum[j] = tanhf(sum[j]);
+        } else if (p.act == CLEAVE_ACT_SIGMOID) {
+#pragma unroll
+          for (int j = 0; j < BN / 2; ++j) sum[j] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-sum[j])));
+        } else if (p.act == CLEAVE_ACT_RELU) {
+#pragma unroll
+          for (int j = 0; j < BN / 2; ++j) sum[j] = act_apply(sum[j], CLEAVE_ACT_RELU);
         }
         if (vec_ok && col0 + BN / 2 <= p.n) {
           float4* dst = reinterpret_cast<float4*>(crow);

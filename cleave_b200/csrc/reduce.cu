@@ -157,9 +157,19 @@ __global__ void __launch_bounds__(kRThreads) colsum_stage2(const float* __restri
 }
 
 // ---- fused MSE: partial sums of (p-t)^2 and, optionally, dp = 2 (p-t) / n -----------------------
+// With bwd_act != identity, p is the OUTPUT of that activation and the value written is the
+// gradient with respect to the pre-activation: act'(p) * 2 (p - t) / n, each factor rounded as the
+// separate mse and *_bwd entry points round it (so the fused result is bit-identical to the chain).
+__device__ __forceinline__ float mse_grad(float p, float e, float fn, int bwd_act) {
+  float d = __fdiv_rn(__fmul_rn(2.0f, e), fn);
+  if (bwd_act == CLEAVE_ACT_SIGMOID) d = __fmul_rn(__fmul_rn(p, __fsub_rn(1.0f, p)), d);
+  else if (bwd_act == CLEAVE_ACT_TANH) d = __fmul_rn(__fsub_rn(1.0f, __fmul_rn(p, p)), d);
+  return d;
+}
+
 __global__ void __launch_bounds__(kRThreads) mse_stage1(const float* __restrict__ p, const float* __restrict__ t,
                                                         float* __restrict__ dp, int64_t n, int64_t slab, float fn,
-                                                        float* __restrict__ partials, int vec) {
+                                                        float* __restrict__ partials, int vec, int bwd_act) {
   const int64_t lo = (int64_t)blockIdx.x * slab;
   int64_t hi = lo + slab;
   if (hi > n) hi = n;
@@ -176,21 +186,21 @@ __global__ void __launch_bounds__(kRThreads) mse_stage1(const float* __restrict_
                                      __fadd_rn(__fmul_rn(e2, e2), __fmul_rn(e3, e3))));
       if (dp) {
         float4 d;
-        d.x = __fdiv_rn(__fmul_rn(2.0f, e0), fn); d.y = __fdiv_rn(__fmul_rn(2.0f, e1), fn);
-        d.z = __fdiv_rn(__fmul_rn(2.0f, e2), fn); d.w = __fdiv_rn(__fmul_rn(2.0f, e3), fn);
+        d.x = mse_grad(a.x, e0, fn, bwd_act); d.y = mse_grad(a.y, e1, fn, bwd_act);
+        d.z = mse_grad(a.z, e2, fn, bwd_act); d.w = mse_grad(a.w, e3, fn, bwd_act);
         __stcs(d4 + i, d);
       }
     }
     for (int64_t i = (hi4 << 2) + threadIdx.x; i < hi; i += kRThreads) {
       float e = __fsub_rn(p[i], t[i]);
       acc = __fadd_rn(acc, __fmul_rn(e, e));
-      if (dp) dp[i] = __fdiv_rn(__fmul_rn(2.0f, e), fn);
+      if (dp) dp[i] = mse_grad(p[i], e, fn, bwd_act);
     }
   } else {
     for (int64_t i = lo + threadIdx.x; i < hi; i += kRThreads) {
       float e = __fsub_rn(p[i], t[i]);
       acc = __fadd_rn(acc, __fmul_rn(e, e));
-      if (dp) dp[i] = __fdiv_rn(__fmul_rn(2.0f, e), fn);
+      if (dp) dp[i] = mse_grad(p[i], e, fn, bwd_act);
     }
   }
   acc = block_reduce<SumRed>(acc);
@@ -208,9 +218,19 @@ __global__ void __launch_bounds__(kRThreads) linreg_stage1(const float* __restri
                                                            const float* __restrict__ w, float* __restrict__ pred,
                                                            int64_t rows, int64_t slab, float fn,
                                                            float* __restrict__ partials) {
+  // Each warp takes 32 consecutive rows at a time.  The 32*FEAT floats of such a group are
+  // contiguous in X, so the warp reads them with fully coalesced 16-byte loads (lane l takes
+  // 16-byte words l, l+32, ...), parks them in a warp-private shared tile and every lane then
+  // picks up ITS row.  Words of row r are stored at slot q ^ swz(r), which makes both the
+  // coalesced writes and the row-wise 16-byte reads bank-conflict free.
+  static_assert(FEAT % 4 == 0 && FEAT >= 4 && FEAT <= 32, "FEAT must be 4, 8, 16 or 32");
+  constexpr int Q = FEAT / 4;                 // 16-byte words per row
+  constexpr int kRowsPerSwz = Q >= 8 ? 1 : 8 / Q;
   __shared__ float sw[FEAT];
+  __shared__ float4 tile[kRWarps][32 * Q];
   if (threadIdx.x < FEAT) sw[threadIdx.x] = w[threadIdx.x];
   __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t lo = (int64_t)blockIdx.x * slab;
   int64_t hi = lo + slab;
   if (hi > rows) hi = rows;
@@ -218,36 +238,50 @@ __global__ void __launch_bounds__(kRThreads) linreg_stage1(const float* __restri
 #pragma unroll
   for (int f = 0; f < FEAT; ++f) g[f] = 0.0f;
   float loss = 0.0f;
-  for (int64_t i = lo + threadIdx.x; i < hi; i += kRThreads) {
-    float xr[FEAT];
-    if (FEAT % 4 == 0) {
-      const float4* x4 = reinterpret_cast<const float4*>(X + i * FEAT);
+  float4* my_tile = tile[warp];
+  const int my_swz = (lane / kRowsPerSwz) & (Q - 1);
+  for (int64_t r0 = lo + (int64_t)warp * 32; r0 < hi; r0 += (int64_t)kRWarps * 32) {
+    const float4* src = reinterpret_cast<const float4*>(X + r0 * FEAT);
+    float4 v[Q];
 #pragma unroll
-      for (int q = 0; q < FEAT / 4; ++q) {
-        float4 v = __ldcs(x4 + q);
-        xr[4 * q] = v.x; xr[4 * q + 1] = v.y; xr[4 * q + 2] = v.z; xr[4 * q + 3] = v.w;
-      }
-    } else {
-#pragma unroll
-      for (int f = 0; f < FEAT; ++f) xr[f] = X[i * FEAT + f];
+    for (int i = 0; i < Q; ++i) {
+      const int idx = lane + 32 * i;
+      v[i] = (r0 + idx / Q < hi) ? __ldcs(src + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    float acc = 0.0f;
 #pragma unroll
-    for (int f = 0; f < FEAT; ++f) acc = __fadd_rn(acc, __fmul_rn(xr[f], sw[f]));
-    if (pred) pred[i] = acc;
-    float e = __fsub_rn(acc, __ldcs(y + i));
-    loss = __fadd_rn(loss, __fmul_rn(e, e));
-    float d = __fdiv_rn(__fmul_rn(2.0f, e), fn);
+    for (int i = 0; i < Q; ++i) {
+      const int idx = lane + 32 * i;
+      const int r = idx / Q, q = idx % Q;
+      my_tile[r * Q + (q ^ ((r / kRowsPerSwz) & (Q - 1)))] = v[i];
+    }
+    __syncwarp();
+    float xr[FEAT];
 #pragma unroll
-    for (int f = 0; f < FEAT; ++f) g[f] = __fadd_rn(g[f], __fmul_rn(xr[f], d));
+    for (int q = 0; q < Q; ++q) {
+      const float4 t = my_tile[lane * Q + (q ^ my_swz)];
+      xr[4 * q] = t.x; xr[4 * q + 1] = t.y; xr[4 * q + 2] = t.z; xr[4 * q + 3] = t.w;
+    }
+    __syncwarp();
+    const int64_t i = r0 + lane;
+    if (i < hi) {
+      float acc = 0.0f;
+#pragma unroll
+      for (int f = 0; f < FEAT; ++f) acc = __fadd_rn(acc, __fmul_rn(xr[f], sw[f]));
+      if (pred) pred[i] = acc;
+      const float e = __fsub_rn(acc, __ldcs(y + i));
+      loss = __fadd_rn(loss, __fmul_rn(e, e));
+      const float d = __fdiv_rn(__fmul_rn(2.0f, e), fn);
+#pragma unroll
+      for (int f = 0; f < FEAT; ++f) g[f] = __fadd_rn(g[f], __fmul_rn(xr[f], d));
+    }
   }
 #pragma unroll
   for (int f = 0; f < FEAT; ++f) {
     float t = block_reduce<SumRed>(g[f]);
-    if (threadIdx.x == 0) partials[(int64_t)blockIdx.x * (FEAT + 1) + f] = t;
+    if (threadIdx.x == 0) partials[(int64_t)f * gridDim.x + blockIdx.x] = t;
   }
   loss = block_reduce<SumRed>(loss);
-  if (threadIdx.x == 0) partials[(int64_t)blockIdx.x * (FEAT + 1) + FEAT] = loss;
+  if (threadIdx.x == 0) partials[(int64_t)FEAT * gridDim.x + blockIdx.x] = loss;
 }
 
 // Generic-feat fallback (feat <= 32, any value): same arithmetic, runtime loops.
@@ -280,23 +314,30 @@ __global__ void __launch_bounds__(kRThreads) linreg_stage1_any(const float* __re
   for (int f = 0; f < kMaxFeat; ++f) {
     if (f < feat) {   // uniform across the block
       float t = block_reduce<SumRed>(g[f]);
-      if (threadIdx.x == 0) partials[(int64_t)blockIdx.x * (feat + 1) + f] = t;
+      if (threadIdx.x == 0) partials[(int64_t)f * gridDim.x + blockIdx.x] = t;
     }
   }
   loss = block_reduce<SumRed>(loss);
-  if (threadIdx.x == 0) partials[(int64_t)blockIdx.x * (feat + 1) + feat] = loss;
+  if (threadIdx.x == 0) partials[(int64_t)feat * gridDim.x + blockIdx.x] = loss;
 }
 
-// Stage 2: thread f (< feat + 1) folds column f of the partials in CTA order.
-// out[0..feat) = gradient, out[feat] = loss sum / rows.
-__global__ void linreg_stage2(const float* __restrict__ partials, int ctas, int feat, float fn,
-                              float* __restrict__ grad, float* __restrict__ loss_out) {
-  const int f = threadIdx.x;
-  if (f > feat) return;
-  float acc = partials[f];
-  for (int b = 1; b < ctas; ++b) acc = __fadd_rn(acc, partials[(int64_t)b * (feat + 1) + f]);
-  if (f < feat) grad[f] = acc;
-  else loss_out[0] = __fdiv_rn(acc, fn);
+// Stage 2: one warp per quantity (feat gradient components, then the loss).  The partials of
+// quantity f are contiguous (partials[f][cta]); lane l folds entries l, l+32, ... in ascending
+// order and the 32 lane sums are combined by a fixed shuffle tree: deterministic.
+// grad[0..feat) = gradient, loss_out[0] = loss sum / rows.
+__global__ void __launch_bounds__(1024) linreg_stage2(const float* __restrict__ partials, int ctas, int feat, float fn,
+                                                     float* __restrict__ grad, float* __restrict__ loss_out) {
+  const int lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int f = threadIdx.x >> 5; f <= feat; f += nwarps) {
+    const float* col = partials + (int64_t)f * ctas;
+    float acc = 0.0f;
+    for (int b = lane; b < ctas; b += 32) acc = __fadd_rn(acc, col[b]);
+    acc = warp_reduce<SumRed>(acc);
+    if (lane == 0) {
+      if (f < feat) grad[f] = acc;
+      else loss_out[0] = __fdiv_rn(acc, fn);
+    }
+  }
 }
 
 // ---- host side -------------------------------------------------------------------------------
@@ -317,7 +358,7 @@ static float reduce_scalar(const float* v, int64_t n, int64_t first, float divis
   int64_t cnt = n - first;
   float* partials = scratch_alloc((kMaxPartials + 4) * sizeof(float));
   if (!partials) return NAN;
-  float* out = partials + kMaxPartials;
+  float* out = scalar_slot();
   cudaStream_t s = ctx().stream;
   int ctas = 0;
   if (cnt > 0) {
@@ -330,7 +371,7 @@ static float reduce_scalar(const float* v, int64_t n, int64_t first, float divis
   reduce_stage2<R><<<1, kRThreads, 0, s>>>(partials, ctas, out, divisor, mode, v);
   count_launch();
   float r = NAN;
-  if (cuda_ok(cudaGetLastError(), "reduction launch")) r = read_scalar(out);
+  if (cuda_ok(cudaGetLastError(), "reduction launch")) r = wait_scalar();
   scratch_free(partials);
   return r;
 }
@@ -411,37 +452,55 @@ int32_t cleave_cuda_colsum_into_f32(cleave_buf out, cleave_buf x, int32_t rows, 
   return colsum_launch(a->ptr, o->ptr, rows, cols) ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
 }
 
-float cleave_cuda_mse_f32(cleave_buf p, cleave_buf t, cleave_buf dp) {
+static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, const char* name) {
   ApiLock lock;
-  Buf* a = as_buf(p, "mse");
-  Buf* b = as_buf(t, "mse");
+  Buf* a = as_buf(p, name);
+  Buf* b = as_buf(t, name);
   if (!a || !b) return NAN;
   Buf* d = nullptr;
   if (dp) {
-    d = as_buf(dp, "mse");
+    d = as_buf(dp, name);
     if (!d) return NAN;
   }
   if (a->len != b->len || (d && d->len != a->len)) {
-    set_error(CLEAVE_CUDA_ERR_SHAPE, "mse: prediction, target and gradient tensors must have the same length");
+    set_error(CLEAVE_CUDA_ERR_SHAPE, "%s: prediction, target and gradient tensors must have the same length", name);
+    return NAN;
+  }
+  if (bwd_act != CLEAVE_ACT_IDENTITY && bwd_act != CLEAVE_ACT_SIGMOID && bwd_act != CLEAVE_ACT_TANH) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "%s: activation code %d has no output-form derivative (use identity, sigmoid or tanh)",
+              name, bwd_act);
     return NAN;
   }
   const int64_t n = a->len;
   float* partials = scratch_alloc((kMaxPartials + 4) * sizeof(float));
   if (!partials) return NAN;
-  float* out = partials + kMaxPartials;
   int64_t slab;
   int ctas;
   slab_for(n, &slab, &ctas);
   int vec = (aligned16(a->ptr) && aligned16(b->ptr) && (!d || aligned16(d->ptr))) ? 1 : 0;
   const float fn = (float)(int32_t)n;
   cudaStream_t s = ctx().stream;
-  mse_stage1<<<ctas, kRThreads, 0, s>>>(a->ptr, b->ptr, d ? d->ptr : nullptr, n, slab, fn, partials, vec);
+  float* out = scalar_slot();
+  mse_stage1<<<ctas, kRThreads, 0, s>>>(a->ptr, b->ptr, d ? d->ptr : nullptr, n, slab, fn, partials, vec, bwd_act);
   reduce_stage2<SumRed><<<1, kRThreads, 0, s>>>(partials, ctas, out, fn, 0, nullptr);
   count_launch(2);
   float r = NAN;
-  if (cuda_ok(cudaGetLastError(), "mse launch")) r = read_scalar(out);
+  if (cuda_ok(cudaGetLastError(), "mse launch")) r = wait_scalar();
   scratch_free(partials);
   return r;
+}
+
+float cleave_cuda_mse_f32(cleave_buf p, cleave_buf t, cleave_buf dp) {
+  return mse_impl(p, t, dp, CLEAVE_ACT_IDENTITY, "mse");
+}
+
+float cleave_cuda_mse_act_bwd_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act) {
+  if (!dz) {
+    ApiLock lock;
+    set_error(CLEAVE_CUDA_ERR_ARG, "mse_act_bwd: the gradient output handle is required");
+    return NAN;
+  }
+  return mse_impl(y, t, dz, act, "mse_act_bwd");
 }
 
 float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out, cleave_buf grad_out,
@@ -471,7 +530,7 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
   int ctas = (int)(((int64_t)rows + slab - 1) / slab);
   float* partials = scratch_alloc(((int64_t)ctas * (feat + 1) + 4) * sizeof(float));
   if (!partials) return NAN;
-  float* out = partials + (int64_t)ctas * (feat + 1);
+  float* out = scalar_slot();
   const float fn = (float)rows;
   cudaStream_t s = ctx().stream;
   float* pp = P ? P->ptr : nullptr;
@@ -481,12 +540,14 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
     linreg_stage1<32><<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials);
   else if (feat == 8 && aligned16(X->ptr))
     linreg_stage1<8><<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials);
+  else if (feat == 4 && aligned16(X->ptr))
+    linreg_stage1<4><<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials);
   else
     linreg_stage1_any<<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, feat, slab, fn, partials);
-  linreg_stage2<<<1, 64, 0, s>>>(partials, ctas, feat, fn, G->ptr, out);
+  linreg_stage2<<<1, 32 * (feat + 1 > 32 ? 32 : feat + 1), 0, s>>>(partials, ctas, feat, fn, G->ptr, out);
   count_launch(2);
   float r = NAN;
-  if (cuda_ok(cudaGetLastError(), "linreg launch")) r = read_scalar(out);
+  if (cuda_ok(cudaGetLastError(), "linreg launch")) r = wait_scalar();
   scratch_free(partials);
   return r;
 }

@@ -89,7 +89,9 @@ static bool init_device(int device) {
   memset(g_ctx.status_host, 0, sizeof(DeviceStatus));
   if (!cuda_ok(cudaHostGetDevicePointer((void**)&g_ctx.status_dev, g_ctx.status_host, 0), "cudaHostGetDevicePointer"))
     return false;
-  if (!cuda_ok(cudaHostAlloc((void**)&g_ctx.scalar_host, 64 * sizeof(float), cudaHostAllocDefault), "cudaHostAlloc"))
+  if (!cuda_ok(cudaHostAlloc((void**)&g_ctx.scalar_host, 64 * sizeof(float), cudaHostAllocMapped), "cudaHostAlloc"))
+    return false;
+  if (!cuda_ok(cudaHostGetDevicePointer((void**)&g_ctx.scalar_dev, g_ctx.scalar_host, 0), "cudaHostGetDevicePointer"))
     return false;
   g_ctx.ready = true;
   return true;
@@ -226,6 +228,15 @@ float read_scalar(const float* dev_scalar) {
   if (!cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize")) return NAN;
   if (check_device_status() != CLEAVE_CUDA_OK) return NAN;
   return c.scalar_host[0];
+}
+
+float* scalar_slot() { return g_ctx.scalar_dev + 1; }   // slot 0 is read_scalar's copy target
+
+float wait_scalar() {
+  Context& c = g_ctx;
+  if (!cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize")) return NAN;
+  if (check_device_status() != CLEAVE_CUDA_OK) return NAN;
+  return ((volatile float*)c.scalar_host)[1];
 }
 
 }  // namespace cleave

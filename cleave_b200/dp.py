@@ -106,6 +106,61 @@ class DataParallel:
         return loss
 
 
+class FusedDataParallel:
+    """Data-parallel SGD where the gradient sum, the update and the replication of the new weights
+    are ONE libcleave_cuda kernel over NVLink peer memory (``cleave_cuda_dp_sgd_allreduce_f32``)
+    instead of an NCCL all-reduce followed by an SGD pass.
+
+    Parameters and gradients live in torch symmetric memory (the plumbing that allocates the same
+    buffer on every rank and exchanges the peer / multicast addresses); ``make_net(params, grads)``
+    must build the replica on those flat buffers.  ``multimem=True`` sums in the NVSwitch when
+    the fabric offers a multicast address; ``False`` uses plain peer loads in rank order.
+    """
+
+    def __init__(self, n_params: int, make_net, group=None, multimem: bool = True):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from .linalg import Tensor
+        if n_params % 4:
+            raise ValueError("the flat parameter vector must be a multiple of 4 elements (16-byte words)")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self._bufs, self._hdls = [], []
+        for n, dt in ((n_params, torch.float32), (n_params, torch.float32), (64, torch.int32)):
+            t = symm.empty(n, dtype=dt, device=dev)
+            t.zero_()
+            self._bufs.append(t)
+        torch.cuda.synchronize()
+        for t in self._bufs:
+            self._hdls.append(symm.rendezvous(t, self.group))
+        dist.barrier(self.group)
+        p, g, f = self._hdls
+        self.multimem = bool(multimem and p.has_multicast_support and p.multicast_ptr and g.multicast_ptr)
+        arr = ctypes.c_void_p * self.world
+        self._tables = [arr(*[int(h.buffer_ptrs[r]) for r in range(self.world)]) for h in (p, g, f)]
+        self._mc = (ctypes.c_void_p(int(p.multicast_ptr)), ctypes.c_void_p(int(g.multicast_ptr))) if self.multimem \
+            else (None, None)
+        self.n_params = n_params
+        self.params = Tensor.from_device_ptr(self._bufs[0].data_ptr(), n_params)
+        self.grads = Tensor.from_device_ptr(self._bufs[1].data_ptr(), n_params)
+        self.net = make_net(self.params, self.grads)
+        self.epoch = 1
+
+    def step(self, X, T, lr: float):
+        from ._lib import lib, raise_last_error
+        loss = self.net.forward_backward(X, T)
+        rc = lib().cleave_cuda_dp_sgd_allreduce_f32(self._tables[0], self._tables[1], self._tables[2], self._mc[0],
+                                                    self._mc[1], self.n_params, self.rank, self.world, float(lr),
+                                                    self.epoch)
+        if rc != 0:
+            raise_last_error("dp_sgd_allreduce")
+        self.epoch += 2
+        return loss
+
+
 class MLP2Replica:
     """Adapter of ``autodiff.MLP2`` to the ``DataParallel`` interface."""
 

@@ -87,6 +87,18 @@ def mse(pred: Tensor, target: Tensor, want_grad: bool = True):
     return (loss, d) if want_grad else loss
 
 
+def mse_act_bwd(y: Tensor, target: Tensor, act: str):
+    """Loss ``mean((y - target)^2)`` for ``y = act(z)`` and the gradient with respect to ``z``
+    (``act'(y) * 2 (y - target) / numel``) in one pass; equals ``mse`` followed by ``*_bwd``."""
+    if y.dims != target.dims:
+        raise TypeError(f"mse_act_bwd: mismatched types {y!r} and {target!r}")
+    dz = Tensor.empty(*y.dims)
+    loss = lib().cleave_cuda_mse_act_bwd_f32(y._h, target._h, dz._h, ACT[act])
+    if math.isnan(loss) and lib().cleave_cuda_last_error():
+        raise_last_error("mse_act_bwd")
+    return loss, dz
+
+
 def sgd_step(w: Tensor, g: Tensor, lr: float, gscale: float = 1.0) -> None:
     """``w = w - lr * (gscale * g)`` in place (examples/xor.cleave:67-70)."""
     if w.dims != g.dims:

@@ -177,6 +177,10 @@ cleave_buf cleave_cuda_bias_act_f32(cleave_buf x, cleave_buf bias, int32_t rows,
 /* mean((p - t)^2) (examples/linear_regression.cleave:20-30 with Mean, nn.cleave:119-139).
  * If dp is non-NULL it receives 2*(p - t)/len, the gradient with respect to p. */
 float cleave_cuda_mse_f32(cleave_buf p, cleave_buf t, cleave_buf dp);
+/* The same loss for y = act(z), with the chain through the activation folded in: dz receives
+ * act'(y) * 2*(y - t)/len, the gradient with respect to the PRE-activation z, in one pass
+ * (mse followed by sigmoid_bwd / tanh_bwd, bit for bit).  act: identity, sigmoid or tanh. */
+float cleave_cuda_mse_act_bwd_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act);
 /* w = w - lr * (gscale * g) in place (examples/xor.cleave:67-70); gscale folds the 1/G of a
  * gradient mean over G data-parallel ranks into the same pass. */
 int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale);
@@ -185,6 +189,23 @@ int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale);
  * (feat) are caller-owned handles; pred_out may be NULL.  feat <= 32.  Returns the loss. */
 float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out,
                                   cleave_buf grad_out, int32_t rows, int32_t feat);
+
+/* ------------------------------------------------------------------ data-parallel step over peer memory
+ * No counterpart in the reference (distribution is "named as a goal but not designed",
+ * doc/hld.md:250).  One kernel per step does what a gradient all-reduce followed by the SGD update
+ * (examples/xor.cleave:67-70 on tensors) would do: every rank owns 1/world of the flat parameter
+ * vector, sums that slice of the gradients over all ranks -- in the NVSwitch when multicast
+ * addresses are given (multimem.ld_reduce), else with plain peer loads in rank order -- applies
+ * w -= lr * (sum / world) and writes the new weights into every rank's parameter buffer.
+ * params_peers / grads_peers / flags_peers: `world` device pointers each, the same symmetric
+ * allocations as seen from this rank (flags: >= 32 zero-initialised uint32 words per rank, used
+ * for the kernel's own bounded cross-GPU barriers).  len: f32 elements, a multiple of 4.
+ * epoch: 1 for the first step, then += 2 per step, identical on every rank.  All ranks must call
+ * it once per step, one process per GPU.  A barrier that times out (2 s) is reported as
+ * CLEAVE_CUDA_ERR_DEVICE_TIMEOUT at the next synchronisation. */
+int32_t cleave_cuda_dp_sgd_allreduce_f32(void* const* params_peers, void* const* grads_peers,
+                                         void* const* flags_peers, void* params_multicast, void* grads_multicast,
+                                         int64_t len, int32_t rank, int32_t world, float lr, uint32_t epoch);
 
 #ifdef __cplusplus
 }

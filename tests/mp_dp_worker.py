@@ -28,10 +28,20 @@ def main():
     dp.use_torch_stream()
     d_in, d_hid, d_out, gb, steps, lr = 64, 256, 32, 512, 6, 0.5
     _, W1, b1, W2, b2, _ = workloads.mlp_inputs(1, d_in, d_hid, d_out)
-    for overlap in (False, True):
-        net = autodiff.MLP2(d_in, d_hid, d_out)
+    n_params = d_in * d_hid + d_hid + d_hid * d_out + d_out
+    for overlap in ("nccl", "nccl-overlap", "fused-p2p", "fused-multimem"):
+        if overlap.startswith("nccl"):
+            net = autodiff.MLP2(d_in, d_hid, d_out)
+            trainer = dp.DataParallel(dp.MLP2Replica(net), overlap=overlap.endswith("overlap"))
+        else:
+            trainer = dp.FusedDataParallel(
+                n_params, lambda p, g: autodiff.MLP2(d_in, d_hid, d_out, params=p, grads=g),
+                multimem=overlap.endswith("multimem"))
+            net = trainer.net
+            if rank == 0:
+                print(f"{overlap}: multimem in use = {trainer.multimem}", flush=True)
         net.load(W1, b1, W2, b2)
-        trainer = dp.DataParallel(dp.MLP2Replica(net), overlap=overlap)
+        dist.barrier()
         for step in range(steps):
             X, T = dp.dp_batch_inputs(gb, rank, world, d_in, d_out, step)
             trainer.step(linalg.Tensor(X), linalg.Tensor(T), lr)
@@ -50,7 +60,9 @@ def main():
         want = np.concatenate([p.ravel() for p in P])
         got = mine.cpu().numpy()
         err = np.max(np.abs(got - want)) / np.max(np.abs(want))
-        assert err <= 1e-5, f"overlap={overlap}: parameters differ from whole-batch training by {err}"
+        assert err <= 1e-5, f"mode={overlap}: parameters differ from whole-batch training by {err}"
+        if rank == 0:
+            print(f"{overlap}: ok, max deviation from whole-batch training {err:.2e}", flush=True)
     # row-block sharded GEMM with B broadcast into local HBM
     m, n, k = 1024, 512, 256
     a, b = workloads.gemm_inputs(m, n, k)

@@ -67,7 +67,7 @@ def test_mse_loss_and_gradient(n):
     assert abs(loss - float(want_loss)) <= abs(float(want_loss) - loss64) + TOL * loss64
 
 
-@pytest.mark.parametrize("rows,feat", [(1, 1), (1000, 16), (5000, 7), (4096, 32), (100003, 16), (1 << 20, 16)])
+@pytest.mark.parametrize("rows,feat", [(1, 1), (1000, 16), (5000, 7), (4096, 32), (100003, 16), (1 << 20, 16), (777, 4), (33333, 8), (65, 32)])
 def test_linreg_step(rows, feat):
     X = workloads.normal(31, rows, feat)
     w_true = workloads.normal(32, feat)
