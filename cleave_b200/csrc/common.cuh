@@ -71,6 +71,15 @@ float read_scalar(const float* dev_scalar);
 float* scalar_slot();
 float wait_scalar();
 
+// ---- optional per-kernel timing -------------------------------------------------------------------
+// Between profile_begin() and profile_end() every profile_mark(true) / profile_mark(false) pair
+// records a CUDA event pair on the launching stream around the kernels in between (the tensor-core
+// GEMM kernel, the linear-regression sweep); profile_end() waits for them and returns the summed
+// duration in milliseconds and the number of pairs.  Outside begin/end the marks cost nothing.
+void profile_begin();
+double profile_end(int* pairs);
+void profile_mark(bool begin);
+
 // ---- launch geometry -------------------------------------------------------------------
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 

@@ -19,7 +19,5 @@ struct GemmArgs {
 bool launch_gemm_exact(const GemmArgs& g);
 bool launch_gemm_3xtf32(const GemmArgs& g);   // false + error if the problem cannot use this path
 bool gemm_3xtf32_supported(const GemmArgs& g);
-void gemm_profile_begin();
-double gemm_profile_end(int* launches);   // total ms of the tensor-core kernels since begin
 
 }  // namespace cleave

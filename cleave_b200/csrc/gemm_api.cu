@@ -78,19 +78,6 @@ cleave_buf cleave_cuda_gemm_batched_f32(cleave_buf a, cleave_buf b, int32_t batc
   return gemm_new(a, b, batch, m, n, k, 0, 0);
 }
 
-void cleave_cuda_profile_begin(void) {
-  ApiLock lock;
-  gemm_profile_begin();
-}
-
-double cleave_cuda_profile_end(int32_t* launches) {
-  ApiLock lock;
-  int n = 0;
-  double ms = gemm_profile_end(&n);
-  if (launches) *launches = n;
-  return ms;
-}
-
 int32_t cleave_cuda_gemm_ex_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n,
                                 int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo, cleave_buf bias,
                                 int32_t act) {

@@ -594,48 +594,6 @@ static bool split_operand(const float* src, float* dst, int batch, int rows, int
   return cuda_ok(cudaGetLastError(), "operand split launch");
 }
 
-// Optional timing of the tensor-core kernel alone (pre-pass excluded): an event pair around each
-// launch on the launching stream, summed by cleave_cuda_profile_end().
-static bool g_profiling = false;
-static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_prof_events;
-static size_t g_prof_used = 0;
-
-static void prof_mark(bool begin) {
-  if (!g_profiling) return;
-  if (begin) {
-    if (g_prof_used == g_prof_events.size()) {
-      cudaEvent_t a, b;
-      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) { cudaGetLastError(); return; }
-      g_prof_events.emplace_back(a, b);
-    }
-    cudaEventRecord(g_prof_events[g_prof_used].first, ctx().stream);
-  } else if (g_prof_used < g_prof_events.size()) {
-    cudaEventRecord(g_prof_events[g_prof_used].second, ctx().stream);
-    ++g_prof_used;
-  }
-}
-
-void gemm_profile_begin() {
-  g_profiling = true;
-  g_prof_used = 0;
-}
-
-double gemm_profile_end(int* launches) {
-  double total = 0.0;
-  g_profiling = false;
-  for (size_t i = 0; i < g_prof_used; ++i) {
-    float ms = 0.f;
-    if (cudaEventSynchronize(g_prof_events[i].second) == cudaSuccess &&
-        cudaEventElapsedTime(&ms, g_prof_events[i].first, g_prof_events[i].second) == cudaSuccess)
-      total += ms;
-    else
-      cudaGetLastError();
-  }
-  if (launches) *launches = (int)g_prof_used;
-  g_prof_used = 0;
-  return total;
-}
-
 template <int BK>
 static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
   using C = Cfg<BK>;
@@ -649,9 +607,9 @@ static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams&
   }
   const int tiles = p.batch * p.mblks * p.nblks;
   const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
-  prof_mark(true);
+  profile_mark(true);
   gemm_3xtf32_kernel<BK><<<grid, kGemmThreads, C::kSmemBytes, ctx().stream>>>(ma, mb, p);
-  prof_mark(false);
+  profile_mark(false);
   count_launch();
   return cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch");
 }

@@ -534,6 +534,7 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
   const float fn = (float)rows;
   cudaStream_t s = ctx().stream;
   float* pp = P ? P->ptr : nullptr;
+  profile_mark(true);
   if (feat == 16 && aligned16(X->ptr))
     linreg_stage1<16><<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials);
   else if (feat == 32 && aligned16(X->ptr))
@@ -545,6 +546,7 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
   else
     linreg_stage1_any<<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, feat, slab, fn, partials);
   linreg_stage2<<<1, 32 * (feat + 1 > 32 ? 32 : feat + 1), 0, s>>>(partials, ctas, feat, fn, G->ptr, out);
+  profile_mark(false);
   count_launch(2);
   float r = NAN;
   if (cuda_ok(cudaGetLastError(), "linreg launch")) r = wait_scalar();

@@ -9,6 +9,7 @@
 #include <mutex>
 #include <unordered_map>
 #include <unordered_set>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -230,6 +231,49 @@ float read_scalar(const float* dev_scalar) {
   return c.scalar_host[0];
 }
 
+static bool g_profiling = false;
+static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_prof_events;
+static size_t g_prof_used = 0;
+
+void profile_mark(bool begin) {
+  if (!g_profiling) return;
+  if (begin) {
+    if (g_prof_used == g_prof_events.size()) {
+      cudaEvent_t a, b;
+      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+      }
+      g_prof_events.emplace_back(a, b);
+    }
+    cudaEventRecord(g_prof_events[g_prof_used].first, g_ctx.stream);
+  } else if (g_prof_used < g_prof_events.size()) {
+    cudaEventRecord(g_prof_events[g_prof_used].second, g_ctx.stream);
+    ++g_prof_used;
+  }
+}
+
+void profile_begin() {
+  g_profiling = true;
+  g_prof_used = 0;
+}
+
+double profile_end(int* pairs) {
+  double total = 0.0;
+  g_profiling = false;
+  for (size_t i = 0; i < g_prof_used; ++i) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(g_prof_events[i].second) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, g_prof_events[i].first, g_prof_events[i].second) == cudaSuccess)
+      total += ms;
+    else
+      cudaGetLastError();
+  }
+  if (pairs) *pairs = (int)g_prof_used;
+  g_prof_used = 0;
+  return total;
+}
+
 float* scalar_slot() { return g_ctx.scalar_dev + 1; }   // slot 0 is read_scalar's copy target
 
 float wait_scalar() {
@@ -307,6 +351,19 @@ void cleave_cuda_trim(void) {
 int64_t cleave_cuda_live_bytes(void) {
   ApiLock lock;
   return g_live_bytes;
+}
+
+void cleave_cuda_profile_begin(void) {
+  ApiLock lock;
+  profile_begin();
+}
+
+double cleave_cuda_profile_end(int32_t* launches) {
+  ApiLock lock;
+  int n = 0;
+  double ms = profile_end(&n);
+  if (launches) *launches = n;
+  return ms;
 }
 
 int64_t cleave_cuda_kernel_launches(void) {

@@ -75,9 +75,10 @@ void cleave_cuda_reset(void);                        /* invalidate every handle,
 void cleave_cuda_trim(void);                         /* return cached device memory to the driver */
 int64_t cleave_cuda_live_bytes(void);                /* bytes held by live handles */
 int64_t cleave_cuda_kernel_launches(void);           /* kernels launched by this library so far */
-/* Measurement aid: between begin and end every tensor-core GEMM kernel launch is bracketed by a
- * CUDA event pair on the launching stream; end waits for them and returns their total duration
- * in milliseconds (operand pre-pass excluded) and, through `launches`, how many there were. */
+/* Measurement aid: between begin and end every tensor-core GEMM kernel launch (operand pre-pass
+ * excluded) and every linear-regression sweep (both of its kernels) is bracketed by a CUDA event
+ * pair on the launching stream; end waits for them and returns their total duration in
+ * milliseconds and, through `launches`, how many pairs there were. */
 void cleave_cuda_profile_begin(void);
 double cleave_cuda_profile_end(int32_t* launches);
 void* cleave_cuda_host_alloc(int64_t bytes);         /* pinned host memory for fast transfers */
