@@ -1,5 +1,5 @@
 """ctypes binding of ``libcleave_cuda.so`` -- the same symbols, argument order and calling
-convention that cleave's ``extern(cleave_cuda_*) fn`` declarations bind (see INTEGRATION.md).
+convention that cleave's ``extern(cleave_cuda_*) fn`` declarations bind.
 
 There is no fallback: if the shared library is missing this module raises at import of the
 library handle, and every compute call fails loudly when no CUDA device is present.
@@ -38,6 +38,9 @@ SIGNATURES = {
     "cleave_cuda_upload_f32": (c_buf, [c_f32p, i64]),
     "cleave_cuda_download_f32": (i64, [c_buf, c_f32p, i64]),
     "cleave_cuda_upload_into_f32": (i32, [c_buf, c_f32p, i64]),
+    "cleave_cuda_upload_async_f32": (i32, [c_buf, c_f32p, i64]),
+    "cleave_cuda_download_async_f32": (i32, [c_buf, c_f32p, i64]),
+    "cleave_cuda_transfers_sync": (i32, []),
     "cleave_cuda_fill_f32": (c_buf, [f32, i64]),
     "cleave_cuda_zeros_f32": (c_buf, [i64]),
     "cleave_cuda_get_f32": (f32, [c_buf, i64]),

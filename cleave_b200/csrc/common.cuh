@@ -16,6 +16,12 @@ struct Buf {
   float* ptr;
   int64_t len;
   int64_t cap_bytes;  // pool block size; 0 for a non-owning view
+  // Asynchronous transfers (copy-engine streams): xfer_ev marks the end of the last such copy
+  // touching this tensor; while xfer_pending the next compute op that uses the handle first makes
+  // the compute stream wait for it.  order_ev is scratch for ordering a copy after compute work.
+  cudaEvent_t xfer_ev;
+  cudaEvent_t order_ev;
+  bool xfer_pending;
 };
 constexpr uint32_t kMagic = 0xC1EA7E5Bu;
 
@@ -57,7 +63,8 @@ struct ApiLock {
 
 // ---- handles and memory ---------------------------------------------------------------
 Buf* new_buf(int64_t len);             // pooled device allocation; nullptr + error on failure
-Buf* as_buf(cleave_buf h, const char* what);   // validates; nullptr + error on failure
+Buf* as_buf(cleave_buf h, const char* what);   // validates, settles a pending async transfer; nullptr + error on failure
+Buf* lookup_buf(cleave_buf h, const char* what);   // validates only
 void release_buf(Buf* b);
 float* scratch_alloc(int64_t bytes);   // pooled scratch (stream-ordered reuse); pair with scratch_free
 void scratch_free(float* p);

@@ -180,13 +180,13 @@ Buf* new_buf(int64_t len) {
   int64_t bs = 0;
   void* p = pool_alloc(len * (int64_t)sizeof(float), &bs);
   if (!p) return nullptr;
-  Buf* b = new Buf{kMagic, (float*)p, len, bs};
+  Buf* b = new Buf{kMagic, (float*)p, len, bs, nullptr, nullptr, false};
   g_live.insert(b);
   g_live_bytes += bs;
   return b;
 }
 
-Buf* as_buf(cleave_buf h, const char* what) {
+Buf* lookup_buf(cleave_buf h, const char* what) {
   Buf* b = (Buf*)h;
   if (!b || g_live.find(b) == g_live.end() || b->magic != kMagic) {
     set_error(CLEAVE_CUDA_ERR_BAD_HANDLE, "%s: not a live tensor handle (%p)", what, (void*)h);
@@ -195,7 +195,23 @@ Buf* as_buf(cleave_buf h, const char* what) {
   return b;
 }
 
+static void settle_transfer(Buf* b) {
+  if (b->xfer_pending) {
+    cudaStreamWaitEvent(g_ctx.stream, b->xfer_ev, 0);   // compute stream continues after the copy
+    b->xfer_pending = false;
+  }
+}
+
+Buf* as_buf(cleave_buf h, const char* what) {
+  Buf* b = lookup_buf(h, what);
+  if (b) settle_transfer(b);
+  return b;
+}
+
 void release_buf(Buf* b) {
+  settle_transfer(b);   // the block returns to the pool in compute-stream order, after any copy in flight
+  if (b->xfer_ev) cudaEventDestroy(b->xfer_ev);
+  if (b->order_ev) cudaEventDestroy(b->order_ev);
   g_live.erase(b);
   if (b->cap_bytes) {
     pool_free(b->ptr, b->cap_bytes);
@@ -449,6 +465,63 @@ int64_t cleave_cuda_download_f32(cleave_buf t, float* host, int64_t len) {
   return len;
 }
 
+// ---- asynchronous transfers on the copy engines ------------------------------------------------
+static cudaStream_t g_h2d_stream = nullptr, g_d2h_stream = nullptr;
+
+static bool transfer_ready(Buf* b) {
+  if (!g_h2d_stream) {
+    if (!cuda_ok(cudaStreamCreateWithFlags(&g_h2d_stream, cudaStreamNonBlocking), "cudaStreamCreate(h2d)")) return false;
+    if (!cuda_ok(cudaStreamCreateWithFlags(&g_d2h_stream, cudaStreamNonBlocking), "cudaStreamCreate(d2h)")) return false;
+  }
+  if (!b->xfer_ev) {
+    if (!cuda_ok(cudaEventCreateWithFlags(&b->xfer_ev, cudaEventDisableTiming), "cudaEventCreate")) return false;
+    if (!cuda_ok(cudaEventCreateWithFlags(&b->order_ev, cudaEventDisableTiming), "cudaEventCreate")) return false;
+  }
+  return true;
+}
+
+// Queues `copy` on `xs` after (a) all compute work queued so far and (b) any earlier async copy
+// touching the same tensor, and leaves the tensor marked so that later compute waits for it.
+static int32_t async_transfer(Buf* b, cudaStream_t xs, void* dst, const void* src, size_t bytes, cudaMemcpyKind kind) {
+  if (!cuda_ok(cudaEventRecord(b->order_ev, g_ctx.stream), "cudaEventRecord")) return -t_err_code;
+  cudaStreamWaitEvent(xs, b->order_ev, 0);
+  if (b->xfer_pending) cudaStreamWaitEvent(xs, b->xfer_ev, 0);
+  if (!cuda_ok(cudaMemcpyAsync(dst, src, bytes, kind, xs), "cudaMemcpyAsync(async transfer)")) return -t_err_code;
+  if (!cuda_ok(cudaEventRecord(b->xfer_ev, xs), "cudaEventRecord")) return -t_err_code;
+  b->xfer_pending = true;
+  return CLEAVE_CUDA_OK;
+}
+
+int32_t cleave_cuda_upload_async_f32(cleave_buf t, const float* pinned_host, int64_t len) {
+  ApiLock lock;
+  Buf* b = lookup_buf(t, "upload_async");
+  if (!b) return -t_err_code;
+  if (!pinned_host || len != b->len)
+    return -set_error(CLEAVE_CUDA_ERR_SHAPE, "upload_async: %lld elements given, tensor has %lld", (long long)len,
+                      (long long)b->len);
+  if (!transfer_ready(b)) return -t_err_code;
+  return async_transfer(b, g_h2d_stream, b->ptr, pinned_host, (size_t)len * sizeof(float), cudaMemcpyHostToDevice);
+}
+
+int32_t cleave_cuda_download_async_f32(cleave_buf t, float* pinned_host, int64_t len) {
+  ApiLock lock;
+  Buf* b = lookup_buf(t, "download_async");
+  if (!b) return -t_err_code;
+  if (!pinned_host || len != b->len)
+    return -set_error(CLEAVE_CUDA_ERR_SHAPE, "download_async: room for %lld elements, tensor has %lld", (long long)len,
+                      (long long)b->len);
+  if (!transfer_ready(b)) return -t_err_code;
+  return async_transfer(b, g_d2h_stream, pinned_host, b->ptr, (size_t)len * sizeof(float), cudaMemcpyDeviceToHost);
+}
+
+int32_t cleave_cuda_transfers_sync(void) {
+  ApiLock lock;
+  if (!g_h2d_stream) return CLEAVE_CUDA_OK;
+  if (!cuda_ok(cudaStreamSynchronize(g_h2d_stream), "cudaStreamSynchronize(h2d)")) return -t_err_code;
+  if (!cuda_ok(cudaStreamSynchronize(g_d2h_stream), "cudaStreamSynchronize(d2h)")) return -t_err_code;
+  return check_device_status() == CLEAVE_CUDA_OK ? CLEAVE_CUDA_OK : -t_err_code;
+}
+
 float cleave_cuda_get_f32(cleave_buf t, int64_t i) {
   ApiLock lock;
   Buf* b = as_buf(t, "get");
@@ -479,7 +552,7 @@ cleave_buf cleave_cuda_wrap_f32(void* device_ptr, int64_t len) {
     return nullptr;
   }
   if (!ensure_init()) return nullptr;
-  Buf* b = new Buf{kMagic, (float*)device_ptr, len, 0};
+  Buf* b = new Buf{kMagic, (float*)device_ptr, len, 0, nullptr, nullptr, false};
   g_live.insert(b);
   return (cleave_buf)b;
 }

@@ -92,6 +92,16 @@ cleave_buf cleave_cuda_alloc_f32(int64_t len);                              /* u
 cleave_buf cleave_cuda_upload_f32(const float* host, int64_t len);          /* [f32; len] -> device */
 int64_t cleave_cuda_download_f32(cleave_buf t, float* host, int64_t len);   /* returns len or <0 */
 int32_t cleave_cuda_upload_into_f32(cleave_buf t, const float* host, int64_t len);
+/* Transfers on the copy engines, overlapping compute.  The host buffer must be pinned
+ * (cleave_cuda_host_alloc) and stay untouched until cleave_cuda_transfers_sync().  An upload is
+ * ordered after all compute queued so far (which may still read the tensor); compute queued later
+ * that uses the SAME handle waits for the copy.  A download is ordered after all compute queued
+ * so far; later compute that writes the tensor waits for it.  Tracking is per handle: views made
+ * with cleave_cuda_wrap_f32 do not inherit it.  To overlap step i's compute with step i+1's
+ * upload, alternate between two tensors and issue the upload before queueing step i. */
+int32_t cleave_cuda_upload_async_f32(cleave_buf t, const float* pinned_host, int64_t len);
+int32_t cleave_cuda_download_async_f32(cleave_buf t, float* pinned_host, int64_t len);
+int32_t cleave_cuda_transfers_sync(void);
 cleave_buf cleave_cuda_fill_f32(float value, int64_t len);
 cleave_buf cleave_cuda_zeros_f32(int64_t len);
 float cleave_cuda_get_f32(cleave_buf t, int64_t flat_index);                /* row-major flat index */
