@@ -425,15 +425,21 @@ def run_dp_mlp(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # The loss of every step is computed on the device; the host reads it back every `log_every`
+    # steps (as a training loop logs), so the queue of kernels is not drained after each step.
+    loss_dev = linalg.Tensor.zero(1)
+    log_every = max(1, args.log_every)
     for _ in range(args.warmup):
-        trainer.step(tX, tT, 1e-3)
+        trainer.step(tX, tT, 1e-3, loss_out=loss_dev)
     barrier()
     launches0 = L.cleave_cuda_kernel_launches()
     sampler = ClockSampler(local) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        loss = trainer.step(tX, tT, 1e-3)
+    for i in range(args.steps):
+        trainer.step(tX, tT, 1e-3, loss_out=loss_dev)
+        if (i + 1) % log_every == 0 or i + 1 == args.steps:
+            loss = loss_dev[0]
     e1.record()
     barrier()
     clocks = sampler.stop() if sampler else None
@@ -454,7 +460,7 @@ def run_dp_mlp(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"2-layer MLP 1024->4096 tanh->1024 sigmoid, MSE, SGD lr 1e-3, global batch "
                                    f"{global_batch} split over {world} rank(s), gradient all-reduce (mean) every step",
-                       "allreduce_bytes_per_step": 4 * nparams, "exchange": mode,
+                       "allreduce_bytes_per_step": 4 * nparams, "exchange": mode, "loss_read_back_every": log_every,
                        "overlap": not args.no_overlap},
             "gpu_launches": int(launches), "clocks": clocks, "loss": loss,
             "replicas_identical": bool(pmin.item() == pmax.item()),
@@ -479,6 +485,7 @@ def main():
     ap.add_argument("--max-size", type=int, default=0, help="gemm_sweep: skip shapes with a dimension above this")
     ap.add_argument("--global-batch", type=int, default=32768)
     ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--log-every", type=int, default=10, help="dp_mlp: read the loss back every this many steps")
     ap.add_argument("--dp-mode", default="fused", choices=["fused", "fused_p2p", "nccl"],
                     help="dp_mlp: gradient exchange as one multimem kernel, one peer-load kernel, or NCCL + SGD")
     ap.add_argument("--size", type=int, default=8192,

@@ -74,6 +74,7 @@ SIGNATURES = {
     "cleave_cuda_bias_act_f32": (c_buf, [c_buf, c_buf, i32, i32, i32]),
     "cleave_cuda_mse_f32": (f32, [c_buf, c_buf, c_buf]),
     "cleave_cuda_mse_act_bwd_f32": (f32, [c_buf, c_buf, c_buf, i32]),
+    "cleave_cuda_mse_act_bwd_dev_f32": (i32, [c_buf, c_buf, c_buf, i32, c_buf]),
     "cleave_cuda_sgd_f32": (i32, [c_buf, c_buf, f32, f32]),
     "cleave_cuda_dp_sgd_allreduce_f32": (i32, [ctypes.POINTER(ctypes.c_void_p)] * 3 + [ctypes.c_void_p, ctypes.c_void_p,
                                                 i64, i32, i32, f32, ctypes.c_uint32]),

@@ -77,12 +77,14 @@ class MLP2:
         Y = gemm_into(Tensor.empty(batch, self.d_out), H, self.W2, bias=self.b2, act=self.act2)
         return H, Y
 
-    def forward_backward(self, X: Tensor, T: Tensor, keep: bool = False, on_grads_ready=None):
+    def forward_backward(self, X: Tensor, T: Tensor, keep: bool = False, on_grads_ready=None,
+                         loss_out: Tensor | None = None):
         """One forward + backward pass; gradients land in ``self.grads``.  Returns the loss
         (and, with ``keep``, the intermediates for inspection).  ``on_grads_ready(i)`` is called
-        when a gradient bucket is final: 0 = [dW2 | db2], 1 = [dW1 | db1]."""
+        when a gradient bucket is final: 0 = [dW2 | db2], 1 = [dW1 | db1].  With ``loss_out`` (a
+        one-element tensor) the loss is left on the device, nothing waits and ``None`` is returned."""
         H, Y = self.forward(X)
-        loss, dZ2 = nn.mse_act_bwd(Y, T, self.act2)   # dY and act2'(Y) * dY in one pass
+        loss, dZ2 = nn.mse_act_bwd(Y, T, self.act2, loss_out)   # dY and act2'(Y) * dY in one pass
         gemm_into(self.dW2, H, dZ2, trans_a=True)            # H^T dZ2
         self._colsum_into(self.db2, dZ2)
         if on_grads_ready:

@@ -342,9 +342,31 @@ __global__ void __launch_bounds__(1024) linreg_stage2(const float* __restrict__ 
 
 // ---- host side -------------------------------------------------------------------------------
 // Slab size (elements per first-stage CTA): at least 4096 elements, a multiple of 4, and no
-// more than kMaxPartials CTAs.  A pure function of n, so the summation tree is reproducible.
-static void slab_for(int64_t n, int64_t* slab, int* ctas) {
-  int64_t s = (n + kMaxPartials - 1) / kMaxPartials;
+// more CTAs than can be resident at once for the kernel in question (one wave: a second,
+// partial wave would cost as much as the first).  A function of n and of the device model only,
+// so the summation tree is reproducible.
+template <class Kernel>
+static int resident_ctas(Kernel kernel) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRThreads, 0) != cudaSuccess || per_sm < 1) {
+    cudaGetLastError();
+    per_sm = 1;
+  }
+  int sms = ctx().sm_count;
+  if (sms <= 0) {   // allocation-free entry point used before the library context exists
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+      cudaGetLastError();
+      sms = 1;
+    }
+  }
+  int64_t c = (int64_t)per_sm * sms;
+  return (int)(c < kMaxPartials ? c : kMaxPartials);
+}
+
+static void slab_for(int64_t n, int max_ctas, int64_t* slab, int* ctas) {
+  int64_t s = (n + max_ctas - 1) / max_ctas;
   if (s < 4096) s = 4096;
   s = (s + 3) / 4 * 4;
   *slab = s;
@@ -363,7 +385,8 @@ static float reduce_scalar(const float* v, int64_t n, int64_t first, float divis
   int ctas = 0;
   if (cnt > 0) {
     int64_t slab;
-    slab_for(cnt, &slab, &ctas);
+    static const int max_ctas = resident_ctas(reduce_stage1<R>);
+    slab_for(cnt, max_ctas, &slab, &ctas);
     int vec = aligned16(base) ? 1 : 0;
     reduce_stage1<R><<<ctas, kRThreads, 0, s>>>(base, cnt, slab, partials, vec);
     count_launch();
@@ -452,8 +475,20 @@ int32_t cleave_cuda_colsum_into_f32(cleave_buf out, cleave_buf x, int32_t rows, 
   return colsum_launch(a->ptr, o->ptr, rows, cols) ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
 }
 
-static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, const char* name) {
+// loss_dev == nullptr: the loss is returned (the call waits for it).  Otherwise it is written to
+// that one-element device tensor, nothing is waited for, and 0 is returned on success.
+static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, const char* name,
+                      cleave_buf loss_dev = nullptr) {
   ApiLock lock;
+  Buf* lo = nullptr;
+  if (loss_dev) {
+    lo = as_buf(loss_dev, name);
+    if (!lo) return NAN;
+    if (lo->len != 1) {
+      set_error(CLEAVE_CUDA_ERR_SHAPE, "%s: the loss output must be a one-element tensor", name);
+      return NAN;
+    }
+  }
   Buf* a = as_buf(p, name);
   Buf* b = as_buf(t, name);
   if (!a || !b) return NAN;
@@ -476,22 +511,32 @@ static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, co
   if (!partials) return NAN;
   int64_t slab;
   int ctas;
-  slab_for(n, &slab, &ctas);
+  static const int max_ctas = resident_ctas(mse_stage1);
+  slab_for(n, max_ctas, &slab, &ctas);
   int vec = (aligned16(a->ptr) && aligned16(b->ptr) && (!d || aligned16(d->ptr))) ? 1 : 0;
   const float fn = (float)(int32_t)n;
   cudaStream_t s = ctx().stream;
-  float* out = scalar_slot();
+  float* out = lo ? lo->ptr : scalar_slot();
   mse_stage1<<<ctas, kRThreads, 0, s>>>(a->ptr, b->ptr, d ? d->ptr : nullptr, n, slab, fn, partials, vec, bwd_act);
   reduce_stage2<SumRed><<<1, kRThreads, 0, s>>>(partials, ctas, out, fn, 0, nullptr);
   count_launch(2);
   float r = NAN;
-  if (cuda_ok(cudaGetLastError(), "mse launch")) r = wait_scalar();
+  if (cuda_ok(cudaGetLastError(), "mse launch")) r = lo ? 0.0f : wait_scalar();
   scratch_free(partials);
   return r;
 }
 
 float cleave_cuda_mse_f32(cleave_buf p, cleave_buf t, cleave_buf dp) {
   return mse_impl(p, t, dp, CLEAVE_ACT_IDENTITY, "mse");
+}
+
+int32_t cleave_cuda_mse_act_bwd_dev_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act, cleave_buf loss_out) {
+  if (!dz || !loss_out) {
+    ApiLock lock;
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "mse_act_bwd_dev: the gradient and loss output handles are required");
+  }
+  float r = mse_impl(y, t, dz, act, "mse_act_bwd_dev", loss_out);
+  return r == 0.0f ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
 }
 
 float cleave_cuda_mse_act_bwd_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act) {
@@ -524,9 +569,18 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
     set_error(CLEAVE_CUDA_ERR_SHAPE, "linreg_step: operand lengths do not match rows=%d feat=%d", rows, feat);
     return NAN;
   }
-  // Row slabs: a function of rows only.  At least 1024 rows per CTA.
-  int64_t slab = ((int64_t)rows + kMaxPartials - 1) / kMaxPartials;
+  // Row slabs: one resident wave of CTAs, at least 1024 rows each, a multiple of 256 rows (8 warps x 32).
+  int max_ctas;
+  switch (feat) {
+    case 4: max_ctas = resident_ctas(linreg_stage1<4>); break;
+    case 8: max_ctas = resident_ctas(linreg_stage1<8>); break;
+    case 16: max_ctas = resident_ctas(linreg_stage1<16>); break;
+    case 32: max_ctas = resident_ctas(linreg_stage1<32>); break;
+    default: max_ctas = resident_ctas(linreg_stage1_any); break;
+  }
+  int64_t slab = ((int64_t)rows + max_ctas - 1) / max_ctas;
   if (slab < 1024) slab = 1024;
+  slab = (slab + 255) / 256 * 256;
   int ctas = (int)(((int64_t)rows + slab - 1) / slab);
   float* partials = scratch_alloc(((int64_t)ctas * (feat + 1) + 4) * sizeof(float));
   if (!partials) return NAN;
@@ -618,7 +672,9 @@ extern "C" int32_t cleave_cuda_sum_noalloc_f32(const float* x_dev, int64_t len, 
   // to be cleared first.
   int64_t slab;
   int ctas;
-  slab_for(len, &slab, &ctas);
+  // The occupancy query reads kernel attributes only; it allocates nothing.
+  static const int max_ctas = resident_ctas(reduce_stage1<SumRed>);
+  slab_for(len, max_ctas, &slab, &ctas);
   reduce_stage1<SumRed><<<ctas, kRThreads, 0, s>>>(x_dev, len, slab, scratch, aligned16(x_dev) ? 1 : 0);
   reduce_stage2<SumRed><<<1, kRThreads, 0, s>>>(scratch, ctas, out_dev, 1.0f, 0, nullptr);
   count_launch(2);

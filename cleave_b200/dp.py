@@ -86,7 +86,7 @@ class DataParallel:
         self._dist = dist
         self._buckets = replica.grad_buckets()
 
-    def step(self, X, T, lr: float):
+    def step(self, X, T, lr: float, loss_out=None):
         dist, pending = self._dist, []
 
         def on_ready(i: int) -> None:
@@ -95,7 +95,7 @@ class DataParallel:
                 pending.append(dist.all_reduce(self._buckets[i], op=dist.ReduceOp.SUM, group=self.group,
                                                async_op=True))
 
-        loss = self.replica.forward_backward(X, T, on_grads_ready=on_ready)
+        loss = self.replica.forward_backward(X, T, on_grads_ready=on_ready, loss_out=loss_out)
         if self.world > 1 and not self.overlap:
             for b in self._buckets:
                 dist.all_reduce(b, op=dist.ReduceOp.SUM, group=self.group)
@@ -149,9 +149,10 @@ class FusedDataParallel:
         self.net = make_net(self.params, self.grads)
         self.epoch = 1
 
-    def step(self, X, T, lr: float):
+    def step(self, X, T, lr: float, loss_out=None):
+        """``loss_out``: optional one-element device tensor; with it the step never waits for the GPU."""
         from ._lib import lib, raise_last_error
-        loss = self.net.forward_backward(X, T)
+        loss = self.net.forward_backward(X, T, loss_out=loss_out)
         rc = lib().cleave_cuda_dp_sgd_allreduce_f32(self._tables[0], self._tables[1], self._tables[2], self._mc[0],
                                                     self._mc[1], self.n_params, self.rank, self.world, float(lr),
                                                     self.epoch)
@@ -173,8 +174,8 @@ class MLP2Replica:
     def grad_buckets(self):
         return self._buckets
 
-    def forward_backward(self, X, T, on_grads_ready=None):
-        return self.net.forward_backward(X, T, on_grads_ready=on_grads_ready)
+    def forward_backward(self, X, T, on_grads_ready=None, loss_out=None):
+        return self.net.forward_backward(X, T, on_grads_ready=on_grads_ready, loss_out=loss_out)
 
     def sgd(self, lr, gscale):
         self.net.sgd(lr, gscale)

@@ -87,12 +87,18 @@ def mse(pred: Tensor, target: Tensor, want_grad: bool = True):
     return (loss, d) if want_grad else loss
 
 
-def mse_act_bwd(y: Tensor, target: Tensor, act: str):
+def mse_act_bwd(y: Tensor, target: Tensor, act: str, loss_out: Tensor | None = None):
     """Loss ``mean((y - target)^2)`` for ``y = act(z)`` and the gradient with respect to ``z``
-    (``act'(y) * 2 (y - target) / numel``) in one pass; equals ``mse`` followed by ``*_bwd``."""
+    (``act'(y) * 2 (y - target) / numel``) in one pass; equals ``mse`` followed by ``*_bwd``.
+    With ``loss_out`` (a one-element tensor) the loss stays on the device, the call does not wait
+    and the returned loss is ``None``."""
     if y.dims != target.dims:
         raise TypeError(f"mse_act_bwd: mismatched types {y!r} and {target!r}")
     dz = Tensor.empty(*y.dims)
+    if loss_out is not None:
+        if lib().cleave_cuda_mse_act_bwd_dev_f32(y._h, target._h, dz._h, ACT[act], loss_out._h) != 0:
+            raise_last_error("mse_act_bwd_dev")
+        return None, dz
     loss = lib().cleave_cuda_mse_act_bwd_f32(y._h, target._h, dz._h, ACT[act])
     if math.isnan(loss) and lib().cleave_cuda_last_error():
         raise_last_error("mse_act_bwd")

@@ -192,6 +192,9 @@ float cleave_cuda_mse_f32(cleave_buf p, cleave_buf t, cleave_buf dp);
  * act'(y) * 2*(y - t)/len, the gradient with respect to the PRE-activation z, in one pass
  * (mse followed by sigmoid_bwd / tanh_bwd, bit for bit).  act: identity, sigmoid or tanh. */
 float cleave_cuda_mse_act_bwd_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act);
+/* Same, but the loss goes to the one-element tensor loss_out and the call does not wait: a
+ * training loop can queue many steps and read the loss only when it wants to log it. */
+int32_t cleave_cuda_mse_act_bwd_dev_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act, cleave_buf loss_out);
 /* w = w - lr * (gscale * g) in place (examples/xor.cleave:67-70); gscale folds the 1/G of a
  * gradient mean over G data-parallel ranks into the same pass. */
 int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale);

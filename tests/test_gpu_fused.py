@@ -33,3 +33,16 @@ def test_mse_act_bwd_rejects_relu():
     y = linalg.Tensor(np.ones(4, f32))
     with pytest.raises(cb.CleaveCudaError):
         nn.mse_act_bwd(y, y, "relu")
+
+
+def test_device_resident_loss_equals_the_returned_loss():
+    rng = np.random.default_rng(3)
+    y = rng.uniform(0, 1, 50001).astype(f32)
+    t = rng.uniform(0, 1, 50001).astype(f32)
+    ty, tt = linalg.Tensor(y), linalg.Tensor(t)
+    loss, dz = nn.mse_act_bwd(ty, tt, "sigmoid")
+    out = linalg.Tensor.zero(1)
+    none, dz2 = nn.mse_act_bwd(ty, tt, "sigmoid", loss_out=out)
+    assert none is None
+    assert out[0] == loss
+    assert np.array_equal(dz.numpy(), dz2.numpy())
