@@ -49,12 +49,55 @@ __device__ __forceinline__ float block_reduce(float v) {
   return v;
 }
 
-// Stage 1: each CTA owns a contiguous slab of the input (so partial b covers elements
-// [b*slab, (b+1)*slab)), reads it as float4 with four loads in flight per thread.
-// Elements are taken from index `first` on (max_of starts its scan at element 1).
+// What the last CTA of a reduction does with the per-CTA partials: thread t folds partials
+// t, t+256, ... in ascending order, then a block tree.
+// mode 0: out = total / divisor (divisor 1 skips the division).
+// mode 1 (max_of): out = (total > first) ? total : first.
+struct Finish {
+  float* out;
+  float divisor;
+  int mode;
+  const float* first;
+  unsigned int* done;   // completion counter of this launch family: zero between launches
+};
+
+// Publishes partials[blockIdx.x] = value (thread 0's) and tells, in every thread, whether this CTA
+// is the last of the grid to do so.  The last CTA re-arms the counter for the next launch.
+__device__ __forceinline__ bool publish_and_check_last(float* partials, float value, unsigned int* done) {
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = value;
+    __threadfence();
+    const unsigned int prev = atomicAdd(done, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) *done = 0;
+  }
+  __syncthreads();
+  if (s_last) __threadfence();
+  return s_last != 0;
+}
+
 template <class R>
-__global__ void __launch_bounds__(kRThreads) reduce_stage1(const float* __restrict__ v, int64_t n, int64_t slab,
-                                                           float* __restrict__ partials, int vec) {
+__device__ __forceinline__ void finish_reduction(const float* partials, int count, const Finish& f) {
+  float acc = R::identity();
+  for (int i = threadIdx.x; i < count; i += kRThreads) acc = R::combine(acc, __ldcg(partials + i));
+  acc = block_reduce<R>(acc);
+  if (threadIdx.x == 0) {
+    if (f.mode == 0) {
+      f.out[0] = f.divisor == 1.0f ? acc : __fdiv_rn(acc, f.divisor);
+    } else {
+      const float v0 = f.first[0];
+      f.out[0] = acc > v0 ? acc : v0;
+    }
+  }
+}
+
+// One launch per reduction.  Each CTA owns a contiguous slab of the input (partial b covers
+// elements [b*slab, (b+1)*slab)) and reads it as float4; the last CTA to finish combines the
+// partials in index order, so the result does not depend on the order in which CTAs ran.
+template <class R>
+__global__ void __launch_bounds__(kRThreads) reduce_kernel(const float* __restrict__ v, int64_t n, int64_t slab,
+                                                           float* __restrict__ partials, int vec, Finish fin) {
   const int64_t lo = (int64_t)blockIdx.x * slab;
   int64_t hi = lo + slab;
   if (hi > n) hi = n;
@@ -75,27 +118,11 @@ __global__ void __launch_bounds__(kRThreads) reduce_stage1(const float* __restri
   }
   float t = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
   t = block_reduce<R>(t);
-  if (threadIdx.x == 0) partials[blockIdx.x] = t;
+  if (publish_and_check_last(partials, t, fin.done)) finish_reduction<R>(partials, gridDim.x, fin);
 }
 
-// Stage 2: one CTA; thread t folds partials t, t+256, ... in ascending order, then a block tree.
-// mode 0: out = total * scale.  mode 1 (max_of): out = (total > first) ? total : first.
-template <class R>
-__global__ void __launch_bounds__(kRThreads) reduce_stage2(const float* __restrict__ partials, int count,
-                                                           float* __restrict__ out, float scale_or_unused, int mode,
-                                                           const float* __restrict__ first) {
-  float acc = R::identity();
-  for (int i = threadIdx.x; i < count; i += kRThreads) acc = R::combine(acc, partials[i]);
-  acc = block_reduce<R>(acc);
-  if (threadIdx.x == 0) {
-    if (mode == 0) {
-      out[0] = scale_or_unused == 1.0f ? acc : __fdiv_rn(acc, scale_or_unused);
-    } else {
-      float f = first[0];
-      out[0] = acc > f ? acc : f;
-    }
-  }
-}
+// Completion counters of the pooled entry points (one reduction runs at a time: single stream).
+static __device__ unsigned int g_reduce_done = 0;
 
 // ---- column sums: x[rows, cols] -> out[cols] ------------------------------------------------
 // grid = (column strips of 128 floats, row splits).  Thread (tx, ty) owns one float4 column
@@ -169,7 +196,8 @@ __device__ __forceinline__ float mse_grad(float p, float e, float fn, int bwd_ac
 
 __global__ void __launch_bounds__(kRThreads) mse_stage1(const float* __restrict__ p, const float* __restrict__ t,
                                                         float* __restrict__ dp, int64_t n, int64_t slab, float fn,
-                                                        float* __restrict__ partials, int vec, int bwd_act) {
+                                                        float* __restrict__ partials, int vec, int bwd_act,
+                                                        Finish fin) {
   const int64_t lo = (int64_t)blockIdx.x * slab;
   int64_t hi = lo + slab;
   if (hi > n) hi = n;
@@ -204,7 +232,7 @@ __global__ void __launch_bounds__(kRThreads) mse_stage1(const float* __restrict_
     }
   }
   acc = block_reduce<SumRed>(acc);
-  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+  if (publish_and_check_last(partials, acc, fin.done)) finish_reduction<SumRed>(partials, gridDim.x, fin);
 }
 
 // ---- linear-regression step: one sweep over X[rows, feat] ------------------------------------
@@ -213,21 +241,96 @@ __global__ void __launch_bounds__(kRThreads) mse_stage1(const float* __restrict_
 // X[i,f] * (2 e / rows) per feature.  Per-CTA partials: [feat] gradient sums, then the loss sum.
 constexpr int kMaxFeat = 32;
 
+// Completion counter of the linear-regression sweep: the last CTA to finish folds the per-CTA
+// partials (second stage) in the same launch.  One sweep runs at a time (single stream).
+static __device__ unsigned int g_linreg_done = 0;
+
+// Second stage, run by the last CTA to finish.  Everything else has drained by then, so its
+// latency is pure tail: all 256 threads first pull their share of every quantity's partials with
+// batches of independent 16-byte loads (thread t owns partials 4t .. 4t+3, then 4t+1024 .., of
+// each quantity, added in ascending order) into scratch[q][t]; then warp w finishes quantities
+// w, w+8, ...: lane l adds scratch[q][l], scratch[q][l+32], ... in ascending order and a fixed
+// shuffle tree combines the lanes.  partials[q] starts at q * pitch, pitch a multiple of 4.
+// The order depends only on the number of CTAs, never on which CTA finished last.
+// NQ = feat + 1 quantities (gradient components, then the loss); scratch holds NQ * 256 floats.
+template <int NQ_MAX>
+__device__ __forceinline__ void linreg_fold(const float* partials, int pitch, int ctas, int feat, float fn,
+                                            float* grad, float* loss_out, float* scratch) {
+  const int t = threadIdx.x, lane = t & 31, nwarps = blockDim.x >> 5;
+  constexpr int kBatch = 9;   // 16-byte loads in flight per thread
+  for (int q0 = 0; q0 < NQ_MAX; q0 += kBatch) {
+    float acc[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) acc[j] = 0.0f;
+    for (int c0 = 4 * t; c0 < ctas; c0 += 4 * kRThreads) {
+      float4 v[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j)
+        v[j] = (q0 + j <= feat) ? __ldcg(reinterpret_cast<const float4*>(partials + (int64_t)(q0 + j) * pitch + c0))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        acc[j] = __fadd_rn(acc[j], v[j].x);
+        if (c0 + 1 < ctas) acc[j] = __fadd_rn(acc[j], v[j].y);
+        if (c0 + 2 < ctas) acc[j] = __fadd_rn(acc[j], v[j].z);
+        if (c0 + 3 < ctas) acc[j] = __fadd_rn(acc[j], v[j].w);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j)
+      if (q0 + j <= feat) scratch[(q0 + j) * kRThreads + t] = acc[j];
+  }
+  __syncthreads();
+  for (int q = t >> 5; q <= feat; q += nwarps) {
+    const float* row = scratch + q * kRThreads;
+    float acc = row[lane];
+#pragma unroll
+    for (int j = 1; j < kRThreads / 32; ++j) acc = __fadd_rn(acc, row[lane + 32 * j]);
+    acc = warp_reduce<SumRed>(acc);
+    if (lane == 0) {
+      if (q < feat) grad[q] = acc;
+      else loss_out[0] = __fdiv_rn(acc, fn);
+    }
+  }
+}
+
+// Publishes this CTA's partials and returns true in exactly one CTA: the last one to arrive.
+__device__ __forceinline__ bool linreg_arrive_last() {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(&g_linreg_done, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) g_linreg_done = 0;   // ready for the next launch
+  }
+  __syncthreads();
+  if (s_last) __threadfence();
+  return s_last != 0;
+}
+
+constexpr int kLrStages = 3;   // row groups in flight per warp (cp.async ring)
+
 template <int FEAT>
-__global__ void __launch_bounds__(kRThreads) linreg_stage1(const float* __restrict__ X, const float* __restrict__ y,
+__global__ void __launch_bounds__(kRThreads, FEAT <= 16 ? 4 : 2) linreg_stage1(const float* __restrict__ X, const float* __restrict__ y,
                                                            const float* __restrict__ w, float* __restrict__ pred,
                                                            int64_t rows, int64_t slab, float fn,
-                                                           float* __restrict__ partials) {
+                                                           float* __restrict__ partials, float* __restrict__ grad,
+                                                           float* __restrict__ loss_out) {
   // Each warp takes 32 consecutive rows at a time.  The 32*FEAT floats of such a group are
-  // contiguous in X, so the warp reads them with fully coalesced 16-byte loads (lane l takes
-  // 16-byte words l, l+32, ...), parks them in a warp-private shared tile and every lane then
-  // picks up ITS row.  Words of row r are stored at slot q ^ swz(r), which makes both the
-  // coalesced writes and the row-wise 16-byte reads bank-conflict free.
+  // contiguous in X, so the warp fetches them with fully coalesced 16-byte asynchronous copies
+  // (cp.async, lane l takes 16-byte words l, l+32, ...) straight into a warp-private ring of
+  // kLrStages shared tiles -- several groups are in flight per warp without holding registers --
+  // and every lane then picks up ITS row.  Words of row r land at slot q ^ swz(r), which makes both
+  // the copies and the row-wise 16-byte reads bank-conflict free.
   static_assert(FEAT % 4 == 0 && FEAT >= 4 && FEAT <= 32, "FEAT must be 4, 8, 16 or 32");
   constexpr int Q = FEAT / 4;                 // 16-byte words per row
+  const int pitch = (gridDim.x + 3) & ~3;     // row pitch of partials[quantity][cta]
   constexpr int kRowsPerSwz = Q >= 8 ? 1 : 8 / Q;
-  __shared__ float sw[FEAT];
-  __shared__ float4 tile[kRWarps][32 * Q];
+  extern __shared__ __align__(16) unsigned char lr_smem[];
+  float4* tile = reinterpret_cast<float4*>(lr_smem);                       // [kRWarps][kLrStages][32 * Q]
+  float* sw = reinterpret_cast<float*>(tile + kRWarps * kLrStages * 32 * Q);   // [FEAT]
+  float* red = sw + FEAT;                                                  // [kRWarps][FEAT + 1]
   if (threadIdx.x < FEAT) sw[threadIdx.x] = w[threadIdx.x];
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -238,58 +341,95 @@ __global__ void __launch_bounds__(kRThreads) linreg_stage1(const float* __restri
 #pragma unroll
   for (int f = 0; f < FEAT; ++f) g[f] = 0.0f;
   float loss = 0.0f;
-  float4* my_tile = tile[warp];
+  float4* my_ring = tile + (size_t)warp * kLrStages * 32 * Q;
   const int my_swz = (lane / kRowsPerSwz) & (Q - 1);
-  for (int64_t r0 = lo + (int64_t)warp * 32; r0 < hi; r0 += (int64_t)kRWarps * 32) {
-    const float4* src = reinterpret_cast<const float4*>(X + r0 * FEAT);
-    float4 v[Q];
+  constexpr int64_t kStep = (int64_t)kRWarps * 32;
+  const float two_over_n = __fdiv_rn(2.0f, fn);
+
+  // Queue the copies of one row group into ring stage `stage` (rows past the slab end are zeroed).
+  auto issue = [&](int stage, int64_t r0) {
+    if (r0 < hi) {
+      const float4* src = reinterpret_cast<const float4*>(X + r0 * FEAT);
+      float4* dst = my_ring + stage * 32 * Q;
 #pragma unroll
-    for (int i = 0; i < Q; ++i) {
-      const int idx = lane + 32 * i;
-      v[i] = (r0 + idx / Q < hi) ? __ldcs(src + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < Q; ++k) {
+        const int idx = lane + 32 * k;
+        const int r = idx / Q, q = idx % Q;
+        float4* d = dst + r * Q + (q ^ ((r / kRowsPerSwz) & (Q - 1)));
+        if (r0 + r < hi) {
+          const unsigned sa = (unsigned)__cvta_generic_to_shared(d);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src + idx) : "memory");
+        } else {
+          *d = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call, possibly empty
+  };
+
+  const int64_t first = lo + (int64_t)warp * 32;
 #pragma unroll
-    for (int i = 0; i < Q; ++i) {
-      const int idx = lane + 32 * i;
-      const int r = idx / Q, q = idx % Q;
-      my_tile[r * Q + (q ^ ((r / kRowsPerSwz) & (Q - 1)))] = v[i];
-    }
+  for (int s = 0; s < kLrStages - 1; ++s) issue(s, first + s * kStep);
+  int stage = 0;
+  for (int64_t r0 = first; r0 < hi; r0 += kStep) {
+    issue((stage + kLrStages - 1) % kLrStages, r0 + (kLrStages - 1) * kStep);
+    const int64_t i = r0 + lane;
+    const float yi = i < hi ? __ldcs(y + i) : 0.0f;
+    asm volatile("cp.async.wait_group %0;" ::"n"(kLrStages - 1) : "memory");
     __syncwarp();
     float xr[FEAT];
+    const float4* cur = my_ring + stage * 32 * Q;
 #pragma unroll
     for (int q = 0; q < Q; ++q) {
-      const float4 t = my_tile[lane * Q + (q ^ my_swz)];
+      const float4 t = cur[lane * Q + (q ^ my_swz)];
       xr[4 * q] = t.x; xr[4 * q + 1] = t.y; xr[4 * q + 2] = t.z; xr[4 * q + 3] = t.w;
     }
-    __syncwarp();
-    const int64_t i = r0 + lane;
+    __syncwarp();   // every lane has its row: the stage may be refilled by the next iteration
     if (i < hi) {
       float acc = 0.0f;
 #pragma unroll
       for (int f = 0; f < FEAT; ++f) acc = __fadd_rn(acc, __fmul_rn(xr[f], sw[f]));
       if (pred) pred[i] = acc;
-      const float e = __fsub_rn(acc, __ldcs(y + i));
+      const float e = __fsub_rn(acc, yi);
       loss = __fadd_rn(loss, __fmul_rn(e, e));
-      const float d = __fdiv_rn(__fmul_rn(2.0f, e), fn);
+      // Gradient terms x * (2 e / n): summed in a tree anyway, so fused multiply-adds are used
+      // here (one rounding per term instead of two); only pred has to match the reference's chain.
+      const float d = __fmul_rn(e, two_over_n);
 #pragma unroll
-      for (int f = 0; f < FEAT; ++f) g[f] = __fadd_rn(g[f], __fmul_rn(xr[f], d));
+      for (int f = 0; f < FEAT; ++f) g[f] = fmaf(xr[f], d, g[f]);
     }
+    stage = (stage + 1) % kLrStages;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  // CTA reduction with one barrier: shuffle tree inside each warp, then warps 0..7 in order.
 #pragma unroll
   for (int f = 0; f < FEAT; ++f) {
-    float t = block_reduce<SumRed>(g[f]);
-    if (threadIdx.x == 0) partials[(int64_t)f * gridDim.x + blockIdx.x] = t;
+    const float t = warp_reduce<SumRed>(g[f]);
+    if (lane == 0) red[warp * (FEAT + 1) + f] = t;
   }
-  loss = block_reduce<SumRed>(loss);
-  if (threadIdx.x == 0) partials[(int64_t)FEAT * gridDim.x + blockIdx.x] = loss;
+  {
+    const float t = warp_reduce<SumRed>(loss);
+    if (lane == 0) red[warp * (FEAT + 1) + FEAT] = t;
+  }
+  __syncthreads();
+  if (threadIdx.x <= FEAT) {
+    float t = red[threadIdx.x];
+#pragma unroll
+    for (int wv = 1; wv < kRWarps; ++wv) t = __fadd_rn(t, red[wv * (FEAT + 1) + threadIdx.x]);
+    partials[(int64_t)threadIdx.x * pitch + blockIdx.x] = t;
+  }
+  // the ring is idle now (all copies were waited for): reuse it as the fold's scratch
+  if (linreg_arrive_last()) linreg_fold<FEAT + 1>(partials, pitch, gridDim.x, FEAT, fn, grad, loss_out, reinterpret_cast<float*>(lr_smem));
 }
 
 // Generic-feat fallback (feat <= 32, any value): same arithmetic, runtime loops.
 __global__ void __launch_bounds__(kRThreads) linreg_stage1_any(const float* __restrict__ X, const float* __restrict__ y,
                                                                const float* __restrict__ w, float* __restrict__ pred,
                                                                int64_t rows, int feat, int64_t slab, float fn,
-                                                               float* __restrict__ partials) {
+                                                               float* __restrict__ partials, float* __restrict__ grad,
+                                                               float* __restrict__ loss_out) {
   __shared__ float sw[kMaxFeat];
+  const int pitch = (gridDim.x + 3) & ~3;
   if (threadIdx.x < feat) sw[threadIdx.x] = w[threadIdx.x];
   __syncthreads();
   const int64_t lo = (int64_t)blockIdx.x * slab;
@@ -314,30 +454,21 @@ __global__ void __launch_bounds__(kRThreads) linreg_stage1_any(const float* __re
   for (int f = 0; f < kMaxFeat; ++f) {
     if (f < feat) {   // uniform across the block
       float t = block_reduce<SumRed>(g[f]);
-      if (threadIdx.x == 0) partials[(int64_t)f * gridDim.x + blockIdx.x] = t;
+      if (threadIdx.x == 0) partials[(int64_t)f * pitch + blockIdx.x] = t;
     }
   }
   loss = block_reduce<SumRed>(loss);
-  if (threadIdx.x == 0) partials[(int64_t)feat * gridDim.x + blockIdx.x] = loss;
+  if (threadIdx.x == 0) partials[(int64_t)feat * pitch + blockIdx.x] = loss;
+  __shared__ float fold_scratch[(kMaxFeat + 1) * kRThreads];
+  if (linreg_arrive_last()) linreg_fold<kMaxFeat + 1>(partials, pitch, gridDim.x, feat, fn, grad, loss_out, fold_scratch);
 }
 
-// Stage 2: one warp per quantity (feat gradient components, then the loss).  The partials of
-// quantity f are contiguous (partials[f][cta]); lane l folds entries l, l+32, ... in ascending
-// order and the 32 lane sums are combined by a fixed shuffle tree: deterministic.
-// grad[0..feat) = gradient, loss_out[0] = loss sum / rows.
-__global__ void __launch_bounds__(1024) linreg_stage2(const float* __restrict__ partials, int ctas, int feat, float fn,
-                                                     float* __restrict__ grad, float* __restrict__ loss_out) {
-  const int lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int f = threadIdx.x >> 5; f <= feat; f += nwarps) {
-    const float* col = partials + (int64_t)f * ctas;
-    float acc = 0.0f;
-    for (int b = lane; b < ctas; b += 32) acc = __fadd_rn(acc, col[b]);
-    acc = warp_reduce<SumRed>(acc);
-    if (lane == 0) {
-      if (f < feat) grad[f] = acc;
-      else loss_out[0] = __fdiv_rn(acc, fn);
-    }
-  }
+static size_t linreg_smem_bytes(int feat) {
+  const int q = feat / 4;
+  size_t ring = (size_t)kRWarps * kLrStages * 32 * q * sizeof(float4);
+  const size_t fold = (size_t)(feat + 1) * kRThreads * sizeof(float);   // the fold reuses the ring as scratch
+  if (ring < fold) ring = fold;
+  return ring + (size_t)(feat + kRWarps * (feat + 1)) * sizeof(float);
 }
 
 // ---- host side -------------------------------------------------------------------------------
@@ -346,9 +477,10 @@ __global__ void __launch_bounds__(1024) linreg_stage2(const float* __restrict__ 
 // partial wave would cost as much as the first).  A function of n and of the device model only,
 // so the summation tree is reproducible.
 template <class Kernel>
-static int resident_ctas(Kernel kernel) {
+static int resident_ctas(Kernel kernel, size_t dyn_smem = 0) {
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRThreads, 0) != cudaSuccess || per_sm < 1) {
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRThreads, dyn_smem) != cudaSuccess ||
+      per_sm < 1) {
     cudaGetLastError();
     per_sm = 1;
   }
@@ -382,16 +514,14 @@ static float reduce_scalar(const float* v, int64_t n, int64_t first, float divis
   if (!partials) return NAN;
   float* out = scalar_slot();
   cudaStream_t s = ctx().stream;
-  int ctas = 0;
-  if (cnt > 0) {
-    int64_t slab;
-    static const int max_ctas = resident_ctas(reduce_stage1<R>);
-    slab_for(cnt, max_ctas, &slab, &ctas);
-    int vec = aligned16(base) ? 1 : 0;
-    reduce_stage1<R><<<ctas, kRThreads, 0, s>>>(base, cnt, slab, partials, vec);
-    count_launch();
-  }
-  reduce_stage2<R><<<1, kRThreads, 0, s>>>(partials, ctas, out, divisor, mode, v);
+  int64_t slab;
+  int ctas;
+  static const int max_ctas = resident_ctas(reduce_kernel<R>);
+  slab_for(cnt, max_ctas, &slab, &ctas);
+  unsigned int* done = nullptr;
+  cudaGetSymbolAddress((void**)&done, g_reduce_done);
+  reduce_kernel<R><<<ctas, kRThreads, 0, s>>>(base, cnt, slab, partials, aligned16(base) ? 1 : 0,
+                                            Finish{out, divisor, mode, v, done});
   count_launch();
   float r = NAN;
   if (cuda_ok(cudaGetLastError(), "reduction launch")) r = wait_scalar();
@@ -513,13 +643,15 @@ static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, co
   int ctas;
   static const int max_ctas = resident_ctas(mse_stage1);
   slab_for(n, max_ctas, &slab, &ctas);
+  unsigned int* done = nullptr;
+  cudaGetSymbolAddress((void**)&done, g_reduce_done);
   int vec = (aligned16(a->ptr) && aligned16(b->ptr) && (!d || aligned16(d->ptr))) ? 1 : 0;
   const float fn = (float)(int32_t)n;
   cudaStream_t s = ctx().stream;
   float* out = lo ? lo->ptr : scalar_slot();
-  mse_stage1<<<ctas, kRThreads, 0, s>>>(a->ptr, b->ptr, d ? d->ptr : nullptr, n, slab, fn, partials, vec, bwd_act);
-  reduce_stage2<SumRed><<<1, kRThreads, 0, s>>>(partials, ctas, out, fn, 0, nullptr);
-  count_launch(2);
+  mse_stage1<<<ctas, kRThreads, 0, s>>>(a->ptr, b->ptr, d ? d->ptr : nullptr, n, slab, fn, partials, vec, bwd_act,
+                                        Finish{out, fn, 0, nullptr, done});
+  count_launch();
   float r = NAN;
   if (cuda_ok(cudaGetLastError(), "mse launch")) r = lo ? 0.0f : wait_scalar();
   scratch_free(partials);
@@ -570,38 +702,49 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
     return NAN;
   }
   // Row slabs: one resident wave of CTAs, at least 1024 rows each, a multiple of 256 rows (8 warps x 32).
+  const bool fast = (feat == 4 || feat == 8 || feat == 16 || feat == 32) && aligned16(X->ptr);
+  const size_t dyn = fast ? linreg_smem_bytes(feat) : 0;
   int max_ctas;
-  switch (feat) {
-    case 4: max_ctas = resident_ctas(linreg_stage1<4>); break;
-    case 8: max_ctas = resident_ctas(linreg_stage1<8>); break;
-    case 16: max_ctas = resident_ctas(linreg_stage1<16>); break;
-    case 32: max_ctas = resident_ctas(linreg_stage1<32>); break;
-    default: max_ctas = resident_ctas(linreg_stage1_any); break;
+  if (fast) {
+    static bool attr_done = false;
+    if (!attr_done) {   // the FEAT = 32 ring exceeds the default 48 KiB dynamic shared memory limit
+      cudaFuncSetAttribute(linreg_stage1<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)linreg_smem_bytes(32));
+      cudaFuncSetAttribute(linreg_stage1<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)linreg_smem_bytes(16));
+      attr_done = true;
+    }
+    switch (feat) {
+      case 4: max_ctas = resident_ctas(linreg_stage1<4>, dyn); break;
+      case 8: max_ctas = resident_ctas(linreg_stage1<8>, dyn); break;
+      case 16: max_ctas = resident_ctas(linreg_stage1<16>, dyn); break;
+      default: max_ctas = resident_ctas(linreg_stage1<32>, dyn); break;
+    }
+  } else {
+    max_ctas = resident_ctas(linreg_stage1_any);
   }
   int64_t slab = ((int64_t)rows + max_ctas - 1) / max_ctas;
   if (slab < 1024) slab = 1024;
   slab = (slab + 255) / 256 * 256;
   int ctas = (int)(((int64_t)rows + slab - 1) / slab);
-  float* partials = scratch_alloc(((int64_t)ctas * (feat + 1) + 4) * sizeof(float));
+  float* partials = scratch_alloc(((int64_t)((ctas + 3) & ~3) * (feat + 1) + 4) * sizeof(float));
   if (!partials) return NAN;
   float* out = scalar_slot();
   const float fn = (float)rows;
   cudaStream_t s = ctx().stream;
   float* pp = P ? P->ptr : nullptr;
   profile_mark(true);
-  if (feat == 16 && aligned16(X->ptr))
-    linreg_stage1<16><<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials);
-  else if (feat == 32 && aligned16(X->ptr))
-    linreg_stage1<32><<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials);
-  else if (feat == 8 && aligned16(X->ptr))
-    linreg_stage1<8><<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials);
-  else if (feat == 4 && aligned16(X->ptr))
-    linreg_stage1<4><<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials);
+  if (fast && feat == 16)
+    linreg_stage1<16><<<ctas, kRThreads, dyn, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials, G->ptr, out);
+  else if (fast && feat == 32)
+    linreg_stage1<32><<<ctas, kRThreads, dyn, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials, G->ptr, out);
+  else if (fast && feat == 8)
+    linreg_stage1<8><<<ctas, kRThreads, dyn, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials, G->ptr, out);
+  else if (fast && feat == 4)
+    linreg_stage1<4><<<ctas, kRThreads, dyn, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, slab, fn, partials, G->ptr, out);
   else
-    linreg_stage1_any<<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, feat, slab, fn, partials);
-  linreg_stage2<<<1, 32 * (feat + 1 > 32 ? 32 : feat + 1), 0, s>>>(partials, ctas, feat, fn, G->ptr, out);
+    linreg_stage1_any<<<ctas, kRThreads, 0, s>>>(X->ptr, Y->ptr, W->ptr, pp, rows, feat, slab, fn, partials, G->ptr,
+                                                 out);
   profile_mark(false);
-  count_launch(2);
+  count_launch(1);
   float r = NAN;
   if (cuda_ok(cudaGetLastError(), "linreg launch")) r = wait_scalar();
   scratch_free(partials);
@@ -623,7 +766,7 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
 // ------------------------------------------------------------------------------------------------
 namespace cleave {
 
-constexpr int kNoAllocScratchFloats = kMaxPartials + 4;     // 1188 floats, 4752 bytes
+constexpr int kNoAllocScratchFloats = kMaxPartials + 4;     // 1188 floats, 4752 bytes: partials, then the counter
 constexpr int64_t kNoAllocMaxLen = 2147483647ll;             // largest tensor an i32 shape can describe
 constexpr int kNoAllocMaxDevices = 64;
 
@@ -666,18 +809,20 @@ extern "C" int32_t cleave_cuda_sum_noalloc_f32(const float* x_dev, int64_t len, 
   float* scratch = noalloc_scratch_for_current_device();
   if (!scratch) return -cleave_cuda_last_error();
   cudaStream_t s = (cudaStream_t)cuda_stream;
-  // Same slab rule and the same two kernels as cleave_cuda_sum_f32, so the summation tree and
-  // therefore the result are identical.  Stage 1 writes partials [0, ctas) and stage 2 reads
-  // exactly those, so nothing left in the array by an earlier call is ever read and nothing has
-  // to be cleared first.
+  // Same slab rule and the same kernel as cleave_cuda_sum_f32, so the summation tree and
+  // therefore the result are identical.  The CTAs write partials [0, ctas) and the last one to
+  // finish reads exactly those, so no value left in the array by an earlier call is ever read.
+  // The one word that must start at zero is the completion counter behind the partials: the
+  // array is zero when the library is loaded and the last CTA of every call sets it back to zero.
   int64_t slab;
   int ctas;
   // The occupancy query reads kernel attributes only; it allocates nothing.
-  static const int max_ctas = resident_ctas(reduce_stage1<SumRed>);
+  static const int max_ctas = resident_ctas(reduce_kernel<SumRed>);
   slab_for(len, max_ctas, &slab, &ctas);
-  reduce_stage1<SumRed><<<ctas, kRThreads, 0, s>>>(x_dev, len, slab, scratch, aligned16(x_dev) ? 1 : 0);
-  reduce_stage2<SumRed><<<1, kRThreads, 0, s>>>(scratch, ctas, out_dev, 1.0f, 0, nullptr);
-  count_launch(2);
+  unsigned int* done = reinterpret_cast<unsigned int*>(scratch + kMaxPartials);
+  reduce_kernel<SumRed><<<ctas, kRThreads, 0, s>>>(x_dev, len, slab, scratch, aligned16(x_dev) ? 1 : 0,
+                                                   Finish{out_dev, 1.0f, 0, nullptr, done});
+  count_launch();
   if (!cuda_ok(cudaGetLastError(), "sum_noalloc launch")) return -cleave_cuda_last_error();
   return CLEAVE_CUDA_OK;
 }

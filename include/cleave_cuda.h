@@ -147,8 +147,8 @@ float cleave_cuda_max_f32(cleave_buf v);
  * when they need the reduction: hosts where another framework owns the device heap, loops
  * where a cudaMalloc stall is not acceptable, processes already at their memory budget.
  * x_dev (len f32 values) and out_dev (one f32) are raw device pointers owned by the caller; the
- * two kernels are queued on cuda_stream (NULL = the default stream) of the CURRENT device and the
- * call returns without waiting.  The partial sums live in a 4752-byte array that is part of the
+ * kernel is queued on cuda_stream (NULL = the default stream) of the CURRENT device and the
+ * call returns without waiting.  The partial sums and a completion counter live in a 4752-byte array that is part of the
  * library image on every GPU; len may be at most 2^31 - 1 (larger is rejected with
  * CLEAVE_CUDA_ERR_UNSUPPORTED).  The first call on each device looks up the array's device
  * address, so make that first call outside any stream capture.  All calls on one device share
