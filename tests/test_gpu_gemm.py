@@ -66,7 +66,10 @@ def test_exact_path_transposed_and_batched():
 # tiles per CTA; more tiles than SMs; K not a multiple of the K-block; tall / wide.
 TC_SHAPES = [(128, 256, 16), (128, 256, 32), (128, 256, 64), (128, 256, 512), (256, 512, 128),
              (100, 200, 50), (129, 257, 33), (1, 1, 1), (5, 300, 7), (300, 5, 1000),
-             (512, 512, 512), (1024, 1024, 1024), (2048, 4096, 256), (640, 768, 2048)]
+             (512, 512, 512), (1024, 1024, 1024), (2048, 4096, 256), (640, 768, 2048),
+             # few tiles with a long K, and more tiles than SMs with a ragged last wave
+             (128, 256, 4096), (256, 512, 2048), (384, 256, 1280), (128, 256, 8192), (4096, 1024, 1024),
+             (2560, 2048, 768), (1920, 2560, 512)]
 
 
 @pytest.mark.parametrize("m,n,k", TC_SHAPES)
