@@ -27,7 +27,8 @@ struct ReluOp { __device__ float operator()(float x) const { return x != x ? x :
 struct ExpOp { __device__ float operator()(float x) const { return expf(x); } };
 // negf -> exp -> addf(1, e) -> divf(1, denom), fused into one pass.
 struct SigmoidOp {
-  __device__ float operator()(float x) const { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
+  // 1/d as a correctly rounded reciprocal: the same value as the IEEE division 1.0f / d, cheaper
+  __device__ float operator()(float x) const { return __frcp_rn(__fadd_rn(1.0f, expf(-x))); }
 };
 struct TanhOp { __device__ float operator()(float x) const { return tanhf(x); } };
 struct IdentityOp { __device__ float operator()(float x) const { return x; } };

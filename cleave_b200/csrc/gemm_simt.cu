@@ -13,7 +13,7 @@ constexpr int kTM = 64, kTN = 64, kTK = 16;
 __device__ __forceinline__ float apply_act(float v, int act) {
   switch (act) {
     case CLEAVE_ACT_RELU: return v != v ? v : (v > 0.0f ? v : 0.0f);
-    case CLEAVE_ACT_SIGMOID: return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v)));
+    case CLEAVE_ACT_SIGMOID: return __frcp_rn(__fadd_rn(1.0f, expf(-v)));
     case CLEAVE_ACT_TANH: return tanhf(v);
     default: return v;
   }

@@ -177,7 +177,7 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ float act_apply(float v, int act) {
   switch (act) {
     case CLEAVE_ACT_RELU: return v != v ? v : (v > 0.0f ? v : 0.0f);
-    case CLEAVE_ACT_SIGMOID: return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v)));
+    case CLEAVE_ACT_SIGMOID: return __frcp_rn(__fadd_rn(1.0f, expf(-v)));
     case CLEAVE_ACT_TANH: return tanhf(v);
     default: return v;
   }
@@ -419,7 +419,7 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           for (int j = 0; j < BN / 2; ++j) sum[j] = tanhf(sum[j]);
         } else if (p.act == CLEAVE_ACT_SIGMOID) {
 #pragma unroll
-          for (int j = 0; j < BN / 2; ++j) sum[j] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-sum[j])));
+          for (int j = 0; j < BN / 2; ++j) sum[j] = __frcp_rn(__fadd_rn(1.0f, expf(-sum[j])));
         } else if (p.act == CLEAVE_ACT_RELU) {
 #pragma unroll
           for (int j = 0; j < BN / 2; ++j) sum[j] = act_apply(sum[j], CLEAVE_ACT_RELU);
