@@ -66,7 +66,8 @@ struct Cfg {
   static constexpr int kABytes = BM * kRowBytes;          // one plane of A
   static constexpr int kBBytes = BN * kRowBytes;          // one plane of B
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;   // + alignment slack
+  static constexpr int kStoreStageBytes = kEpiWarps * 32 * 128;      // per drain warp: 32 rows x 32 floats
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreStageBytes + 1024;   // + alignment slack
   static constexpr uint32_t kLayoutType = BK == 32 ? 2u : 4u;       // SWIZZLE_128B : SWIZZLE_64B
   static constexpr uint32_t kSBO = 8 * kRowBytes;                   // bytes between 8-row groups
 };
@@ -393,6 +394,7 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (!ok) break;
       const int row = mb * BM + q * 32 + lane;
       const int col0 = nb * BN + half * (BN / 2);
+      const bool full_tile = (mb * BM + BM <= p.m) && (nb * BN + BN <= p.n);   // uniform over the CTA
       if (row < p.m) {
         float* crow = p.c + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
         if (p.bias != nullptr) {
@@ -424,14 +426,41 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
           for (int j = 0; j < BN / 2; ++j) sum[j] = act_apply(sum[j], CLEAVE_ACT_RELU);
         }
-        if (vec_ok && col0 + BN / 2 <= p.n) {
-          float4* dst = reinterpret_cast<float4*>(crow);
+        if (!(full_tile && vec_ok)) {
+          if (vec_ok && col0 + BN / 2 <= p.n) {
+            float4* dst = reinterpret_cast<float4*>(crow);
 #pragma unroll
-          for (int j = 0; j < BN / 8; ++j) dst[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
-        } else {
+            for (int j = 0; j < BN / 8; ++j) dst[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
+          } else {
 #pragma unroll
-          for (int j = 0; j < BN / 2; ++j)
-            if (col0 + j < p.n) crow[j] = sum[j];
+            for (int j = 0; j < BN / 2; ++j)
+              if (col0 + j < p.n) crow[j] = sum[j];
+          }
+        }
+      }
+      if (full_tile && vec_ok) {
+        // Coalesced store of the warp's 32 x 128 block.  A thread owns one ROW (what tcgen05.ld
+        // hands out), but a store instruction is efficient when the warp covers whole 128-byte
+        // lines.  So, 32 columns at a time, every thread parks its 8 16-byte words in a
+        // warp-private shared tile (word j of row r at slot j ^ (r & 7): conflict free both ways)
+        // and the warp then writes 4 rows x 128 bytes per instruction.
+        float4* stage = reinterpret_cast<float4*>(smem_raw + (ring - smem_u32(smem_raw)) +
+                                                  C::kStages * C::kStageBytes) + (warp - 2) * (32 * 8);
+        float* cblock = p.c + ((int64_t)b * p.m + mb * BM + q * 32) * (int64_t)p.n + col0;
+#pragma unroll
+        for (int pass = 0; pass < BN / 64; ++pass) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            stage[lane * 8 + (j ^ (lane & 7))] = make_float4(sum[32 * pass + 4 * j], sum[32 * pass + 4 * j + 1],
+                                                             sum[32 * pass + 4 * j + 2], sum[32 * pass + 4 * j + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3), slot = lane & 7;
+            const float4 v = stage[r * 8 + (slot ^ (r & 7))];
+            *reinterpret_cast<float4*>(cblock + (int64_t)r * p.n + 32 * pass + 4 * slot) = v;
+          }
+          __syncwarp();
         }
       }
     }
