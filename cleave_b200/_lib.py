@@ -14,6 +14,8 @@ LIB_PATH = os.path.join(_HERE, "libcleave_cuda.so")
 
 c_buf = ctypes.c_void_p
 c_f32p = ctypes.POINTER(ctypes.c_float)
+c_f64p = ctypes.POINTER(ctypes.c_double)
+f64 = ctypes.c_double
 i32, i64, f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_float
 
 # name -> (restype, argtypes); mirrors include/cleave_cuda.h declaration by declaration.
@@ -76,6 +78,25 @@ SIGNATURES = {
     "cleave_cuda_mse_act_bwd_f32": (f32, [c_buf, c_buf, c_buf, i32]),
     "cleave_cuda_mse_act_bwd_dev_f32": (i32, [c_buf, c_buf, c_buf, i32, c_buf]),
     "cleave_cuda_sgd_f32": (i32, [c_buf, c_buf, f32, f32]),
+    "cleave_cuda_alloc_f64": (c_buf, [i64]),
+    "cleave_cuda_upload_f64": (c_buf, [c_f64p, i64]),
+    "cleave_cuda_download_f64": (i64, [c_buf, c_f64p, i64]),
+    "cleave_cuda_fill_f64": (c_buf, [f64, i64]),
+    "cleave_cuda_zeros_f64": (c_buf, [i64]),
+    "cleave_cuda_get_f64": (f64, [c_buf, i64]),
+    "cleave_cuda_add_f64": (c_buf, [c_buf, c_buf]),
+    "cleave_cuda_sub_f64": (c_buf, [c_buf, c_buf]),
+    "cleave_cuda_mul_f64": (c_buf, [c_buf, c_buf]),
+    "cleave_cuda_div_f64": (c_buf, [c_buf, c_buf]),
+    "cleave_cuda_neg_f64": (c_buf, [c_buf]),
+    "cleave_cuda_relu_f64": (c_buf, [c_buf]),
+    "cleave_cuda_sigmoid_f64": (c_buf, [c_buf]),
+    "cleave_cuda_tanh_f64": (c_buf, [c_buf]),
+    "cleave_cuda_exp_f64": (c_buf, [c_buf]),
+    "cleave_cuda_sum_f64": (f64, [c_buf]),
+    "cleave_cuda_mean_f64": (f64, [c_buf]),
+    "cleave_cuda_max_f64": (f64, [c_buf]),
+    "cleave_cuda_gemm_f64": (c_buf, [c_buf, c_buf, i32, i32, i32]),
     "cleave_cuda_dp_sgd_allreduce_f32": (i32, [ctypes.POINTER(ctypes.c_void_p)] * 3 + [ctypes.c_void_p, ctypes.c_void_p,
                                                 i64, i32, i32, f32, ctypes.c_uint32]),
     "cleave_cuda_linreg_step_f32": (f32, [c_buf, c_buf, c_buf, c_buf, c_buf, i32, i32]),

@@ -10,7 +10,9 @@
 
 namespace cleave {
 
-// One device tensor: dense row-major f32, `len` elements at `ptr`.
+enum { DT_F32 = 0, DT_F64 = 1 };
+
+// One device tensor: dense row-major, `len` elements of `dtype` at `ptr` (f64 entry points cast).
 struct Buf {
   uint32_t magic;   // kMagic while live
   float* ptr;
@@ -22,6 +24,7 @@ struct Buf {
   cudaEvent_t xfer_ev;
   cudaEvent_t order_ev;
   bool xfer_pending;
+  int dtype;          // DT_F32 or DT_F64
 };
 constexpr uint32_t kMagic = 0xC1EA7E5Bu;
 
@@ -62,9 +65,12 @@ struct ApiLock {
 };
 
 // ---- handles and memory ---------------------------------------------------------------
-Buf* new_buf(int64_t len);             // pooled device allocation; nullptr + error on failure
-Buf* as_buf(cleave_buf h, const char* what);   // validates, settles a pending async transfer; nullptr + error on failure
-Buf* lookup_buf(cleave_buf h, const char* what);   // validates only
+Buf* new_buf(int64_t len, int dtype = DT_F32);   // pooled device allocation; nullptr + error on failure
+// Validates the handle and its element type, settles a pending async transfer; nullptr + error on failure.
+Buf* as_buf(cleave_buf h, const char* what, int dtype = DT_F32);
+Buf* lookup_buf(cleave_buf h, const char* what);   // validates liveness only
+double* scalar_slot_f64();   // like scalar_slot(), for f64 results; read back with wait_scalar_f64()
+double wait_scalar_f64();
 void release_buf(Buf* b);
 float* scratch_alloc(int64_t bytes);   // pooled scratch (stream-ordered reuse); pair with scratch_free
 void scratch_free(float* p);

@@ -171,16 +171,16 @@ static void pool_free(void* p, int64_t block_bytes) {
   g_cached_bytes += block_bytes;
 }
 
-Buf* new_buf(int64_t len) {
+Buf* new_buf(int64_t len, int dtype) {
   if (len <= 0) {
     set_error(CLEAVE_CUDA_ERR_ARG, "tensor length must be positive, got %lld", (long long)len);
     return nullptr;
   }
   if (!ensure_init()) return nullptr;
   int64_t bs = 0;
-  void* p = pool_alloc(len * (int64_t)sizeof(float), &bs);
+  void* p = pool_alloc(len * (int64_t)(dtype == DT_F64 ? sizeof(double) : sizeof(float)), &bs);
   if (!p) return nullptr;
-  Buf* b = new Buf{kMagic, (float*)p, len, bs, nullptr, nullptr, false};
+  Buf* b = new Buf{kMagic, (float*)p, len, bs, nullptr, nullptr, false, dtype};
   g_live.insert(b);
   g_live_bytes += bs;
   return b;
@@ -202,9 +202,15 @@ static void settle_transfer(Buf* b) {
   }
 }
 
-Buf* as_buf(cleave_buf h, const char* what) {
+Buf* as_buf(cleave_buf h, const char* what, int dtype) {
   Buf* b = lookup_buf(h, what);
-  if (b) settle_transfer(b);
+  if (!b) return nullptr;
+  if (b->dtype != dtype) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "%s: tensor holds %s elements, this entry point works on %s", what,
+              b->dtype == DT_F64 ? "f64" : "f32", dtype == DT_F64 ? "f64" : "f32");
+    return nullptr;
+  }
+  settle_transfer(b);
   return b;
 }
 
@@ -291,6 +297,15 @@ double profile_end(int* pairs) {
 }
 
 float* scalar_slot() { return g_ctx.scalar_dev + 1; }   // slot 0 is read_scalar's copy target
+
+double* scalar_slot_f64() { return reinterpret_cast<double*>(g_ctx.scalar_dev + 2); }   // 8-byte aligned
+
+double wait_scalar_f64() {
+  Context& c = g_ctx;
+  if (!cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize")) return NAN;
+  if (check_device_status() != CLEAVE_CUDA_OK) return NAN;
+  return *reinterpret_cast<volatile double*>(c.scalar_host + 2);
+}
 
 float wait_scalar() {
   Context& c = g_ctx;
@@ -535,13 +550,13 @@ float cleave_cuda_get_f32(cleave_buf t, int64_t i) {
 
 int64_t cleave_cuda_len(cleave_buf t) {
   ApiLock lock;
-  Buf* b = as_buf(t, "len");
+  Buf* b = lookup_buf(t, "len");
   return b ? b->len : -t_err_code;
 }
 
 void cleave_cuda_free(cleave_buf t) {
   ApiLock lock;
-  Buf* b = as_buf(t, "free");
+  Buf* b = lookup_buf(t, "free");
   if (b) release_buf(b);
 }
 
@@ -552,14 +567,15 @@ cleave_buf cleave_cuda_wrap_f32(void* device_ptr, int64_t len) {
     return nullptr;
   }
   if (!ensure_init()) return nullptr;
-  Buf* b = new Buf{kMagic, (float*)device_ptr, len, 0, nullptr, nullptr, false};
+  Buf* b = new Buf{kMagic, (float*)device_ptr, len, 0, nullptr, nullptr, false, DT_F32};
   g_live.insert(b);
   return (cleave_buf)b;
 }
 
 void* cleave_cuda_data_ptr(cleave_buf t) {
   ApiLock lock;
-  Buf* b = as_buf(t, "data_ptr");
+  Buf* b = lookup_buf(t, "data_ptr");
+  if (b) as_buf(t, "data_ptr", b->dtype);   // orders the compute stream after a pending async transfer
   return b ? (void*)b->ptr : nullptr;
 }
 

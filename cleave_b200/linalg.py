@@ -18,7 +18,10 @@ import math
 
 import numpy as np
 
-from ._lib import c_f32p, lib, raise_last_error
+from ._lib import c_f32p, c_f64p, lib, raise_last_error
+
+_NP = {"f32": np.float32, "f64": np.float64}
+_PTR = {"f32": c_f32p, "f64": c_f64p}
 
 
 def _prod(dims) -> int:
@@ -26,45 +29,52 @@ def _prod(dims) -> int:
 
 
 class Tensor:
-    """``Tensor<f32, Dims...>``: a device-resident f32 array with a static shape."""
+    """``Tensor<T, Dims...>`` for ``T`` = f32 (default) or f64: a device-resident array with a static shape."""
 
-    __slots__ = ("_h", "dims", "_owner")
+    __slots__ = ("_h", "dims", "dtype", "_owner")
 
-    def __init__(self, data=None, *, dims=None, _handle=None):
+    def __init__(self, data=None, *, dims=None, dtype: str = "f32", _handle=None):
         """``Tensor(data)`` uploads a nested list / array, like ``Tensor::<f32, ...>(data: [...])``."""
+        if dtype not in _NP:
+            raise TypeError(f"Tensor element type must be f32 or f64, not {dtype!r}")
+        self.dtype = dtype
         if _handle is not None:
             self._h, self.dims = _handle, tuple(int(d) for d in dims)
             return
-        a = np.ascontiguousarray(data, dtype=np.float32)
+        a = np.ascontiguousarray(data, dtype=_NP[dtype])
         if dims is not None and tuple(dims) != a.shape:
             raise TypeError(f"data has shape {a.shape}, declared dims are {tuple(dims)}")
         if a.ndim < 1 or a.size == 0:
             raise TypeError("a Tensor needs rank >= 1 and at least one element")
-        h = lib().cleave_cuda_upload_f32(a.ctypes.data_as(c_f32p), a.size)
+        h = self._fn("upload")(a.ctypes.data_as(_PTR[dtype]), a.size)
         if not h:
             raise_last_error("Tensor upload")
         self._h, self.dims = h, a.shape
 
+    def _fn(self, op: str):
+        """The library entry point of ``op`` for this tensor's element type."""
+        return getattr(lib(), f"cleave_cuda_{op}_{self.dtype}")
+
     # ---- construction -------------------------------------------------------------------
     @classmethod
-    def _wrap(cls, handle, dims, what="op"):
+    def _wrap(cls, handle, dims, what="op", dtype: str = "f32"):
         if not handle:
             raise_last_error(what)
-        return cls(dims=dims, _handle=handle)
+        return cls(dims=dims, dtype=dtype, _handle=handle)
 
     @classmethod
-    def zero(cls, *dims) -> "Tensor":
-        """``Ring::zero()`` for ``Tensor<f32, dims...>`` (tensor.cleave:79)."""
-        return cls._wrap(lib().cleave_cuda_zeros_f32(_prod(dims)), dims, "zero")
+    def zero(cls, *dims, dtype: str = "f32") -> "Tensor":
+        """``Ring::zero()`` for ``Tensor<T, dims...>`` (tensor.cleave:79)."""
+        return cls._wrap(getattr(lib(), f"cleave_cuda_zeros_{dtype}")(_prod(dims)), dims, "zero", dtype)
 
     @classmethod
-    def filled(cls, value: float, *dims) -> "Tensor":
+    def filled(cls, value: float, *dims, dtype: str = "f32") -> "Tensor":
         """``Tensor::<T, Dims...>(data: [value; Dims...])``."""
-        return cls._wrap(lib().cleave_cuda_fill_f32(float(value), _prod(dims)), dims, "fill")
+        return cls._wrap(getattr(lib(), f"cleave_cuda_fill_{dtype}")(float(value), _prod(dims)), dims, "fill", dtype)
 
     @classmethod
-    def empty(cls, *dims) -> "Tensor":
-        return cls._wrap(lib().cleave_cuda_alloc_f32(_prod(dims)), dims, "alloc")
+    def empty(cls, *dims, dtype: str = "f32") -> "Tensor":
+        return cls._wrap(getattr(lib(), f"cleave_cuda_alloc_{dtype}")(_prod(dims)), dims, "alloc", dtype)
 
     @classmethod
     def from_device_ptr(cls, ptr: int, *dims) -> "Tensor":
@@ -82,9 +92,9 @@ class Tensor:
 
     def numpy(self, out: np.ndarray | None = None) -> np.ndarray:
         if out is None:
-            out = np.empty(self.dims, np.float32)
-        assert out.dtype == np.float32 and out.size == self.numel and out.flags.c_contiguous
-        if lib().cleave_cuda_download_f32(self._h, out.ctypes.data_as(c_f32p), out.size) < 0:
+            out = np.empty(self.dims, _NP[self.dtype])
+        assert out.dtype == _NP[self.dtype] and out.size == self.numel and out.flags.c_contiguous
+        if self._fn("download")(self._h, out.ctypes.data_as(_PTR[self.dtype]), out.size) < 0:
             raise_last_error("download")
         return out
 
@@ -92,6 +102,8 @@ class Tensor:
         """Same storage, new static shape (row-major flattening is the identity on memory)."""
         if _prod(dims) != self.numel:
             raise TypeError(f"cannot view {self.dims} as {dims}")
+        if self.dtype != "f32":
+            raise TypeError("views are available for f32 tensors only")
         t = Tensor.from_device_ptr(self.data_ptr, *dims)
         t._owner = self   # keep the storage alive
         return t
@@ -106,24 +118,24 @@ class Tensor:
             if not 0 <= int(i) < d:
                 raise IndexError(f"index {idx} out of bounds for dims {self.dims}")
             flat = flat * d + int(i)
-        v = lib().cleave_cuda_get_f32(self._h, flat)
+        v = self._fn("get")(self._h, flat)
         if math.isnan(v) and lib().cleave_cuda_last_error():
             raise_last_error("index")
-        return float(np.float32(v))
+        return float(_NP[self.dtype](v))
 
     # ---- Ring<Tensor> -------------------------------------------------------------------
-    def _binary(self, other, fn, name):
+    def _binary(self, other, name):
         if not isinstance(other, Tensor):
             raise TypeError(f"{name}: operand is not a Tensor (a bare scalar is not broadcast)")
-        if other.dims != self.dims:
-            raise TypeError(f"{name}: mismatched types Tensor<f32,{self.dims}> and Tensor<f32,{other.dims}>")
-        return Tensor._wrap(fn(self._h, other._h), self.dims, name)
+        if other.dims != self.dims or other.dtype != self.dtype:
+            raise TypeError(f"{name}: mismatched types {self!r} and {other!r}")
+        return Tensor._wrap(self._fn(name)(self._h, other._h), self.dims, name, self.dtype)
 
-    def __add__(self, o): return self._binary(o, lib().cleave_cuda_add_f32, "add")
-    def __sub__(self, o): return self._binary(o, lib().cleave_cuda_sub_f32, "sub")
-    def __mul__(self, o): return self._binary(o, lib().cleave_cuda_mul_f32, "mul")
-    def __truediv__(self, o): return self._binary(o, lib().cleave_cuda_div_f32, "div")
-    def __neg__(self): return Tensor._wrap(lib().cleave_cuda_neg_f32(self._h), self.dims, "neg")
+    def __add__(self, o): return self._binary(o, "add")
+    def __sub__(self, o): return self._binary(o, "sub")
+    def __mul__(self, o): return self._binary(o, "mul")
+    def __truediv__(self, o): return self._binary(o, "div")
+    def __neg__(self): return Tensor._wrap(self._fn("neg")(self._h), self.dims, "neg", self.dtype)
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -134,15 +146,15 @@ class Tensor:
                 pass
 
     def __repr__(self):
-        return f"Tensor<f32, {', '.join(map(str, self.dims))}>"
+        return f"Tensor<{self.dtype}, {', '.join(map(str, self.dims))}>"
 
 
 def matmul(a: Tensor, b: Tensor) -> Tensor:
     """``MatMul<Tensor<T,N,M>, Tensor<T,M,K>, Tensor<T,N,K>>::matmul`` (matrix.cleave:27-62)."""
-    if len(a.dims) != 2 or len(b.dims) != 2 or a.dims[1] != b.dims[0]:
-        raise TypeError(f"matmul: no impl for Tensor<f32,{a.dims}> x Tensor<f32,{b.dims}>")
+    if len(a.dims) != 2 or len(b.dims) != 2 or a.dims[1] != b.dims[0] or a.dtype != b.dtype:
+        raise TypeError(f"matmul: no impl for {a!r} x {b!r}")
     (m, k), n = a.dims, b.dims[1]
-    return Tensor._wrap(lib().cleave_cuda_gemm_f32(a._h, b._h, m, n, k), (m, n), "matmul")
+    return Tensor._wrap(a._fn("gemm")(a._h, b._h, m, n, k), (m, n), "matmul", a.dtype)
 
 
 def matmul_nt(a: Tensor, b: Tensor) -> Tensor:

@@ -15,23 +15,23 @@ from ._lib import lib, raise_last_error
 from .linalg import ACT, Tensor
 
 
-def _unary(fn_name: str, what: str):
+def _unary(what: str):
     def f(x: Tensor) -> Tensor:
-        return Tensor._wrap(getattr(lib(), fn_name)(x._h), x.dims, what)
+        return Tensor._wrap(x._fn(what)(x._h), x.dims, what, x.dtype)
 
     f.__name__ = what
     return f
 
 
-relu = _unary("cleave_cuda_relu_f32", "relu")
-sigmoid = _unary("cleave_cuda_sigmoid_f32", "sigmoid")
-tanh = _unary("cleave_cuda_tanh_f32", "tanh")
-exp = _unary("cleave_cuda_exp_f32", "exp")
+relu = _unary("relu")
+sigmoid = _unary("sigmoid")
+tanh = _unary("tanh")
+exp = _unary("exp")
 
 
-def _scalar(fn_name: str, what: str):
+def _scalar(op: str, what: str):
     def f(v: Tensor) -> float:
-        r = getattr(lib(), fn_name)(v._h)
+        r = v._fn(op)(v._h)
         if math.isnan(r) and lib().cleave_cuda_last_error():
             raise_last_error(what)
         return r
@@ -40,9 +40,9 @@ def _scalar(fn_name: str, what: str):
     return f
 
 
-sum = _scalar("cleave_cuda_sum_f32", "sum")  # noqa: A001 - the reference's name
-mean = _scalar("cleave_cuda_mean_f32", "mean")
-max_of = _scalar("cleave_cuda_max_f32", "max_of")
+sum = _scalar("sum", "sum")  # noqa: A001 - the reference's name
+mean = _scalar("mean", "mean")
+max_of = _scalar("max", "max_of")
 
 
 # ---- derivative forms (what derive() emits for the activations, applied to a whole tensor) ------

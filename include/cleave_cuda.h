@@ -204,6 +204,32 @@ int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale);
 float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out,
                                   cleave_buf grad_out, int32_t rows, int32_t feat);
 
+/* ------------------------------------------------------------------ f64 instances
+ * The reference's algebras are declared for every T: Float (Ring<f64> stdlib/num/num.cleave:189-196,
+ * Activation<f64> stdlib/nn/nn.cleave:60-64, Tensor<T, Dims...> stdlib/linalg/tensor.cleave:40), so
+ * the operator surface exists for f64 tensors too.  Same semantics as the f32 entry points above;
+ * a handle remembers its element type and the two families reject each other's tensors.
+ * Matmul is the exact kernel only (bit-identical to the reference loop; no f64 tensor-core mode). */
+cleave_buf cleave_cuda_alloc_f64(int64_t len);
+cleave_buf cleave_cuda_upload_f64(const double* host, int64_t len);
+int64_t cleave_cuda_download_f64(cleave_buf t, double* host, int64_t len);
+cleave_buf cleave_cuda_fill_f64(double value, int64_t len);
+cleave_buf cleave_cuda_zeros_f64(int64_t len);
+double cleave_cuda_get_f64(cleave_buf t, int64_t flat_index);
+cleave_buf cleave_cuda_add_f64(cleave_buf a, cleave_buf b);
+cleave_buf cleave_cuda_sub_f64(cleave_buf a, cleave_buf b);
+cleave_buf cleave_cuda_mul_f64(cleave_buf a, cleave_buf b);
+cleave_buf cleave_cuda_div_f64(cleave_buf a, cleave_buf b);
+cleave_buf cleave_cuda_neg_f64(cleave_buf a);
+cleave_buf cleave_cuda_relu_f64(cleave_buf x);
+cleave_buf cleave_cuda_sigmoid_f64(cleave_buf x);
+cleave_buf cleave_cuda_tanh_f64(cleave_buf x);
+cleave_buf cleave_cuda_exp_f64(cleave_buf x);
+double cleave_cuda_sum_f64(cleave_buf v);
+double cleave_cuda_mean_f64(cleave_buf v);
+double cleave_cuda_max_f64(cleave_buf v);
+cleave_buf cleave_cuda_gemm_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k);
+
 /* ------------------------------------------------------------------ data-parallel step over peer memory
  * No counterpart in the reference (distribution is "named as a goal but not designed",
  * doc/hld.md:250).  One kernel per step does what a gradient all-reduce followed by the SGD update

@@ -459,4 +459,59 @@ float ref_mlp2_fwd_bwd_f32(const float* X, const float* W1, const float* b1, con
   return loss;
 }
 
+// ---------------------------------------------------------------------------------
+// f64 instances.  The reference declares every algebra for T: Float, so the same loops
+// run on binary64 (Ring<f64> stdlib/num/num.cleave:189-196; Activation<f64>
+// stdlib/nn/nn.cleave:60-64; Tensor<T, Dims...> stdlib/linalg/tensor.cleave:40;
+// Transcendental<f64> num.cleave:231-234).  Same operation order as the f32 versions above.
+// ---------------------------------------------------------------------------------
+void ref_matmul_f64(const double* A, const double* B, double* C, int64_t m, int64_t k, int64_t n) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    double* c = C + i * n;
+    for (int64_t j = 0; j < n; ++j) c[j] = 0.0;
+    for (int64_t p = 0; p < k; ++p) {
+      const double a = A[i * k + p];
+      const double* b = B + p * n;
+      for (int64_t j = 0; j < n; ++j) {
+        double prod = a * b[j];
+        c[j] = c[j] + prod;
+      }
+    }
+  }
+}
+void ref_add_f64(const double* a, const double* b, double* o, int64_t n) { for (int64_t i = 0; i < n; ++i) o[i] = a[i] + b[i]; }
+void ref_sub_f64(const double* a, const double* b, double* o, int64_t n) { for (int64_t i = 0; i < n; ++i) o[i] = a[i] - b[i]; }
+void ref_mul_f64(const double* a, const double* b, double* o, int64_t n) { for (int64_t i = 0; i < n; ++i) o[i] = a[i] * b[i]; }
+void ref_div_f64(const double* a, const double* b, double* o, int64_t n) { for (int64_t i = 0; i < n; ++i) o[i] = a[i] / b[i]; }
+void ref_neg_f64(const double* a, double* o, int64_t n) { for (int64_t i = 0; i < n; ++i) o[i] = -a[i]; }
+void ref_relu_f64(const double* x, double* o, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    const double v = x[i];
+    o[i] = v != v ? v : ((v == 0.0) ? 0.0 : (v > 0.0 ? v : 0.0));   // maximumf(x, +0): NaN propagates, -0 -> +0
+  }
+}
+void ref_exp_f64(const double* x, double* o, int64_t n) { for (int64_t i = 0; i < n; ++i) o[i] = std::exp(x[i]); }
+void ref_sigmoid_f64(const double* x, double* o, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    double negx = -x[i];
+    double e = std::exp(negx);
+    double denom = 1.0 + e;
+    o[i] = 1.0 / denom;
+  }
+}
+void ref_tanh_f64(const double* x, double* o, int64_t n) { for (int64_t i = 0; i < n; ++i) o[i] = std::tanh(x[i]); }
+double ref_sum_f64(const double* v, int64_t n) {
+  double acc = v[0];
+  for (int64_t i = 1; i < n; ++i) acc = acc + v[i];
+  return acc;
+}
+double ref_mean_f64(const double* v, int64_t n) { return ref_sum_f64(v, n) / (double)(int32_t)n; }
+double ref_max_f64(const double* v, int64_t n) {
+  double acc = v[0];
+  for (int64_t i = 1; i < n; ++i)
+    if (v[i] > acc) acc = v[i];
+  return acc;
+}
+
 }  // extern "C"

@@ -70,6 +70,13 @@ def lib() -> ctypes.CDLL:
             sig[f"ref_{name}_f32"] = (None, [_f32p, _f32p, _i64])
         for name in ("tanh_bwd", "sigmoid_bwd", "relu_bwd"):
             sig[f"ref_{name}_f32"] = (None, [_f32p, _f32p, _f32p, _i64])
+        sig["ref_matmul_f64"] = (None, [_f64p, _f64p, _f64p, _i64, _i64, _i64])
+        for name in ("add", "sub", "mul", "div"):
+            sig[f"ref_{name}_f64"] = (None, [_f64p, _f64p, _f64p, _i64])
+        for name in ("neg", "relu", "exp", "sigmoid", "tanh"):
+            sig[f"ref_{name}_f64"] = (None, [_f64p, _f64p, _i64])
+        for name in ("sum", "mean", "max"):
+            sig[f"ref_{name}_f64"] = (ctypes.c_double, [_f64p, _i64])
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
             fn.restype = res
@@ -287,3 +294,36 @@ def mlp2_fwd_bwd(X, W1, b1, W2, b2, T, act1="tanh", act2="sigmoid", mean_loss=Tr
     )
     r["loss"] = np.float32(loss)
     return r
+
+
+# ------------------------------------------------------------------ f64 instances
+def _c64(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float64)
+
+
+def matmul64(a, b) -> np.ndarray:
+    a, b = _c64(a), _c64(b)
+    m, k = a.shape
+    n = b.shape[1]
+    c = np.empty((m, n), np.float64)
+    lib().ref_matmul_f64(_pd(a), _pd(b), _pd(c), m, k, n)
+    return c
+
+
+def binary64(name: str, a, b) -> np.ndarray:
+    a, b = _c64(a), _c64(b)
+    o = np.empty_like(a)
+    getattr(lib(), f"ref_{name}_f64")(_pd(a), _pd(b), _pd(o), a.size)
+    return o
+
+
+def unary64(name: str, a) -> np.ndarray:
+    a = _c64(a)
+    o = np.empty_like(a)
+    getattr(lib(), f"ref_{name}_f64")(_pd(a), _pd(o), a.size)
+    return o
+
+
+def reduce64(name: str, v) -> float:
+    v = _c64(v).ravel()
+    return float(getattr(lib(), f"ref_{name}_f64")(_pd(v), v.size))
