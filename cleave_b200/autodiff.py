@@ -85,11 +85,13 @@ class MLP2:
         one-element tensor) the loss is left on the device, nothing waits and ``None`` is returned."""
         H, Y = self.forward(X)
         loss, dZ2 = nn.mse_act_bwd(Y, T, self.act2, loss_out)   # dY and act2'(Y) * dY in one pass
+        # dH first: it is the last reader of W2 in this step, so once [dW2 | db2] are announced a
+        # data-parallel exchange may already overwrite W2 and b2 while the rest of the pass runs.
+        dH = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True)   # dZ2 W2^T
         gemm_into(self.dW2, H, dZ2, trans_a=True)            # H^T dZ2
         self._colsum_into(self.db2, dZ2)
         if on_grads_ready:
             on_grads_ready(0)
-        dH = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True)   # dZ2 W2^T
         dZ1 = _ACT_BWD[self.act1](H, dH)
         gemm_into(self.dW1, X, dZ1, trans_a=True)            # X^T dZ1
         self._colsum_into(self.db1, dZ1)

@@ -218,27 +218,27 @@ using namespace cleave;
 
 extern "C" int32_t cleave_cuda_dp_sgd_allreduce_f32(void* const* params_peers, void* const* grads_peers,
                                                     void* const* flags_peers, void* params_multicast,
-                                                    void* grads_multicast, int64_t len, int32_t rank, int32_t world,
-                                                    float lr, uint32_t epoch) {
+                                                    void* grads_multicast, int64_t offset, int64_t len, int32_t rank,
+                                                    int32_t world, float lr, uint32_t epoch, void* cuda_stream) {
   ApiLock lock;
   if (!ensure_init()) return -cleave_cuda_last_error();
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
     return -set_error(CLEAVE_CUDA_ERR_ARG, "dp_sgd_allreduce: rank %d / world %d (at most %d ranks)", rank, world,
                       kMaxRanks);
-  if (!params_peers || !grads_peers || !flags_peers || len <= 0 || len % 4 != 0)
-    return -set_error(CLEAVE_CUDA_ERR_ARG, "dp_sgd_allreduce: need peer pointer tables and a length that is a "
-                                           "positive multiple of 4 (got %lld)", (long long)len);
+  if (!params_peers || !grads_peers || !flags_peers || len <= 0 || len % 4 != 0 || offset < 0 || offset % 4 != 0)
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "dp_sgd_allreduce: need peer pointer tables and an offset and length that "
+                                           "are multiples of 4 (got %lld, %lld)", (long long)offset, (long long)len);
   DpArgs a{};
   for (int r = 0; r < world; ++r) {
     if (!params_peers[r] || !grads_peers[r] || !flags_peers[r] || ((uintptr_t)params_peers[r] & 15u) ||
         ((uintptr_t)grads_peers[r] & 15u))
       return -set_error(CLEAVE_CUDA_ERR_ARG, "dp_sgd_allreduce: peer %d has a NULL or unaligned buffer", r);
-    a.params[r] = (float*)params_peers[r];
-    a.grads[r] = (const float*)grads_peers[r];
+    a.params[r] = (float*)params_peers[r] + offset;
+    a.grads[r] = (const float*)grads_peers[r] + offset;
     a.flags[r] = (uint32_t*)flags_peers[r];
   }
-  a.params_mc = (float*)params_multicast;
-  a.grads_mc = (const float*)grads_multicast;
+  a.params_mc = params_multicast ? (float*)params_multicast + offset : nullptr;
+  a.grads_mc = grads_multicast ? (const float*)grads_multicast + offset : nullptr;
   a.rank = rank;
   a.world = world;
   const int64_t words = len / 4, base = words / world, extra = words % world;
@@ -253,7 +253,8 @@ extern "C" int32_t cleave_cuda_dp_sgd_allreduce_f32(void* const* params_peers, v
   int grid = ceil_div(a.word_hi - a.word_lo, kDpThreads * 4);
   if (grid > ctx().sm_count) grid = ctx().sm_count;
   if (grid < 1) grid = 1;
-  dp_sgd_allreduce_kernel<<<grid, kDpThreads, 0, ctx().stream>>>(a);
+  cudaStream_t s = cuda_stream ? (cudaStream_t)cuda_stream : ctx().stream;
+  dp_sgd_allreduce_kernel<<<grid, kDpThreads, 0, s>>>(a);
   count_launch();
   if (!cuda_ok(cudaGetLastError(), "dp_sgd_allreduce launch")) return -cleave_cuda_last_error();
   return CLEAVE_CUDA_OK;

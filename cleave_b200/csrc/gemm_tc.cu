@@ -485,7 +485,10 @@ __device__ __forceinline__ float tf32_round(float x) {
 }
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   hi = tf32_round(x);
-  lo = tf32_round(__fsub_rn(x, hi));
+  // A finite x just below FLT_MAX must not round up to infinity: truncate instead.
+  if (fabsf(hi) == INFINITY && fabsf(x) != INFINITY) hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+  // Non-finite values carry no low part (inf - inf would inject a NaN of its own).
+  lo = (fabsf(hi) == INFINITY || hi != hi) ? 0.0f : tf32_round(__fsub_rn(x, hi));
 }
 
 // Source already K-major: src[b][r][k] (r < rows, k < K).  dst planes [b][2][rows_p][Kp].

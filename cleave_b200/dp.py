@@ -147,18 +147,51 @@ class FusedDataParallel:
         self.params = Tensor.from_device_ptr(self._bufs[0].data_ptr(), n_params)
         self.grads = Tensor.from_device_ptr(self._bufs[1].data_ptr(), n_params)
         self.net = make_net(self.params, self.grads)
-        self.epoch = 1
+        # Buckets in the order the backward pass completes them: [W2 | b2] first, then [W1 | b1].
+        o = [int(x) for x in self.net._offsets]
+        self._buckets = [(o[2], o[4] - o[2]), (o[0], o[2] - o[0])]
+        if any(off % 4 or n % 4 for off, n in self._buckets):
+            self._buckets = [(0, n_params)]          # ragged layer sizes: exchange everything at the end
+        # Each bucket has its own signal words (32 apart) and epoch counter; the first bucket is
+        # exchanged on a side stream while the backward pass continues on the main one.
+        self._flag_tables = [arr(*[int(f.buffer_ptrs[r]) + 128 * b for r in range(self.world)])
+                             for b in range(len(self._buckets))]
+        self._epochs = [1] * len(self._buckets)
+        self._main = torch.cuda.current_stream()
+        from ._lib import lib
+        if (lib().cleave_cuda_get_stream() or 0) != self._main.cuda_stream:
+            raise RuntimeError("the library must run on torch's current stream: call dp.use_torch_stream() first")
+        self._side = torch.cuda.Stream()
+        self._ready = torch.cuda.Event()
+        self._done = torch.cuda.Event()
+        self._torch = torch
+
+    def _exchange(self, b: int, lr: float, stream) -> None:
+        from ._lib import lib, raise_last_error
+        off, n = self._buckets[b]
+        rc = lib().cleave_cuda_dp_sgd_allreduce_f32(self._tables[0], self._tables[1], self._flag_tables[b], self._mc[0],
+                                                    self._mc[1], off, n, self.rank, self.world, float(lr),
+                                                    self._epochs[b], ctypes.c_void_p(stream.cuda_stream))
+        if rc != 0:
+            raise_last_error("dp_sgd_allreduce")
+        self._epochs[b] += 2
 
     def step(self, X, T, lr: float, loss_out=None):
         """``loss_out``: optional one-element device tensor; with it the step never waits for the GPU."""
-        from ._lib import lib, raise_last_error
-        loss = self.net.forward_backward(X, T, loss_out=loss_out)
-        rc = lib().cleave_cuda_dp_sgd_allreduce_f32(self._tables[0], self._tables[1], self._tables[2], self._mc[0],
-                                                    self._mc[1], self.n_params, self.rank, self.world, float(lr),
-                                                    self.epoch)
-        if rc != 0:
-            raise_last_error("dp_sgd_allreduce")
-        self.epoch += 2
+        early = len(self._buckets) == 2
+
+        def on_ready(i: int) -> None:
+            if i == 0 and early:
+                # [dW2 | db2] are final and W2 has been consumed: exchange them beside the rest of the pass
+                self._ready.record(self._main)
+                self._side.wait_event(self._ready)
+                self._exchange(0, lr, self._side)
+                self._done.record(self._side)
+
+        loss = self.net.forward_backward(X, T, on_grads_ready=on_ready, loss_out=loss_out)
+        self._exchange(len(self._buckets) - 1, lr, self._main)
+        if early:
+            self._main.wait_event(self._done)
         return loss
 
 

@@ -57,7 +57,9 @@ enum { CLEAVE_ACT_IDENTITY = 0, CLEAVE_ACT_RELU = 1, CLEAVE_ACT_SIGMOID = 2, CLE
 enum {
   CLEAVE_GEMM_AUTO = 0,   /* tensor-core path for large problems, exact path for small ones */
   CLEAVE_GEMM_EXACT = 1,  /* SIMT f32, k-ascending multiply-then-add: bit-identical to the CPU path */
-  CLEAVE_GEMM_3XTF32 = 2  /* tcgen05 + TMEM + TMA, split-precision TF32 (3 MMAs per product) */
+  CLEAVE_GEMM_3XTF32 = 2  /* tcgen05 + TMEM + TMA, split-precision TF32 (3 MMAs per product).  Finite operands only:
+                             an infinite operand yields NaN (inf * 0 from the split) where the reference loop may
+                             yield +-inf; NaN operands propagate as NaN on both paths */
 };
 
 /* ------------------------------------------------------------------ runtime
@@ -239,13 +241,20 @@ cleave_buf cleave_cuda_gemm_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n
  * w -= lr * (sum / world) and writes the new weights into every rank's parameter buffer.
  * params_peers / grads_peers / flags_peers: `world` device pointers each, the same symmetric
  * allocations as seen from this rank (flags: >= 32 zero-initialised uint32 words per rank, used
- * for the kernel's own bounded cross-GPU barriers).  len: f32 elements, a multiple of 4.
- * epoch: 1 for the first step, then += 2 per step, identical on every rank.  All ranks must call
- * it once per step, one process per GPU.  A barrier that times out (2 s) is reported as
- * CLEAVE_CUDA_ERR_DEVICE_TIMEOUT at the next synchronisation. */
+ * for the kernel's own bounded cross-GPU barriers).  The call covers elements
+ * [offset, offset + len) of the flat vectors (both multiples of 4), so a training step can
+ * exchange the gradients in several buckets as the backward pass completes them; calls that
+ * may be in flight at the same time must use different flag words (pass flags pointers that
+ * are 32 words apart).  epoch: 1 for the first call on a set of flag words, then += 2 per call,
+ * identical on every rank.  cuda_stream: the stream to launch on (NULL = the library's), so a
+ * bucket can overlap the rest of the backward pass.  Every rank must make the same calls, one
+ * process per GPU.  A bucket may only be exchanged once no rank reads its WEIGHTS any more in
+ * this step.  A barrier that times out (2 s) is reported as CLEAVE_CUDA_ERR_DEVICE_TIMEOUT at
+ * the next synchronisation. */
 int32_t cleave_cuda_dp_sgd_allreduce_f32(void* const* params_peers, void* const* grads_peers,
                                          void* const* flags_peers, void* params_multicast, void* grads_multicast,
-                                         int64_t len, int32_t rank, int32_t world, float lr, uint32_t epoch);
+                                         int64_t offset, int64_t len, int32_t rank, int32_t world, float lr,
+                                         uint32_t epoch, void* cuda_stream);
 
 #ifdef __cplusplus
 }

@@ -149,3 +149,25 @@ def test_large_gemm_sampled_rows():
     rhs = got.astype(np.float64).sum(axis=0)
     scale = np.abs(a).astype(np.float64).sum(axis=0) @ np.abs(b).astype(np.float64)
     assert np.max(np.abs(lhs - rhs) / scale) <= TOL
+
+
+def test_non_finite_and_extreme_operands():
+    # NaN propagates on both paths; the exact path follows the reference for infinities;
+    # values next to FLT_MAX must not overflow in the hi/lo split.
+    a, b = workloads.gemm_inputs(128, 256, 64)
+    a[3, 5] = np.nan
+    got = gemm(a, b, GEMM_3XTF32)
+    want = ref.matmul(a, b)
+    assert np.isnan(got[3]).all() and np.isnan(want[3]).all()
+    ok = np.ones(128, bool)
+    ok[3] = False
+    assert_gemm_close(np.ascontiguousarray(got[ok]), np.ascontiguousarray(a[ok]), b, what="rows without NaN")
+    a[3, 5] = np.inf
+    with np.errstate(all="ignore"):
+        assert np.array_equal(gemm(a, b, GEMM_EXACT), ref.matmul(a, b), equal_nan=True)
+    big = np.zeros((128, 32), f32)
+    big[:, 0] = np.float32(3.4028234e38)          # FLT_MAX: rounds to infinity in tf32 unless truncated
+    one = np.zeros((32, 256), f32)
+    one[0, :] = 0.5
+    got = gemm(big, one, GEMM_3XTF32)
+    assert np.isfinite(got).all() and np.allclose(got, np.float32(3.4028234e38) * 0.5, rtol=1e-6)
