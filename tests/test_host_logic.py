@@ -67,3 +67,25 @@ def test_workloads_are_reproducible_and_distributed_as_stated():
     lim = np.sqrt(6.0 / (16 + 64))
     assert np.abs(W1).max() <= lim and not b1_.any() and not b2_.any()
     assert T.min() >= 0 and T.max() < 1
+
+
+def test_shard_properties_hold_for_arbitrary_sizes():
+    from hypothesis import given, settings, strategies as st
+
+    from cleave_b200 import dp
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.integers(0, 10**7), st.integers(1, 16))
+    def check(n, world):
+        spans = [dp.shard(n, r, world) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        sizes = [hi - lo for lo, hi in spans]
+        assert all(s >= 0 for s in sizes) and max(sizes) - min(sizes) <= 1
+        blocks = [dp.row_block(n, r, world) for r in range(world)]
+        assert blocks[0][0] == 0 and blocks[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+        owned = sorted(b for r in range(world) for b in dp.batch_shard(min(n, 500), r, world))
+        assert owned == list(range(min(n, 500)))
+
+    check()
