@@ -7,7 +7,6 @@ identical parameters equal to single-process training on the whole batch.
 """
 import os
 import socket
-import sys
 
 import numpy as np
 import pytest

@@ -11,7 +11,7 @@ from cleave_b200 import linalg, workloads
 from cleave_b200.linalg import GEMM_3XTF32, GEMM_EXACT
 from oracle import ref
 
-from _util import TOL, assert_gemm_close, gemm_errors, rel_err
+from _util import TOL, assert_gemm_close, rel_err
 
 pytestmark = pytest.mark.gpu
 f32 = np.float32

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 import cleave_b200 as cb
-from cleave_b200 import autodiff, linalg, nn, workloads
+from cleave_b200 import autodiff, linalg, workloads
 from oracle import ref
 
 from _util import TOL

@@ -5,7 +5,7 @@ import pytest
 from cleave_b200 import autodiff, linalg, nn, workloads
 from oracle import ref
 
-from _util import TOL, rel_err, scaled_err
+from _util import TOL, scaled_err
 
 pytestmark = pytest.mark.gpu
 f32 = np.float32
