@@ -125,6 +125,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -143,14 +151,20 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint
       : "memory");
 }
 
-// Shared-memory matrix descriptor, K-major operand, swizzled rows of `kRowBytes`:
+// Shared-memory matrix descriptor.
+// K-major operand (contraction index contiguous), swizzled rows of `kRowBytes`: start + k-step * 32 B,
+// stride byte offset = pitch of 8-row groups, leading byte offset unused.
+// MN-major operand (row / column index contiguous), 128-byte swizzle: the tile is a sequence of
+// 32-wide blocks along M or N, each block BK rows of 128 bytes; a k-step (8 rows) is 1024 bytes,
+// stride byte offset = 1024 (pitch of 8-row groups), leading byte offset = BK * 128 (pitch of blocks).
 //   bits  0-13 start address >> 4     bits 16-29 leading byte offset >> 4 (1: unused when swizzled)
 //   bits 32-45 stride byte offset >> 4 (8-row group pitch)   bits 46-47 descriptor version (1)
 //   bits 61-63 swizzle mode (2 = 128 B, 4 = 64 B)
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t sbo_bytes, uint32_t layout_type) {
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t sbo_bytes, uint32_t layout_type,
+                                                   uint32_t lbo_bytes = 16) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
   d |= (uint64_t)(sbo_bytes >> 4) << 32;
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)layout_type << 61;
@@ -158,8 +172,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 }
 
 // Instruction descriptor: f32 accumulator (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2),
-// both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// bit 15 / 16 = 1 for an MN-major A / B operand, N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t instr_desc(bool a_mn, bool b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
 
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -220,7 +237,7 @@ __device__ __forceinline__ void report(DeviceStatus* st, int code, int where, in
   __threadfence_system();
 }
 
-template <int BK>
+template <int BK, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
   using C = Cfg<BK>;
@@ -285,8 +302,10 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint32_t full = smem_u32(&bar_full[stage]);
           const uint32_t sa = ring + stage * C::kStageBytes;
           mbar_arrive_expect_tx(full, C::kStageBytes);
-          tma_load_3d(sa, &map_a, full, kb * BK, mb * BM, b * 2);
-          tma_load_3d(sa + 2 * C::kABytes, &map_b, full, kb * BK, nb * BN, b * 2);
+          if (A_MN) tma_load_4d(sa, &map_a, full, 0, kb * BK, mb * (BM / 32), b * 2);
+          else tma_load_3d(sa, &map_a, full, kb * BK, mb * BM, b * 2);
+          if (B_MN) tma_load_4d(sa + 2 * C::kABytes, &map_b, full, 0, kb * BK, nb * (BN / 32), b * 2);
+          else tma_load_3d(sa + 2 * C::kABytes, &map_b, full, kb * BK, nb * BN, b * 2);
 #pragma unroll
           for (int s = 0; s < C::kStages; ++s)
             if (s == stage) armed[s]++;
@@ -336,11 +355,17 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const uint32_t b_lo = b_hi + C::kBBytes;
 #pragma unroll
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-              const uint32_t off = kk * UMMA_K * 4;   // 32 bytes along K inside the swizzled row
-              const uint64_t da_hi = make_smem_desc(a_hi + off, C::kSBO, C::kLayoutType);
-              const uint64_t da_lo = make_smem_desc(a_lo + off, C::kSBO, C::kLayoutType);
-              const uint64_t db_hi = make_smem_desc(b_hi + off, C::kSBO, C::kLayoutType);
-              const uint64_t db_lo = make_smem_desc(b_lo + off, C::kSBO, C::kLayoutType);
+              // K-major: 32 bytes along K inside the swizzled row; MN-major: the next 8-row group
+              const uint32_t off_a = A_MN ? kk * 1024 : kk * UMMA_K * 4;
+              const uint32_t off_b = B_MN ? kk * 1024 : kk * UMMA_K * 4;
+              constexpr uint32_t sbo_a = A_MN ? 512u : C::kSBO, lay_a = A_MN ? 1u : C::kLayoutType;
+              constexpr uint32_t sbo_b = B_MN ? 512u : C::kSBO, lay_b = B_MN ? 1u : C::kLayoutType;
+              constexpr uint32_t lbo_a = A_MN ? BK * 128u : 16u, lbo_b = B_MN ? BK * 128u : 16u;
+              constexpr uint32_t kInstrDesc = instr_desc(A_MN, B_MN);
+              const uint64_t da_hi = make_smem_desc(a_hi + off_a, sbo_a, lay_a, lbo_a);
+              const uint64_t da_lo = make_smem_desc(a_lo + off_a, sbo_a, lay_a, lbo_a);
+              const uint64_t db_hi = make_smem_desc(b_hi + off_b, sbo_b, lay_b, lbo_b);
+              const uint64_t db_lo = make_smem_desc(b_lo + off_b, sbo_b, lay_b, lbo_b);
               // the first MMA of a chunk overwrites the accumulator; small terms go first
               umma_tf32(d_tmem, da_lo, db_hi, kInstrDesc, (kb != kb0 || kk != 0) ? 1u : 0u);
               umma_tf32(d_tmem, da_hi, db_lo, kInstrDesc, 1u);
@@ -483,7 +508,18 @@ __device__ __forceinline__ float tf32_round(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
   return __uint_as_float(u);
 }
+// Experiment switch (CLEAVE_CUDA_SPLIT_MODE): 0 = hi rounded to tf32 (product default);
+// 1 = hi left as the raw f32 value, lo = x - truncate_to_tf32(x); 2 = raw hi, lo = x - round_to_tf32(x).
+// Modes 1 and 2 probe what the tensor pipe does with the 13 low mantissa bits of an f32 operand.
+__constant__ int c_split_mode = 0;
+
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  if (c_split_mode != 0) {
+    const float t = c_split_mode == 1 ? __uint_as_float(__float_as_uint(x) & 0xFFFFE000u) : tf32_round(x);
+    hi = x;
+    lo = tf32_round(__fsub_rn(x, t));
+    return;
+  }
   hi = tf32_round(x);
   // A finite x just below FLT_MAX must not round up to infinity: truncate instead.
   if (fabsf(hi) == INFINITY && fabsf(x) != INFINITY) hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
@@ -571,23 +607,38 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// 3-D map over the split planes of one operand: dims {Kp, rows_p, 2*batch}, box {BK, box_rows, 2}.
-static bool make_operand_map(CUtensorMap* map, float* planes, int rows_p, int Kp, int batch, int bk, int box_rows) {
+// Tensor map over the split planes of one operand.
+// K-major planes [2*batch][rows_p][Kp]: 3-D, dims {Kp, rows_p, 2*batch}, box {BK, tile_rows, 2}.
+// MN-major planes [2*batch][Kp][rows_p]: 4-D with the row index cut into blocks of 32 so that one
+// box lands as tile_rows/32 blocks of BK rows x 128 bytes: dims {32, Kp, rows_p/32, 2*batch},
+// box {32, BK, tile_rows/32, 2}, 128-byte swizzle.
+static bool make_operand_map(CUtensorMap* map, float* planes, int rows_p, int Kp, int batch, int bk, int box_rows,
+                             bool mn_major) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) {
     set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     return false;
   }
-  cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)rows_p, (cuuint64_t)(2 * batch)};
-  cuuint64_t strides[2] = {(cuuint64_t)Kp * 4, (cuuint64_t)rows_p * Kp * 4};
-  cuuint32_t box[3] = {(cuuint32_t)bk, (cuuint32_t)box_rows, 2};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, planes, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r;
+  if (!mn_major) {
+    cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)rows_p, (cuuint64_t)(2 * batch)};
+    cuuint64_t strides[2] = {(cuuint64_t)Kp * 4, (cuuint64_t)rows_p * Kp * 4};
+    cuuint32_t box[3] = {(cuuint32_t)bk, (cuuint32_t)box_rows, 2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[4] = {32, (cuuint64_t)Kp, (cuuint64_t)(rows_p / 32), (cuuint64_t)(2 * batch)};
+    cuuint64_t strides[3] = {(cuuint64_t)rows_p * 4, 128, (cuuint64_t)rows_p * Kp * 4};
+    cuuint32_t box[4] = {32, (cuuint32_t)bk, (cuuint32_t)(box_rows / 32), 2};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) {
-    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (rows %d, K %d, batch %d)", (int)r,
-              rows_p, Kp, batch);
+    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (rows %d, K %d, batch %d, %s-major)",
+              (int)r, rows_p, Kp, batch, mn_major ? "MN" : "K");
     return false;
   }
   return true;
@@ -595,11 +646,19 @@ static bool make_operand_map(CUtensorMap* map, float* planes, int rows_p, int Kp
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+static bool g_mn_major = true;   // CLEAVE_CUDA_GEMM_MN=0: transpose such operands in the pre-pass instead
 static int g_bk = 0;   // K-block: 16 (64-byte rows, 4 stages) or 32 (128-byte rows, 2 stages)
 static int choose_bk() {
   if (g_bk == 0) {
     const char* e = getenv("CLEAVE_CUDA_GEMM_BK");
     g_bk = (e && atoi(e) == 32) ? 32 : 16;
+    const char* mn = getenv("CLEAVE_CUDA_GEMM_MN");
+    if (mn && mn[0] == '0') g_mn_major = false;
+    const char* sm = getenv("CLEAVE_CUDA_SPLIT_MODE");
+    if (sm && sm[0] >= '1' && sm[0] <= '2') {
+      const int mode = sm[0] - '0';
+      cudaMemcpyToSymbol(c_split_mode, &mode, sizeof(int));
+    }
   }
   return g_bk;
 }
@@ -610,14 +669,21 @@ bool gemm_3xtf32_supported(const GemmArgs& g) {
          (int64_t)g.batch * ceil_div(g.m, BM) * ceil_div(g.n, BN) < (1ll << 30);
 }
 
+// Writes the hi / lo planes of one operand.  `k_contiguous`: the source has the contraction index
+// contiguous ([rows][K]); otherwise it is stored [K][rows].  `mn_major`: the planes keep the
+// [K][rows] order (no transpose; the kernel reads them as an MN-major operand) -- only
+// meaningful for a source that is not k-contiguous.
 static bool split_operand(const float* src, float* dst, int batch, int rows, int K, int rows_p, int Kp,
-                          bool k_contiguous) {
+                          bool k_contiguous, bool mn_major) {
   cudaStream_t s = ctx().stream;
-  if (k_contiguous) {
-    int vec = (aligned16(src) && K % 4 == 0) ? 1 : 0;
-    int64_t items = (int64_t)rows_p * (Kp / 4);
+  if (k_contiguous || mn_major) {
+    // a padded 2-D split copy: R x C source -> Rp x Cp planes
+    const int R = k_contiguous ? rows : K, Cc = k_contiguous ? K : rows;
+    const int Rp = k_contiguous ? rows_p : Kp, Cp = k_contiguous ? Kp : rows_p;
+    int vec = (aligned16(src) && Cc % 4 == 0) ? 1 : 0;
+    int64_t items = (int64_t)Rp * (Cp / 4);
     int grid = stream_grid(items, 256, 8);
-    split_copy_kernel<<<dim3(grid, 1, batch), 256, 0, s>>>(src, dst, rows, K, rows_p, Kp, vec);
+    split_copy_kernel<<<dim3(grid, 1, batch), 256, 0, s>>>(src, dst, R, Cc, Rp, Cp, vec);
   } else {
     split_transpose_kernel<<<dim3(ceil_div(Kp, 32), ceil_div(rows_p, 32), batch), 256, 0, s>>>(src, dst, rows, K,
                                                                                                rows_p, Kp);
@@ -626,12 +692,12 @@ static bool split_operand(const float* src, float* dst, int batch, int rows, int
   return cuda_ok(cudaGetLastError(), "operand split launch");
 }
 
-template <int BK>
+template <int BK, bool A_MN, bool B_MN>
 static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
   using C = Cfg<BK>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_kernel<BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_kernel<BK, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       C::kSmemBytes),
                  "cudaFuncSetAttribute(gemm)"))
       return false;
@@ -640,7 +706,7 @@ static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams&
   const int tiles = p.batch * p.mblks * p.nblks;
   const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
   profile_mark(true);
-  gemm_3xtf32_kernel<BK><<<grid, kGemmThreads, C::kSmemBytes, ctx().stream>>>(ma, mb, p);
+  gemm_3xtf32_kernel<BK, A_MN, B_MN><<<grid, kGemmThreads, C::kSmemBytes, ctx().stream>>>(ma, mb, p);
   profile_mark(false);
   count_launch();
   return cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch");
@@ -672,12 +738,14 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     const int nb = (g.batch - b0) < chunk ? (g.batch - b0) : chunk;
     const float* a = g.a + (int64_t)b0 * g.m * g.k;
     const float* b = g.b + (int64_t)b0 * g.k * g.n;
-    // A is K-contiguous when stored [m,k]; B is K-contiguous when stored [n,k].
-    ok = split_operand(a, wa, nb, g.m, g.k, Mp, Kp, g.trans_a == 0) &&
-         split_operand(b, wb, nb, g.n, g.k, Np, Kp, g.trans_b != 0);
+    // A is K-contiguous when stored [m,k]; B is K-contiguous when stored [n,k].  An operand stored
+    // the other way round is left in that order and read as an MN-major operand (no transpose).
+    const bool a_mn = g.trans_a != 0 && g_mn_major, b_mn = g.trans_b == 0 && g_mn_major;
+    ok = split_operand(a, wa, nb, g.m, g.k, Mp, Kp, g.trans_a == 0, a_mn) &&
+         split_operand(b, wb, nb, g.n, g.k, Np, Kp, g.trans_b != 0, b_mn);
     if (!ok) break;
     CUtensorMap ma, mb;
-    ok = make_operand_map(&ma, wa, Mp, Kp, nb, bk, BM) && make_operand_map(&mb, wb, Np, Kp, nb, bk, BN);
+    ok = make_operand_map(&ma, wa, Mp, Kp, nb, bk, BM, a_mn) && make_operand_map(&mb, wb, Np, Kp, nb, bk, BN, b_mn);
     if (!ok) break;
     TcParams p;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
@@ -691,7 +759,13 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.nblks = Np / BN;
     p.act = g.act;
     p.status = ctx().status_dev;
-    ok = bk == 32 ? run_tc<32>(ma, mb, p) : run_tc<16>(ma, mb, p);
+    if (bk == 32) {
+      ok = a_mn ? (b_mn ? run_tc<32, true, true>(ma, mb, p) : run_tc<32, true, false>(ma, mb, p))
+                : (b_mn ? run_tc<32, false, true>(ma, mb, p) : run_tc<32, false, false>(ma, mb, p));
+    } else {
+      ok = a_mn ? (b_mn ? run_tc<16, true, true>(ma, mb, p) : run_tc<16, true, false>(ma, mb, p))
+                : (b_mn ? run_tc<16, false, true>(ma, mb, p) : run_tc<16, false, false>(ma, mb, p));
+    }
   }
   scratch_free(wa);
   scratch_free(wb);
