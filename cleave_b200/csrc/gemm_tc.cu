@@ -2,26 +2,40 @@
 // staged by TMA into a multi-stage shared-memory ring guarded by mbarriers, and a 3xTF32
 // split so that the f32 result stays within rounding distance of the reference's f32 loop.
 //
-// Split precision.  Every f32 operand value x is written as hi + lo with
-//   hi = tf32(x)  (round to nearest, 10 explicit mantissa bits),  lo = tf32(x - hi),
-// and a*b is accumulated as  a_lo*b_hi + a_hi*b_lo + a_hi*b_hi  in the f32 TMEM accumulator.
-// The dropped a_lo*b_lo term and the rounding of lo are each <= 2^-22 |a b|.
+// Split precision.  Every f32 operand value x is used as hi + lo and a*b is accumulated as
+// a_lo*b_hi + a_hi*b_lo + a_hi*b_hi in the f32 TMEM accumulator.  Two ways to get the planes:
+//   pre-pass path   hi = tf32(x) (round to nearest), lo = tf32(x - hi); dropped a_lo*b_lo and the
+//                   rounding of lo are each <= 2^-22 |a b|
+//   direct path     hi = x as the tensor pipe reads it: the pipe ignores the 13 low mantissa bits of an
+//                   f32 operand (measured), i.e. truncates; lo = tf32(x - truncate(x)), exact
+//                   subtraction, so the terms above are <= 2^-20 / 2^-21 |a b|
+// Both stay an order of magnitude inside the 1e-5 tolerance (measured ~5e-7 componentwise).
 //
-// Data path.  A pre-pass writes both operands K-major (the contraction index contiguous) as two
-// planes [hi | lo] of shape [rows_padded, K_padded], transposing where the caller's layout has
-// the other index contiguous; this makes NN / NT / TN one kernel.  Padding (rows to the tile
-// height, K to the K-block) is zero-filled so every TMA box is fully in bounds.
+// Data path, pre-pass.  split_copy_kernel writes both operands as two planes [hi | lo], padded
+// (rows to the tile height, K to 32) and zero-filled so every TMA box is in bounds; an operand whose
+// contraction index is strided keeps its [K][rows] order and is read as an MN-major operand.
+// Data path, direct.  TMA reads the caller's tensors themselves (16-byte aligned, contiguous extent
+// a multiple of 4; out-of-range parts of a box read as zero) into a deep ring of raw stages, and
+// four "split" warps write the lo planes of each stage into a second, shallow ring just ahead of
+// the MMAs.  No workspace and no extra HBM pass, but the split warps' shared-memory traffic competes
+// with the MMAs' operand reads, so the kernel itself runs ~1.2x longer: the host picks this path
+// for small and narrow problems, where the pre-pass would cost more than that.
 //
-// Kernel.  Persistent, one CTA per SM, 192 threads:
-//   warp 0      TMA producer (one elected lane): per K-block one 3-D box per operand
-//               {BK, rows, 2 planes} -> shared memory, completion on the stage's "full" mbarrier
-//   warp 1      MMA issuer (one elected lane): 3 x (BK/8) tcgen05.mma per K-block into one of two
-//               128x256 f32 accumulators in TMEM; tcgen05.commit releases the stage ("empty")
-//               and, after each K-chunk, publishes the accumulator ("tmem_full")
-//   warps 2-9   drain + epilogue: after every K-chunk (256 values of k) tcgen05.ld the chunk's
-//               partial sums and add them, round-to-nearest, to 128 running sums per thread in
-//               registers; hand the accumulator back ("tmem_empty"); after the last chunk apply
-//               bias + activation and store C with 128-bit stores
+// Kernel.  Persistent, one CTA per SM; 320 threads (pre-pass path) or 512 (direct path):
+//   producer    one elected lane: per K-block one TMA box per operand -> shared memory, completion
+//               on the stage's "full" mbarrier
+//   MMA issuer  one elected lane: 3 x (BK/8) tcgen05.mma per K-block into one of two 128x256 f32
+//               accumulators in TMEM; tcgen05.commit releases the stage ("empty") and, after each
+//               K-chunk, publishes the accumulator ("tmem_full").  On the last tile column the
+//               MMA's N shrinks to the live columns of C.
+//   8 drain     after every K-chunk (256 values of k) tcgen05.ld the chunk's partial sums and add
+//   warps       them, round-to-nearest, to 128 running sums per thread in registers; hand the
+//               accumulator back ("tmem_empty"); after the last chunk apply bias + activation and
+//               store C through a swizzled shared tile with full 128-byte lines
+//   4 split     direct path only: raw stage -> lo stage, then fence.proxy.async and an arrival on
+//   warps       the lo stage's "lo_full" mbarrier, which the issuer waits for
+// On the direct path the warps form four warpgroups and registers move (setmaxnreg) from the
+// producer/issuer and split groups to the drain groups.
 // The two TMEM accumulators alternate per chunk, so draining chunk i overlaps the MMAs of
 // chunk i+1 (and the stores of one tile overlap the first chunk of the next).
 //
@@ -51,24 +65,41 @@ constexpr int BM = 128;          // tile rows  (UMMA M)
 constexpr int BN = 256;          // tile cols  (UMMA N)
 constexpr int UMMA_K = 8;        // tf32 MMA K (32 bytes)
 constexpr int kEpiWarps = 8;     // two per TMEM lane quarter, 128 columns each
-constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;     // producer, issuer, drain warps
+// Direct path (the kernel splits raw operands itself): four warpgroups.  0: producer, issuer and
+// two idle warps; 1-2: drain warps; 3: split warps.  Registers move from groups 0 and 3 to the
+// drain groups (setmaxnreg), whose 128 running sums per thread do not fit the 128 registers that
+// 512 threads would get each.
+constexpr int kSplitWarps = 4;
+constexpr int kDirectThreads = 512;
+constexpr int kRegsLight = 64, kRegsSplit = 72, kRegsDrain = 184;   // 128*64 + 128*72 + 256*184 <= 65536
 constexpr int kChunkK = 256;     // k values accumulated in TMEM before a drain into registers
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = kAccStages * BN;   // 512: all of TMEM
 constexpr int kGroupM = 16;      // tile-rows per rasterisation group
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s per wait
 
-template <int BK>
+#ifndef CLEAVE_RAW_STAGES
+#define CLEAVE_RAW_STAGES 6
+#endif
+// Shared-memory plan.  Pre-pass path: kStages stages of [A hi | A lo | B hi | B lo], all written by
+// TMA.  Direct path: a deep ring of raw stages [A | B] written by TMA plus a shallow ring of lo
+// stages [A lo | B lo] written by the split warps just ahead of the MMAs, so the depth that hides
+// the TMA latency costs 24 KiB per stage instead of 48.
+template <int BK, bool DIRECT>
 struct Cfg {
-  static_assert(BK == 16 || BK == 32, "BK must give a 64- or 128-byte row");
+  static_assert(BK == 16, "one K-block size is built: 64-byte rows (K-major) / 16 rows of 128 bytes (MN-major)");
   static constexpr int kRowBytes = BK * 4;
-  static constexpr int kStages = BK == 32 ? 2 : 4;
   static constexpr int kABytes = BM * kRowBytes;          // one plane of A
   static constexpr int kBBytes = BN * kRowBytes;          // one plane of B
-  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+  static constexpr int kStages = DIRECT ? CLEAVE_RAW_STAGES : 4;        // ring that TMA fills
+  static constexpr int kLoStages = DIRECT ? 8 - CLEAVE_RAW_STAGES : 1;  // direct path: ring of lo planes
+  static constexpr int kStageBytes = DIRECT ? kABytes + kBBytes : 2 * (kABytes + kBBytes);
+  static constexpr int kLoRingOffset = kStages * kStageBytes;
+  static constexpr int kRingBytes = kLoRingOffset + (DIRECT ? kLoStages * (kABytes + kBBytes) : 0);
   static constexpr int kStoreStageBytes = kEpiWarps * 32 * 128;      // per drain warp: 32 rows x 32 floats
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreStageBytes + 1024;   // + alignment slack
-  static constexpr uint32_t kLayoutType = BK == 32 ? 2u : 4u;       // SWIZZLE_128B : SWIZZLE_64B
+  static constexpr int kSmemBytes = kRingBytes + kStoreStageBytes + 1024;   // + alignment slack
+  static constexpr uint32_t kLayoutType = 4u;                       // K-major planes: SWIZZLE_64B
   static constexpr uint32_t kSBO = 8 * kRowBytes;                   // bytes between 8-row groups
 };
 
@@ -154,12 +185,14 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint
 // Shared-memory matrix descriptor.
 // K-major operand (contraction index contiguous), swizzled rows of `kRowBytes`: start + k-step * 32 B,
 // stride byte offset = pitch of 8-row groups, leading byte offset unused.
-// MN-major operand (row / column index contiguous), 128-byte swizzle: the tile is a sequence of
-// 32-wide blocks along M or N, each block BK rows of 128 bytes; a k-step (8 rows) is 1024 bytes,
-// stride byte offset = 1024 (pitch of 8-row groups), leading byte offset = BK * 128 (pitch of blocks).
+// MN-major operand (row / column index contiguous): for 4-byte elements the only layout the tensor
+// pipe takes is the 128-byte swizzle with 32-byte atoms (TMA: CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B).
+// The tile is a sequence of 32-wide blocks along M or N, each block BK rows of 128 bytes; the
+// swizzle pattern spans 4 rows (512 bytes), a k-step (8 rows) is 1024 bytes, stride byte offset =
+// 512 (pitch of 4-row groups), leading byte offset = BK * 128 (pitch of blocks).
 //   bits  0-13 start address >> 4     bits 16-29 leading byte offset >> 4 (1: unused when swizzled)
 //   bits 32-45 stride byte offset >> 4 (8-row group pitch)   bits 46-47 descriptor version (1)
-//   bits 61-63 swizzle mode (2 = 128 B, 4 = 64 B)
+//   bits 61-63 swizzle mode (1 = 128 B with 32-byte atoms, 2 = 128 B, 4 = 64 B)
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t sbo_bytes, uint32_t layout_type,
                                                    uint32_t lbo_bytes = 16) {
   uint64_t d = 0;
@@ -173,9 +206,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 
 // Instruction descriptor: f32 accumulator (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2),
 // bit 15 / 16 = 1 for an MN-major A / B operand, N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-__host__ __device__ constexpr uint32_t instr_desc(bool a_mn, bool b_mn) {
+__host__ __device__ constexpr uint32_t instr_desc(bool a_mn, bool b_mn, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -201,6 +234,15 @@ __device__ __forceinline__ float act_apply(float v, int act) {
   }
 }
 
+// Low part of the in-kernel split: d = x minus x with its 13 low mantissa bits cleared (exact), then
+// half a tf32 unit is added to d's magnitude so that the tensor pipe's own truncation of the 13 low
+// bits rounds d to the nearest tf32 value.  Integer / full-rate instructions only: a cvt per
+// element would make the split warps slower than the MMAs they feed.
+__device__ __forceinline__ float split_lo(float x) {
+  const float d = __fsub_rn(x, __uint_as_float(__float_as_uint(x) & 0xFFFFE000u));
+  return __uint_as_float(__float_as_uint(d) + 0x1000u);
+}
+
 struct TcParams {
   float* c;             // [batch][m][n]
   const float* bias;    // [n] or null
@@ -209,6 +251,8 @@ struct TcParams {
   int chunk_kb;         // K-blocks per accumulation chunk (kChunkK / BK)
   int batch, mblks, nblks;
   int act;
+  int a_blocked, b_blocked;   // direct path, MN-major operand: one 4-D box per stage instead of 32-wide boxes
+  int b_box_rows;             // direct path: rows of B fetched and split per stage (BN, less when n is small)
   DeviceStatus* status;
 };
 
@@ -237,13 +281,15 @@ __device__ __forceinline__ void report(DeviceStatus* st, int code, int where, in
   __threadfence_system();
 }
 
-template <int BK, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BK, bool A_MN, bool B_MN, bool DIRECT>
+__global__ void __launch_bounds__(DIRECT ? kDirectThreads : kGemmThreads, 1)
 gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
-  using C = Cfg<BK>;
+  using C = Cfg<BK, DIRECT>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
   __shared__ __align__(8) uint64_t bar_empty[C::kStages];
+  __shared__ __align__(8) uint64_t bar_lo_full[C::kLoStages];    // direct path: lo planes written
+  __shared__ __align__(8) uint64_t bar_lo_empty[C::kLoStages];   // direct path: lo planes consumed
   __shared__ __align__(8) uint64_t bar_tmem_full[kAccStages];
   __shared__ __align__(8) uint64_t bar_tmem_empty[kAccStages];
   __shared__ uint32_t tmem_slot;
@@ -251,6 +297,8 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  constexpr int kDrainFirst = DIRECT ? 4 : 2;                 // first of the kEpiWarps drain warps
+  constexpr int kSplitFirst = kDrainFirst + kEpiWarps;        // direct path only
   // Operand ring, 1024-byte aligned (the swizzle pattern is a function of address bits 4-9).
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int total_tiles = p.batch * p.mblks * p.nblks;
@@ -260,6 +308,10 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int s = 0; s < C::kLoStages; ++s) {
+      mbar_init(smem_u32(&bar_lo_full[s]), 32 * kSplitWarps);   // every split thread arrives
+      mbar_init(smem_u32(&bar_lo_empty[s]), 1);
     }
     for (int a = 0; a < kAccStages; ++a) {
       mbar_init(smem_u32(&bar_tmem_full[a]), 1);
@@ -279,6 +331,8 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
+  if (warp < kDrainFirst) {
+  if constexpr (DIRECT) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLight));
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -301,11 +355,40 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           }
           const uint32_t full = smem_u32(&bar_full[stage]);
           const uint32_t sa = ring + stage * C::kStageBytes;
-          mbar_arrive_expect_tx(full, C::kStageBytes);
-          if (A_MN) tma_load_4d(sa, &map_a, full, 0, kb * BK, mb * (BM / 32), b * 2);
-          else tma_load_3d(sa, &map_a, full, kb * BK, mb * BM, b * 2);
-          if (B_MN) tma_load_4d(sa + 2 * C::kABytes, &map_b, full, 0, kb * BK, nb * (BN / 32), b * 2);
-          else tma_load_3d(sa + 2 * C::kABytes, &map_b, full, kb * BK, nb * BN, b * 2);
+          if constexpr (DIRECT) {
+            // Raw f32 tiles straight from the caller's tensors (out-of-range parts read as zero).
+            // An MN-major tile is fetched as 32-wide blocks of BK rows x 128 bytes.
+            const uint32_t sb = sa + C::kABytes;
+            mbar_arrive_expect_tx(full, C::kABytes + p.b_box_rows * C::kRowBytes);
+            if (A_MN) {
+              if (p.a_blocked) {
+                tma_load_4d(sa, &map_a, full, 0, kb * BK, mb * (BM / 32), b);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BM / 32; ++j)
+                  tma_load_3d(sa + j * (BK * 128), &map_a, full, mb * BM + j * 32, kb * BK, b);
+              }
+            } else {
+              tma_load_3d(sa, &map_a, full, kb * BK, mb * BM, b);
+            }
+            if (B_MN) {
+              if (p.b_blocked) {
+                tma_load_4d(sb, &map_b, full, 0, kb * BK, nb * (BN / 32), b);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BN / 32; ++j)
+                  if (j * 32 < p.b_box_rows) tma_load_3d(sb + j * (BK * 128), &map_b, full, nb * BN + j * 32, kb * BK, b);
+              }
+            } else {
+              tma_load_3d(sb, &map_b, full, kb * BK, nb * BN, b);
+            }
+          } else {
+            mbar_arrive_expect_tx(full, C::kStageBytes);
+            if (A_MN) tma_load_4d(sa, &map_a, full, 0, kb * BK, mb * (BM / 32), b * 2);
+            else tma_load_3d(sa, &map_a, full, kb * BK, mb * BM, b * 2);
+            if (B_MN) tma_load_4d(sa + 2 * C::kABytes, &map_b, full, 0, kb * BK, nb * (BN / 32), b * 2);
+            else tma_load_3d(sa + 2 * C::kABytes, &map_b, full, kb * BK, nb * BN, b * 2);
+          }
 #pragma unroll
           for (int s = 0; s < C::kStages; ++s)
             if (s == stage) armed[s]++;
@@ -327,12 +410,18 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
+      int stage = 0, slot = 0;
+      uint32_t phase = 0, lo_phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        // Columns past the edge of C need no arithmetic: the MMA's N shrinks to the live part of
+        // the tile (a multiple of 16); the accumulator columns beyond it are never stored.
+        int tb, tmb, tnb;
+        decode_tile(t, p, tb, tmb, tnb);
+        const int live_n = (p.n - tnb * BN) < BN ? (p.n - tnb * BN) : BN;
+        const uint32_t idesc = instr_desc(A_MN, B_MN, (live_n + 15) & ~15);
         for (int kb0 = 0; ok && kb0 < p.num_kb; kb0 += p.chunk_kb) {
           if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
             report(p.status, 2, 200 + acc, t);
@@ -343,16 +432,17 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
           const int kb_end = (kb0 + p.chunk_kb) < p.num_kb ? (kb0 + p.chunk_kb) : p.num_kb;
           for (int kb = kb0; kb < kb_end; ++kb) {
-            if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
+            if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag) ||
+                (DIRECT && !mbar_wait(smem_u32(&bar_lo_full[slot]), lo_phase, &abort_flag))) {
               report(p.status, 3, 300 + stage, kb);
               ok = false;
               break;
             }
             tcgen05_fence_after();
             const uint32_t a_hi = ring + stage * C::kStageBytes;
-            const uint32_t a_lo = a_hi + C::kABytes;
-            const uint32_t b_hi = a_hi + 2 * C::kABytes;
-            const uint32_t b_lo = b_hi + C::kBBytes;
+            const uint32_t a_lo = DIRECT ? ring + C::kLoRingOffset + slot * (C::kABytes + C::kBBytes) : a_hi + C::kABytes;
+            const uint32_t b_hi = DIRECT ? a_hi + C::kABytes : a_hi + 2 * C::kABytes;
+            const uint32_t b_lo = DIRECT ? a_lo + C::kABytes : b_hi + C::kBBytes;
 #pragma unroll
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
               // K-major: 32 bytes along K inside the swizzled row; MN-major: the next 8-row group
@@ -361,18 +451,21 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
               constexpr uint32_t sbo_a = A_MN ? 512u : C::kSBO, lay_a = A_MN ? 1u : C::kLayoutType;
               constexpr uint32_t sbo_b = B_MN ? 512u : C::kSBO, lay_b = B_MN ? 1u : C::kLayoutType;
               constexpr uint32_t lbo_a = A_MN ? BK * 128u : 16u, lbo_b = B_MN ? BK * 128u : 16u;
-              constexpr uint32_t kInstrDesc = instr_desc(A_MN, B_MN);
               const uint64_t da_hi = make_smem_desc(a_hi + off_a, sbo_a, lay_a, lbo_a);
               const uint64_t da_lo = make_smem_desc(a_lo + off_a, sbo_a, lay_a, lbo_a);
               const uint64_t db_hi = make_smem_desc(b_hi + off_b, sbo_b, lay_b, lbo_b);
               const uint64_t db_lo = make_smem_desc(b_lo + off_b, sbo_b, lay_b, lbo_b);
               // the first MMA of a chunk overwrites the accumulator; small terms go first
-              umma_tf32(d_tmem, da_lo, db_hi, kInstrDesc, (kb != kb0 || kk != 0) ? 1u : 0u);
-              umma_tf32(d_tmem, da_hi, db_lo, kInstrDesc, 1u);
-              umma_tf32(d_tmem, da_hi, db_hi, kInstrDesc, 1u);
+              umma_tf32(d_tmem, da_lo, db_hi, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+              umma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+              umma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
             }
             tcgen05_commit(smem_u32(&bar_empty[stage]));   // stage reusable once these MMAs retire
             if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+            if constexpr (DIRECT) {
+              tcgen05_commit(smem_u32(&bar_lo_empty[slot]));
+              if (++slot == C::kLoStages) { slot = 0; lo_phase ^= 1u; }
+            }
           }
           if (!ok) break;
           tcgen05_commit(smem_u32(&bar_tmem_full[acc]));   // chunk complete
@@ -380,10 +473,63 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
       }
     }
+  }
+  } else if (DIRECT && warp >= kSplitFirst) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsSplit));
+    // ------------------------------------------------------------------ operand split (warps 12..15)
+    // The tensor pipe reads an f32 operand as tf32 by dropping its 13 low mantissa bits, so the raw
+    // tile itself serves as the hi plane.  These warps write the matching lo plane,
+    // lo = tf32(x - truncate(x)), at the same (swizzled) offsets of the stage's lo buffers; the
+    // subtraction is exact.  A non-finite x gives lo = NaN, as documented for this path.
+    const int st = threadIdx.x - 32 * kSplitFirst;
+    uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    int stage = 0, slot = 0;
+    uint32_t phase = 0, lo_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag) ||
+            !mbar_wait(smem_u32(&bar_lo_empty[slot]), lo_phase ^ 1u, &abort_flag)) {
+          if (lane == 0) report(p.status, 6, 600 + stage, kb);
+          ok = false;
+          break;
+        }
+        const float4* a_raw = reinterpret_cast<const float4*>(ring_ptr + stage * C::kStageBytes);
+        const float4* b_raw = a_raw + C::kABytes / 16;
+        float4* a_lo = reinterpret_cast<float4*>(ring_ptr + C::kLoRingOffset + slot * (C::kABytes + C::kBBytes));
+        float4* b_lo = a_lo + C::kABytes / 16;
+        constexpr int kA4 = C::kABytes / 16 / (32 * kSplitWarps), kB4 = C::kBBytes / 16 / (32 * kSplitWarps);
+        float4 v[kA4 + kB4];
+#pragma unroll
+        for (int i = 0; i < kA4; ++i) v[i] = a_raw[st + i * 32 * kSplitWarps];
+        const int b_f4 = p.b_box_rows * (C::kRowBytes / 16);   // 16-byte words of B present in the stage
+#pragma unroll
+        for (int i = 0; i < kB4; ++i)
+          if (st + i * 32 * kSplitWarps < b_f4) v[kA4 + i] = b_raw[st + i * 32 * kSplitWarps];
+#pragma unroll
+        for (int i = 0; i < kA4 + kB4; ++i) {
+          v[i].x = split_lo(v[i].x);
+          v[i].y = split_lo(v[i].y);
+          v[i].z = split_lo(v[i].z);
+          v[i].w = split_lo(v[i].w);
+        }
+#pragma unroll
+        for (int i = 0; i < kA4; ++i) a_lo[st + i * 32 * kSplitWarps] = v[i];
+#pragma unroll
+        for (int i = 0; i < kB4; ++i)
+          if (st + i * 32 * kSplitWarps < b_f4) b_lo[st + i * 32 * kSplitWarps] = v[kA4 + i];
+        // make these generic-proxy writes visible to the tensor pipe's (async-proxy) reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(smem_u32(&bar_lo_full[slot]));
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        if (++slot == C::kLoStages) { slot = 0; lo_phase ^= 1u; }
+      }
+    }
   } else {
-    // ------------------------------------------------------------------ drain + epilogue (warps 2..9)
+    // ------------------------------------------------------------------ drain + epilogue (kEpiWarps warps)
+    if constexpr (DIRECT) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsDrain));
     const int q = warp & 3;             // TMEM lane quarter this warp may read: lanes 32q .. 32q+31
-    const int half = (warp - 2) >> 2;   // which 128 of the tile's 256 columns
+    const int half = (warp - kDrainFirst) >> 2;   // which 128 of the tile's 256 columns
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = (p.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0);
@@ -470,7 +616,7 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // warp-private shared tile (word j of row r at slot j ^ (r & 7): conflict free both ways)
         // and the warp then writes 4 rows x 128 bytes per instruction.
         float4* stage = reinterpret_cast<float4*>(smem_raw + (ring - smem_u32(smem_raw)) +
-                                                  C::kStages * C::kStageBytes) + (warp - 2) * (32 * 8);
+                                                  C::kRingBytes) + (warp - kDrainFirst) * (32 * 8);
         float* cblock = p.c + ((int64_t)b * p.m + mb * BM + q * 32) * (int64_t)p.n + col0;
 #pragma unroll
         for (int pass = 0; pass < BN / 64; ++pass) {
@@ -508,18 +654,7 @@ __device__ __forceinline__ float tf32_round(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
   return __uint_as_float(u);
 }
-// Experiment switch (CLEAVE_CUDA_SPLIT_MODE): 0 = hi rounded to tf32 (product default);
-// 1 = hi left as the raw f32 value, lo = x - truncate_to_tf32(x); 2 = raw hi, lo = x - round_to_tf32(x).
-// Modes 1 and 2 probe what the tensor pipe does with the 13 low mantissa bits of an f32 operand.
-__constant__ int c_split_mode = 0;
-
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-  if (c_split_mode != 0) {
-    const float t = c_split_mode == 1 ? __uint_as_float(__float_as_uint(x) & 0xFFFFE000u) : tf32_round(x);
-    hi = x;
-    lo = tf32_round(__fsub_rn(x, t));
-    return;
-  }
   hi = tf32_round(x);
   // A finite x just below FLT_MAX must not round up to infinity: truncate instead.
   if (fabsf(hi) == INFINITY && fabsf(x) != INFINITY) hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
@@ -646,21 +781,19 @@ static bool make_operand_map(CUtensorMap* map, float* planes, int rows_p, int Kp
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
-static bool g_mn_major = true;   // CLEAVE_CUDA_GEMM_MN=0: transpose such operands in the pre-pass instead
-static int g_bk = 0;   // K-block: 16 (64-byte rows, 4 stages) or 32 (128-byte rows, 2 stages)
-static int choose_bk() {
-  if (g_bk == 0) {
-    const char* e = getenv("CLEAVE_CUDA_GEMM_BK");
-    g_bk = (e && atoi(e) == 32) ? 32 : 16;
-    const char* mn = getenv("CLEAVE_CUDA_GEMM_MN");
-    if (mn && mn[0] == '0') g_mn_major = false;
-    const char* sm = getenv("CLEAVE_CUDA_SPLIT_MODE");
-    if (sm && sm[0] >= '1' && sm[0] <= '2') {
-      const int mode = sm[0] - '0';
-      cudaMemcpyToSymbol(c_split_mode, &mode, sizeof(int));
-    }
-  }
-  return g_bk;
+// Switches for measurements (read once).  CLEAVE_CUDA_GEMM_DIRECT: 0 = every problem goes through the
+// split pre-pass, 2 = every addressable problem is split in the kernel, otherwise the choice below.
+// CLEAVE_CUDA_GEMM_MN=0 makes the pre-pass transpose instead of writing MN-major planes.
+static bool g_mn_major = true;
+static int g_direct = 1;
+static void read_options() {
+  static bool done = false;
+  if (done) return;
+  done = true;
+  const char* mn = getenv("CLEAVE_CUDA_GEMM_MN");
+  if (mn && mn[0] == '0') g_mn_major = false;
+  const char* d = getenv("CLEAVE_CUDA_GEMM_DIRECT");
+  if (d && (d[0] == '0' || d[0] == '2')) g_direct = d[0] - '0';
 }
 
 bool gemm_3xtf32_supported(const GemmArgs& g) {
@@ -692,13 +825,13 @@ static bool split_operand(const float* src, float* dst, int batch, int rows, int
   return cuda_ok(cudaGetLastError(), "operand split launch");
 }
 
-template <int BK, bool A_MN, bool B_MN>
+template <int BK, bool A_MN, bool B_MN, bool DIRECT>
 static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
-  using C = Cfg<BK>;
+  using C = Cfg<BK, DIRECT>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_kernel<BK, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      C::kSmemBytes),
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_kernel<BK, A_MN, B_MN, DIRECT>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes),
                  "cudaFuncSetAttribute(gemm)"))
       return false;
     attr_set = true;
@@ -706,10 +839,97 @@ static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams&
   const int tiles = p.batch * p.mblks * p.nblks;
   const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
   profile_mark(true);
-  gemm_3xtf32_kernel<BK, A_MN, B_MN><<<grid, kGemmThreads, C::kSmemBytes, ctx().stream>>>(ma, mb, p);
+  gemm_3xtf32_kernel<BK, A_MN, B_MN, DIRECT>
+      <<<grid, DIRECT ? kDirectThreads : kGemmThreads, C::kSmemBytes, ctx().stream>>>(ma, mb, p);
   profile_mark(false);
   count_launch();
   return cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch");
+}
+
+template <bool DIRECT>
+static bool run_tc_layout(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
+  return a_mn ? (b_mn ? run_tc<16, true, true, DIRECT>(ma, mb, p) : run_tc<16, true, false, DIRECT>(ma, mb, p))
+              : (b_mn ? run_tc<16, false, true, DIRECT>(ma, mb, p) : run_tc<16, false, false, DIRECT>(ma, mb, p));
+}
+
+// Tensor map straight over a caller's operand ([batch] matrices, row-major, unpadded).
+// `k_contiguous` ([rows][K]): dims {K, rows, batch}, box {BK, tile_rows, 1}, 64-byte swizzle.
+// Otherwise ([K][rows], read MN-major), 128-byte swizzle with 32-byte atoms, either
+//   blocked (rows a multiple of 32): dims {32, K, rows/32, batch}, box {32, BK, tile_rows/32, 1} -- one box
+//   per stage lands as tile_rows/32 blocks of BK rows x 128 bytes; or
+//   plain: dims {rows, K, batch}, box {32, BK, 1}; the kernel issues tile_rows/32 such boxes per stage.
+// Needs a 16-byte aligned base and a contiguous extent that is a multiple of 4 elements.
+static bool make_direct_map(CUtensorMap* map, const float* base, int rows, int K, int batch, bool k_contiguous,
+                            int tile_rows, bool blocked) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  const cuuint64_t inner = k_contiguous ? K : rows, outer = k_contiguous ? rows : K;
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r;
+  if (blocked) {
+    cuuint64_t dims[4] = {32, (cuuint64_t)K, (cuuint64_t)(rows / 32), (cuuint64_t)batch};
+    cuuint64_t strides[3] = {(cuuint64_t)rows * 4, 128, (cuuint64_t)rows * K * 4};
+    cuuint32_t box[4] = {32, 16, (cuuint32_t)(tile_rows / 32), 1};
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[3] = {inner, outer, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {inner * 4, inner * outer * 4};
+    cuuint32_t box[3] = {k_contiguous ? 16u : 32u, k_contiguous ? (cuuint32_t)tile_rows : 16u, 1};
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE,
+            k_contiguous ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS) {
+    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (operand %d x %d, batch %d)", (int)r,
+              rows, K, batch);
+    return false;
+  }
+  return true;
+}
+
+// The kernel can read the caller's tensors itself when TMA can address them.  Splitting in the
+// kernel costs shared-memory bandwidth that the MMAs also need (measured: the kernel runs ~1.2x
+// longer), the pre-pass costs one HBM round trip over both operands; the pre-pass is the cheaper of
+// the two once 1/M + 1/N drops below ~1/1300 (large, square-ish outputs).
+static bool direct_eligible(const GemmArgs& g) {
+  if (g_direct == 0) return false;
+  const int a_inner = g.trans_a ? g.m : g.k, b_inner = g.trans_b ? g.k : g.n;
+  if (!(aligned16(g.a) && aligned16(g.b) && a_inner % 4 == 0 && b_inner % 4 == 0)) return false;
+  if (g_direct == 2) return true;
+  return (int64_t)g.m * g.n < 1300ll * ((int64_t)g.m + g.n);
+}
+
+static bool launch_direct(const GemmArgs& g) {
+  const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
+  const bool a_blocked = a_mn && g.m % 32 == 0, b_blocked = b_mn && g.n % 32 == 0;
+  // A narrow C needs only the first round_up(n, 32) rows of each B tile.
+  const int b_box_rows = g.n < BN ? round_up(g.n, 32) : BN;
+  CUtensorMap ma, mb;
+  if (!make_direct_map(&ma, g.a, g.m, g.k, g.batch, !a_mn, BM, a_blocked) ||
+      !make_direct_map(&mb, g.b, g.n, g.k, g.batch, !b_mn, b_box_rows, b_blocked))
+    return false;
+  TcParams p;
+  p.a_blocked = a_blocked;
+  p.b_blocked = b_blocked;
+  p.b_box_rows = b_box_rows;
+  p.c = g.c;
+  p.bias = g.bias;
+  p.m = g.m;
+  p.n = g.n;
+  p.num_kb = ceil_div(g.k, 16);
+  p.chunk_kb = kChunkK / 16;
+  p.batch = g.batch;
+  p.mblks = ceil_div(g.m, BM);
+  p.nblks = ceil_div(g.n, BN);
+  p.act = g.act;
+  p.status = ctx().status_dev;
+  return run_tc_layout<true>(a_mn, b_mn, ma, mb, p);
 }
 
 bool launch_gemm_3xtf32(const GemmArgs& g) {
@@ -718,8 +938,10 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
               g.k, g.batch);
     return false;
   }
-  const int bk = choose_bk();
-  const int Kp = round_up(g.k, 32);        // multiple of both K-block sizes
+  read_options();
+  if (direct_eligible(g)) return launch_direct(g);
+  const int bk = 16;
+  const int Kp = round_up(g.k, 32);
   const int Mp = round_up(g.m, BM);
   const int Np = round_up(g.n, BN);
   // Bound the split workspace: process the batch in chunks of at most ~4 GiB of planes.
@@ -758,14 +980,10 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.mblks = Mp / BM;
     p.nblks = Np / BN;
     p.act = g.act;
+    p.a_blocked = p.b_blocked = 0;
+    p.b_box_rows = BN;
     p.status = ctx().status_dev;
-    if (bk == 32) {
-      ok = a_mn ? (b_mn ? run_tc<32, true, true>(ma, mb, p) : run_tc<32, true, false>(ma, mb, p))
-                : (b_mn ? run_tc<32, false, true>(ma, mb, p) : run_tc<32, false, false>(ma, mb, p));
-    } else {
-      ok = a_mn ? (b_mn ? run_tc<16, true, true>(ma, mb, p) : run_tc<16, true, false>(ma, mb, p))
-                : (b_mn ? run_tc<16, false, true>(ma, mb, p) : run_tc<16, false, false>(ma, mb, p));
-    }
+    ok = run_tc_layout<false>(a_mn, b_mn, ma, mb, p);
   }
   scratch_free(wa);
   scratch_free(wb);
