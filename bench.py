@@ -295,6 +295,8 @@ def run_gemm_sweep(args):
     shapes = [(1024,) * 3, (2048,) * 3, (4096,) * 3, (8192,) * 3, (16384,) * 3, (16384, 16384, 64), (16384, 64, 16384)]
     if args.max_size:
         shapes = [s for s in shapes if max(s) <= args.max_size]
+    if args.shape:
+        shapes = [tuple(int(x) for x in args.shape.split(","))]
     out = []
     for (m, n, k) in shapes:
         a = linalg.Tensor(workloads.uniform_pm1(1, m, k))
@@ -483,6 +485,7 @@ def main():
                     help="gemm = the headline; the others are secondary configurations")
     ap.add_argument("--ops-rows", type=int, default=4096, help="ops: rows of the 4096-column test tensors")
     ap.add_argument("--max-size", type=int, default=0, help="gemm_sweep: skip shapes with a dimension above this")
+    ap.add_argument("--shape", default="", help="gemm_sweep: run only this problem, given as M,N,K")
     ap.add_argument("--global-batch", type=int, default=32768)
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--log-every", type=int, default=10, help="dp_mlp: read the loss back every this many steps")

@@ -281,9 +281,18 @@ __device__ __forceinline__ void report(DeviceStatus* st, int code, int where, in
   __threadfence_system();
 }
 
-template <int BK, bool A_MN, bool B_MN, bool DIRECT>
-__global__ void __launch_bounds__(DIRECT ? kDirectThreads : kGemmThreads, 1)
-gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+// PATH: where the hi / lo planes of a stage come from.
+constexpr int kPathPlanes = 0;   // pre-pass wrote padded [hi | lo] planes; one TMA box per operand brings both
+constexpr int kPathDirect = 1;   // TMA brings the caller's raw tile (= hi); split warps write lo in shared memory
+constexpr int kPathLoPlane = 2;  // TMA brings the raw tile (= hi) from the caller's tensor and lo from a plane
+                                 // that a one-pass pre-pass wrote in the same (unpadded) layout
+
+template <int BK, bool A_MN, bool B_MN, int PATH>
+__global__ void __launch_bounds__(PATH == kPathDirect ? kDirectThreads : kGemmThreads, 1)
+gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
+                   TcParams p) {
+  constexpr bool DIRECT = PATH == kPathDirect;
   using C = Cfg<BK, DIRECT>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
@@ -338,6 +347,10 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      if constexpr (PATH == kPathLoPlane) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a_lo) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b_lo) : "memory");
+      }
       int stage = 0;
       uint32_t phase = 0;
       uint32_t armed[C::kStages];
@@ -381,6 +394,25 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
               }
             } else {
               tma_load_3d(sb, &map_b, full, kb * BK, nb * BN, b);
+            }
+          } else if constexpr (PATH == kPathLoPlane) {
+            // hi from the caller's tensor, lo from the lo plane: same geometry, same coordinates
+            // (an MN-major operand reaches this path only in its blocked, one-box form)
+            mbar_arrive_expect_tx(full, C::kStageBytes);
+            const uint32_t sb = sa + 2 * C::kABytes;
+            if (A_MN) {
+              tma_load_4d(sa, &map_a, full, 0, kb * BK, mb * (BM / 32), b);
+              tma_load_4d(sa + C::kABytes, &map_a_lo, full, 0, kb * BK, mb * (BM / 32), b);
+            } else {
+              tma_load_3d(sa, &map_a, full, kb * BK, mb * BM, b);
+              tma_load_3d(sa + C::kABytes, &map_a_lo, full, kb * BK, mb * BM, b);
+            }
+            if (B_MN) {
+              tma_load_4d(sb, &map_b, full, 0, kb * BK, nb * (BN / 32), b);
+              tma_load_4d(sb + C::kBBytes, &map_b_lo, full, 0, kb * BK, nb * (BN / 32), b);
+            } else {
+              tma_load_3d(sb, &map_b, full, kb * BK, nb * BN, b);
+              tma_load_3d(sb + C::kBBytes, &map_b_lo, full, kb * BK, nb * BN, b);
             }
           } else {
             mbar_arrive_expect_tx(full, C::kStageBytes);
@@ -723,6 +755,25 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(const float* __res
   }
 }
 
+// Lo-plane pre-pass: dst[i] = lo part of src[i], same layout as the source (n4 16-byte words).
+__global__ void __launch_bounds__(256, 4) split_lo_kernel(const float4* __restrict__ src, float4* __restrict__ dst,
+                                                          int64_t n4) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n4; i += 4 * stride) {
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __ldcs(src + i + j * stride);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      dst[i + j * stride] = make_float4(split_lo(v[j].x), split_lo(v[j].y), split_lo(v[j].z), split_lo(v[j].w));
+  }
+  for (; i < n4; i += stride) {
+    const float4 v = __ldcs(src + i);
+    dst[i] = make_float4(split_lo(v.x), split_lo(v.y), split_lo(v.z), split_lo(v.w));
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -781,9 +832,10 @@ static bool make_operand_map(CUtensorMap* map, float* planes, int rows_p, int Kp
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
-// Switches for measurements (read once).  CLEAVE_CUDA_GEMM_DIRECT: 0 = every problem goes through the
-// split pre-pass, 2 = every addressable problem is split in the kernel, otherwise the choice below.
-// CLEAVE_CUDA_GEMM_MN=0 makes the pre-pass transpose instead of writing MN-major planes.
+// Switches for measurements (read once).  CLEAVE_CUDA_GEMM_DIRECT forces one operand path for every
+// problem it can serve: 0 = padded [hi | lo] planes, 2 = split in the kernel, 3 = lo planes; otherwise
+// the choice in launch_gemm_3xtf32.  CLEAVE_CUDA_GEMM_MN=0 makes the planes pre-pass transpose instead
+// of writing MN-major planes.
 static bool g_mn_major = true;
 static int g_direct = 1;
 static void read_options() {
@@ -793,7 +845,7 @@ static void read_options() {
   const char* mn = getenv("CLEAVE_CUDA_GEMM_MN");
   if (mn && mn[0] == '0') g_mn_major = false;
   const char* d = getenv("CLEAVE_CUDA_GEMM_DIRECT");
-  if (d && (d[0] == '0' || d[0] == '2')) g_direct = d[0] - '0';
+  if (d && (d[0] == '0' || d[0] == '2' || d[0] == '3')) g_direct = d[0] - '0';
 }
 
 bool gemm_3xtf32_supported(const GemmArgs& g) {
@@ -825,12 +877,12 @@ static bool split_operand(const float* src, float* dst, int batch, int rows, int
   return cuda_ok(cudaGetLastError(), "operand split launch");
 }
 
-template <int BK, bool A_MN, bool B_MN, bool DIRECT>
-static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
-  using C = Cfg<BK, DIRECT>;
+template <int BK, bool A_MN, bool B_MN, int PATH>
+static bool run_tc(const CUtensorMap* maps, const TcParams& p) {
+  using C = Cfg<BK, PATH == kPathDirect>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_kernel<BK, A_MN, B_MN, DIRECT>,
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_kernel<BK, A_MN, B_MN, PATH>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes),
                  "cudaFuncSetAttribute(gemm)"))
       return false;
@@ -839,17 +891,19 @@ static bool run_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams&
   const int tiles = p.batch * p.mblks * p.nblks;
   const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
   profile_mark(true);
-  gemm_3xtf32_kernel<BK, A_MN, B_MN, DIRECT>
-      <<<grid, DIRECT ? kDirectThreads : kGemmThreads, C::kSmemBytes, ctx().stream>>>(ma, mb, p);
+  gemm_3xtf32_kernel<BK, A_MN, B_MN, PATH>
+      <<<grid, PATH == kPathDirect ? kDirectThreads : kGemmThreads, C::kSmemBytes, ctx().stream>>>(
+          maps[0], maps[1], maps[2], maps[3], p);
   profile_mark(false);
   count_launch();
   return cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch");
 }
 
-template <bool DIRECT>
-static bool run_tc_layout(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
-  return a_mn ? (b_mn ? run_tc<16, true, true, DIRECT>(ma, mb, p) : run_tc<16, true, false, DIRECT>(ma, mb, p))
-              : (b_mn ? run_tc<16, false, true, DIRECT>(ma, mb, p) : run_tc<16, false, false, DIRECT>(ma, mb, p));
+// maps: {A, B, A lo, B lo}; the last two are read on the lo-plane path only.
+template <int PATH>
+static bool run_tc_layout(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p) {
+  return a_mn ? (b_mn ? run_tc<16, true, true, PATH>(maps, p) : run_tc<16, true, false, PATH>(maps, p))
+              : (b_mn ? run_tc<16, false, true, PATH>(maps, p) : run_tc<16, false, false, PATH>(maps, p));
 }
 
 // Tensor map straight over a caller's operand ([batch] matrices, row-major, unpadded).
@@ -893,16 +947,23 @@ static bool make_direct_map(CUtensorMap* map, const float* base, int rows, int K
   return true;
 }
 
-// The kernel can read the caller's tensors itself when TMA can address them.  Splitting in the
-// kernel costs shared-memory bandwidth that the MMAs also need (measured: the kernel runs ~1.2x
-// longer), the pre-pass costs one HBM round trip over both operands; the pre-pass is the cheaper of
-// the two once 1/M + 1/N drops below ~1/1300 (large, square-ish outputs).
-static bool direct_eligible(const GemmArgs& g) {
-  if (g_direct == 0) return false;
+// TMA can read the caller's tensors themselves when they are 16-byte aligned and their contiguous
+// extent is a multiple of 4 elements.
+static bool addressable(const GemmArgs& g) {
   const int a_inner = g.trans_a ? g.m : g.k, b_inner = g.trans_b ? g.k : g.n;
-  if (!(aligned16(g.a) && aligned16(g.b) && a_inner % 4 == 0 && b_inner % 4 == 0)) return false;
-  if (g_direct == 2) return true;
+  return aligned16(g.a) && aligned16(g.b) && a_inner % 4 == 0 && b_inner % 4 == 0;
+}
+
+// Splitting in the kernel costs shared-memory bandwidth that the MMAs also need (measured: the kernel
+// runs ~1.2x longer); a pre-pass costs an HBM round trip over both operands.  The pre-pass is the
+// cheaper of the two once 1/M + 1/N drops below ~1/1300 (large, square-ish outputs).
+static bool prefer_direct(const GemmArgs& g) {
   return (int64_t)g.m * g.n < 1300ll * ((int64_t)g.m + g.n);
+}
+
+// The lo-plane path fetches an MN-major operand as one blocked box, which needs whole 32-wide blocks.
+static bool lo_plane_eligible(const GemmArgs& g) {
+  return addressable(g) && (!g.trans_a || g.m % 32 == 0) && (g.trans_b || g.n % 32 == 0);
 }
 
 static bool launch_direct(const GemmArgs& g) {
@@ -910,10 +971,12 @@ static bool launch_direct(const GemmArgs& g) {
   const bool a_blocked = a_mn && g.m % 32 == 0, b_blocked = b_mn && g.n % 32 == 0;
   // A narrow C needs only the first round_up(n, 32) rows of each B tile.
   const int b_box_rows = g.n < BN ? round_up(g.n, 32) : BN;
-  CUtensorMap ma, mb;
-  if (!make_direct_map(&ma, g.a, g.m, g.k, g.batch, !a_mn, BM, a_blocked) ||
-      !make_direct_map(&mb, g.b, g.n, g.k, g.batch, !b_mn, b_box_rows, b_blocked))
+  CUtensorMap maps[4];
+  if (!make_direct_map(&maps[0], g.a, g.m, g.k, g.batch, !a_mn, BM, a_blocked) ||
+      !make_direct_map(&maps[1], g.b, g.n, g.k, g.batch, !b_mn, b_box_rows, b_blocked))
     return false;
+  maps[2] = maps[0];
+  maps[3] = maps[1];
   TcParams p;
   p.a_blocked = a_blocked;
   p.b_blocked = b_blocked;
@@ -929,7 +992,60 @@ static bool launch_direct(const GemmArgs& g) {
   p.nblks = ceil_div(g.n, BN);
   p.act = g.act;
   p.status = ctx().status_dev;
-  return run_tc_layout<true>(a_mn, b_mn, ma, mb, p);
+  return run_tc_layout<kPathDirect>(a_mn, b_mn, maps, p);
+}
+
+// hi planes are the caller's tensors, lo planes come from one streaming pass per operand.
+static bool launch_lo_plane(const GemmArgs& g) {
+  const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
+  const int64_t a_elems = (int64_t)g.m * g.k, b_elems = (int64_t)g.n * g.k;
+  int chunk = (int)((4ll << 30) / ((a_elems + b_elems) * 4));
+  if (chunk < 1) chunk = 1;
+  if (chunk > g.batch) chunk = g.batch;
+  float* wa = scratch_alloc(chunk * a_elems * 4);
+  if (!wa) return false;
+  float* wb = scratch_alloc(chunk * b_elems * 4);
+  if (!wb) { scratch_free(wa); return false; }
+  bool ok = true;
+  for (int b0 = 0; ok && b0 < g.batch; b0 += chunk) {
+    const int nb = (g.batch - b0) < chunk ? (g.batch - b0) : chunk;
+    const float* a = g.a + b0 * a_elems;
+    const float* b = g.b + b0 * b_elems;
+    const int64_t a4 = nb * a_elems / 4, b4 = nb * b_elems / 4;
+    split_lo_kernel<<<stream_grid(a4, 256, 4), 256, 0, ctx().stream>>>(reinterpret_cast<const float4*>(a),
+                                                                        reinterpret_cast<float4*>(wa), a4);
+    count_launch();
+    split_lo_kernel<<<stream_grid(b4, 256, 4), 256, 0, ctx().stream>>>(reinterpret_cast<const float4*>(b),
+                                                                        reinterpret_cast<float4*>(wb), b4);
+    count_launch();
+    ok = cuda_ok(cudaGetLastError(), "lo-plane split launch");
+    if (!ok) break;
+    CUtensorMap maps[4];
+    ok = make_direct_map(&maps[0], a, g.m, g.k, nb, !a_mn, BM, a_mn) &&
+         make_direct_map(&maps[1], b, g.n, g.k, nb, !b_mn, BN, b_mn) &&
+         make_direct_map(&maps[2], wa, g.m, g.k, nb, !a_mn, BM, a_mn) &&
+         make_direct_map(&maps[3], wb, g.n, g.k, nb, !b_mn, BN, b_mn);
+    if (!ok) break;
+    TcParams p;
+    p.a_blocked = a_mn;
+    p.b_blocked = b_mn;
+    p.b_box_rows = BN;
+    p.c = g.c + (int64_t)b0 * g.m * g.n;
+    p.bias = g.bias;
+    p.m = g.m;
+    p.n = g.n;
+    p.num_kb = ceil_div(g.k, 16);
+    p.chunk_kb = kChunkK / 16;
+    p.batch = nb;
+    p.mblks = ceil_div(g.m, BM);
+    p.nblks = ceil_div(g.n, BN);
+    p.act = g.act;
+    p.status = ctx().status_dev;
+    ok = run_tc_layout<kPathLoPlane>(a_mn, b_mn, maps, p);
+  }
+  scratch_free(wa);
+  scratch_free(wb);
+  return ok;
 }
 
 bool launch_gemm_3xtf32(const GemmArgs& g) {
@@ -939,7 +1055,16 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     return false;
   }
   read_options();
-  if (direct_eligible(g)) return launch_direct(g);
+  // Measured choice.  Small / narrow problems: split in the kernel.  Up to 4096^2 outputs: lo planes (the
+  // pre-pass moves 2/3 of the bytes of the padded one: 183 vs 300 us at 8192^3, 50 vs 80 us at 4096^3).
+  // Beyond that the padded [hi | lo] planes win although their pre-pass is longer: the kernel runs
+  // 3-5 % slower when its hi operand is the raw tensor (low mantissa bits that the tensor pipe ignores
+  // still travel through shared memory; the kernel runs under the power cap).
+  if (g_direct == 2 || (g_direct == 1 && prefer_direct(g))) {
+    if (addressable(g)) return launch_direct(g);
+  } else if (g_direct == 3 || (g_direct == 1 && (int64_t)g.m * g.n <= (1ll << 24))) {
+    if (lo_plane_eligible(g)) return launch_lo_plane(g);
+  }
   const int bk = 16;
   const int Kp = round_up(g.k, 32);
   const int Mp = round_up(g.m, BM);
@@ -966,9 +1091,12 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     ok = split_operand(a, wa, nb, g.m, g.k, Mp, Kp, g.trans_a == 0, a_mn) &&
          split_operand(b, wb, nb, g.n, g.k, Np, Kp, g.trans_b != 0, b_mn);
     if (!ok) break;
-    CUtensorMap ma, mb;
-    ok = make_operand_map(&ma, wa, Mp, Kp, nb, bk, BM, a_mn) && make_operand_map(&mb, wb, Np, Kp, nb, bk, BN, b_mn);
+    CUtensorMap maps[4];
+    ok = make_operand_map(&maps[0], wa, Mp, Kp, nb, bk, BM, a_mn) &&
+         make_operand_map(&maps[1], wb, Np, Kp, nb, bk, BN, b_mn);
     if (!ok) break;
+    maps[2] = maps[0];
+    maps[3] = maps[1];
     TcParams p;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
     p.bias = g.bias;
@@ -983,7 +1111,7 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.a_blocked = p.b_blocked = 0;
     p.b_box_rows = BN;
     p.status = ctx().status_dev;
-    ok = run_tc_layout<false>(a_mn, b_mn, ma, mb, p);
+    ok = run_tc_layout<kPathPlanes>(a_mn, b_mn, maps, p);
   }
   scratch_free(wa);
   scratch_free(wb);

@@ -1,8 +1,8 @@
 """Runs the tensor-core GEMM over a fixed list of problems and checks each against the CPU oracle.
 
 Started by test_gpu_gemm_paths.py with CLEAVE_CUDA_GEMM_DIRECT set, because the library reads that
-switch once per process: 0 sends every problem through the split pre-pass, 2 makes the kernel split
-every operand that TMA can address.  Prints one line ``OK <cases> <gemm calls> <calls TMA cannot address> <kernel launches>`` on success.
+switch once per process: 0 sends every problem through the padded-planes pre-pass, 2 makes the kernel
+split every operand that TMA can address, 3 uses the lo-plane pre-pass wherever it applies.  Prints one line ``OK <cases> <gemm calls> <calls TMA cannot address> <kernel launches>`` on success.
 """
 import os
 import sys

@@ -1,5 +1,5 @@
-"""Both operand paths of the tensor-core GEMM -- split pre-pass, and split inside the kernel --
-against the oracle on the same problems.  The library chooses between them by shape; here each
+"""The three operand paths of the tensor-core GEMM -- padded hi/lo planes, split inside the kernel,
+lo planes beside the caller's own tensors -- against the oracle on the same problems.  The library chooses between them by shape; here each
 is forced for a whole process (the switch is read once), so the worker runs as a child."""
 import os
 import subprocess
@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("mode", ["0", "2"])
+@pytest.mark.parametrize("mode", ["0", "2", "3"])
 def test_forced_operand_path(mode):
     env = dict(os.environ, CLEAVE_CUDA_GEMM_DIRECT=mode)
     r = subprocess.run([sys.executable, os.path.join(HERE, "gemm_paths_worker.py")], env=env, capture_output=True,
@@ -20,6 +20,7 @@ def test_forced_operand_path(mode):
     last = r.stdout.strip().splitlines()[-1].split()
     assert last[0] == "OK"
     gemms, unaddressable, launches = int(last[2]), int(last[3]), int(last[4])
-    # the pre-pass path launches two split kernels and the GEMM; the direct path only the GEMM,
-    # except for operands that TMA cannot address, which still take the pre-pass
-    assert launches == (3 * gemms if mode == "0" else gemms + 2 * unaddressable)
+    # both pre-pass paths (0: padded hi/lo planes, 3: lo planes) launch two split kernels and the
+    # GEMM; the direct path only the GEMM, except for operands that TMA cannot address, which
+    # take the padded planes
+    assert launches == (gemms + 2 * unaddressable if mode == "2" else 3 * gemms)
