@@ -58,228 +58,9 @@
 
 #include "common.cuh"
 #include "gemm.cuh"
+#include "tc_common.cuh"
 
 namespace cleave {
-
-constexpr int BM = 128;          // tile rows  (UMMA M)
-constexpr int BN = 256;          // tile cols  (UMMA N)
-constexpr int UMMA_K = 8;        // tf32 MMA K (32 bytes)
-constexpr int kEpiWarps = 8;     // two per TMEM lane quarter, 128 columns each
-constexpr int kGemmThreads = 64 + 32 * kEpiWarps;     // producer, issuer, drain warps
-// Direct path (the kernel splits raw operands itself): four warpgroups.  0: producer, issuer and
-// two idle warps; 1-2: drain warps; 3: split warps.  Registers move from groups 0 and 3 to the
-// drain groups (setmaxnreg), whose 128 running sums per thread do not fit the 128 registers that
-// 512 threads would get each.
-constexpr int kSplitWarps = 4;
-constexpr int kDirectThreads = 512;
-constexpr int kRegsLight = 64, kRegsSplit = 72, kRegsDrain = 184;   // 128*64 + 128*72 + 256*184 <= 65536
-constexpr int kChunkK = 256;     // k values accumulated in TMEM before a drain into registers
-constexpr int kAccStages = 2;
-constexpr int kTmemCols = kAccStages * BN;   // 512: all of TMEM
-constexpr int kGroupM = 16;      // tile-rows per rasterisation group
-constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s per wait
-
-#ifndef CLEAVE_RAW_STAGES
-#define CLEAVE_RAW_STAGES 6
-#endif
-// Shared-memory plan.  Pre-pass path: kStages stages of [A hi | A lo | B hi | B lo], all written by
-// TMA.  Direct path: a deep ring of raw stages [A | B] written by TMA plus a shallow ring of lo
-// stages [A lo | B lo] written by the split warps just ahead of the MMAs, so the depth that hides
-// the TMA latency costs 24 KiB per stage instead of 48.
-template <int BK, bool DIRECT>
-struct Cfg {
-  static_assert(BK == 16, "one K-block size is built: 64-byte rows (K-major) / 16 rows of 128 bytes (MN-major)");
-  static constexpr int kRowBytes = BK * 4;
-  static constexpr int kABytes = BM * kRowBytes;          // one plane of A
-  static constexpr int kBBytes = BN * kRowBytes;          // one plane of B
-  static constexpr int kStages = DIRECT ? CLEAVE_RAW_STAGES : 4;        // ring that TMA fills
-  static constexpr int kLoStages = DIRECT ? 8 - CLEAVE_RAW_STAGES : 1;  // direct path: ring of lo planes
-  static constexpr int kStageBytes = DIRECT ? kABytes + kBBytes : 2 * (kABytes + kBBytes);
-  static constexpr int kLoRingOffset = kStages * kStageBytes;
-  static constexpr int kRingBytes = kLoRingOffset + (DIRECT ? kLoStages * (kABytes + kBBytes) : 0);
-  static constexpr int kStoreStageBytes = kEpiWarps * 32 * 128;      // per drain warp: 32 rows x 32 floats
-  static constexpr int kSmemBytes = kRingBytes + kStoreStageBytes + 1024;   // + alignment slack
-  static constexpr uint32_t kLayoutType = 4u;                       // K-major planes: SWIZZLE_64B
-  static constexpr uint32_t kSBO = 8 * kRowBytes;                   // bytes between 8-row groups
-};
-
-// ---- PTX wrappers ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Bounded wait.  Returns false if the CTA is aborting or the wall-clock limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xFFu) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
-                                            int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc], tf32 inputs, f32 accumulate.
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor.
-// K-major operand (contraction index contiguous), swizzled rows of `kRowBytes`: start + k-step * 32 B,
-// stride byte offset = pitch of 8-row groups, leading byte offset unused.
-// MN-major operand (row / column index contiguous): for 4-byte elements the only layout the tensor
-// pipe takes is the 128-byte swizzle with 32-byte atoms (TMA: CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B).
-// The tile is a sequence of 32-wide blocks along M or N, each block BK rows of 128 bytes; the
-// swizzle pattern spans 4 rows (512 bytes), a k-step (8 rows) is 1024 bytes, stride byte offset =
-// 512 (pitch of 4-row groups), leading byte offset = BK * 128 (pitch of blocks).
-//   bits  0-13 start address >> 4     bits 16-29 leading byte offset >> 4 (1: unused when swizzled)
-//   bits 32-45 stride byte offset >> 4 (8-row group pitch)   bits 46-47 descriptor version (1)
-//   bits 61-63 swizzle mode (1 = 128 B with 32-byte atoms, 2 = 128 B, 4 = 64 B)
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t sbo_bytes, uint32_t layout_type,
-                                                   uint32_t lbo_bytes = 16) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)(lbo_bytes >> 4) << 16;
-  d |= (uint64_t)(sbo_bytes >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)layout_type << 61;
-  return d;
-}
-
-// Instruction descriptor: f32 accumulator (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2),
-// bit 15 / 16 = 1 for an MN-major A / B operand, N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-__host__ __device__ constexpr uint32_t instr_desc(bool a_mn, bool b_mn, int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ float act_apply(float v, int act) {
-  switch (act) {
-    case CLEAVE_ACT_RELU: return v != v ? v : (v > 0.0f ? v : 0.0f);
-    case CLEAVE_ACT_SIGMOID: return __frcp_rn(__fadd_rn(1.0f, expf(-v)));
-    case CLEAVE_ACT_TANH: return tanhf(v);
-    default: return v;
-  }
-}
-
-// Low part of the in-kernel split: d = x minus x with its 13 low mantissa bits cleared (exact), then
-// half a tf32 unit is added to d's magnitude so that the tensor pipe's own truncation of the 13 low
-// bits rounds d to the nearest tf32 value.  Integer / full-rate instructions only: a cvt per
-// element would make the split warps slower than the MMAs they feed.
-__device__ __forceinline__ float split_lo(float x) {
-  const float d = __fsub_rn(x, __uint_as_float(__float_as_uint(x) & 0xFFFFE000u));
-  return __uint_as_float(__float_as_uint(d) + 0x1000u);
-}
-
-struct TcParams {
-  float* c;             // [batch][m][n]
-  const float* bias;    // [n] or null
-  int m, n;
-  int num_kb;           // K_padded / BK
-  int chunk_kb;         // K-blocks per accumulation chunk (kChunkK / BK)
-  int batch, mblks, nblks;
-  int act;
-  int a_blocked, b_blocked;   // direct path, MN-major operand: one 4-D box per stage instead of 32-wide boxes
-  int b_box_rows;             // direct path: rows of B fetched and split per stage (BN, less when n is small)
-  DeviceStatus* status;
-};
-
-// Tile index -> (batch, tile-row, tile-col); tile-rows are walked in groups of kGroupM with the
-// row index fastest inside a group, so consecutive tiles share a B panel and nearby A panels.
-__device__ __forceinline__ void decode_tile(int t, const TcParams& p, int& b, int& mb, int& nb) {
-  const int per_batch = p.mblks * p.nblks;
-  b = t / per_batch;
-  int r = t - b * per_batch;
-  const int group_span = kGroupM * p.nblks;
-  const int gid = r / group_span;
-  const int first_m = gid * kGroupM;
-  const int rows_here = (p.mblks - first_m) < kGroupM ? (p.mblks - first_m) : kGroupM;
-  r -= gid * group_span;
-  mb = first_m + r % rows_here;
-  nb = r / rows_here;
-}
-
-__device__ __forceinline__ void report(DeviceStatus* st, int code, int where, int detail) {
-  // Plain stores to mapped host memory (several CTAs may report; any one record will do).
-  volatile DeviceStatus* v = st;
-  v->where = where;
-  v->block = blockIdx.x;
-  v->detail = detail;
-  v->code = code;
-  __threadfence_system();
-}
 
 // PATH: where the hi / lo planes of a stage come from.
 constexpr int kPathPlanes = 0;   // pre-pass wrote padded [hi | lo] planes; one TMA box per operand brings both
@@ -595,77 +376,9 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) break;
-      const int row = mb * BM + q * 32 + lane;
-      const int col0 = nb * BN + half * (BN / 2);
-      const bool full_tile = (mb * BM + BM <= p.m) && (nb * BN + BN <= p.n);   // uniform over the CTA
-      if (row < p.m) {
-        float* crow = p.c + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
-        if (p.bias != nullptr) {
-          if (vec_ok && col0 + BN / 2 <= p.n && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) {
-            const float4* b4 = reinterpret_cast<const float4*>(p.bias + col0);
-#pragma unroll
-            for (int j = 0; j < BN / 8; ++j) {
-              const float4 bv = __ldg(b4 + j);
-              sum[4 * j] = __fadd_rn(sum[4 * j], bv.x);
-              sum[4 * j + 1] = __fadd_rn(sum[4 * j + 1], bv.y);
-              sum[4 * j + 2] = __fadd_rn(sum[4 * j + 2], bv.z);
-              sum[4 * j + 3] = __fadd_rn(sum[4 * j + 3], bv.w);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < BN / 2; ++j)
-              if (col0 + j < p.n) sum[j] = __fadd_rn(sum[j], __ldg(p.bias + col0 + j));
-          }
-        }
-        // One loop per activation (the choice is uniform for the launch), so each is a straight
-        // unrolled sequence over independent elements.
-        if (p.act == CLEAVE_ACT_TANH) {
-#pragma unroll
-          for (int j = 0; j < BN / 2; ++j) sum[j] = tanhf(sum[j]);
-        } else if (p.act == CLEAVE_ACT_SIGMOID) {
-#pragma unroll
-          for (int j = 0; j < BN / 2; ++j) sum[j] = __frcp_rn(__fadd_rn(1.0f, expf(-sum[j])));
-        } else if (p.act == CLEAVE_ACT_RELU) {
-#pragma unroll
-          for (int j = 0; j < BN / 2; ++j) sum[j] = act_apply(sum[j], CLEAVE_ACT_RELU);
-        }
-        if (!(full_tile && vec_ok)) {
-          if (vec_ok && col0 + BN / 2 <= p.n) {
-            float4* dst = reinterpret_cast<float4*>(crow);
-#pragma unroll
-            for (int j = 0; j < BN / 8; ++j) dst[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < BN / 2; ++j)
-              if (col0 + j < p.n) crow[j] = sum[j];
-          }
-        }
-      }
-      if (full_tile && vec_ok) {
-        // Coalesced store of the warp's 32 x 128 block.  A thread owns one ROW (what tcgen05.ld
-        // hands out), but a store instruction is efficient when the warp covers whole 128-byte
-        // lines.  So, 32 columns at a time, every thread parks its 8 16-byte words in a
-        // warp-private shared tile (word j of row r at slot j ^ (r & 7): conflict free both ways)
-        // and the warp then writes 4 rows x 128 bytes per instruction.
-        float4* stage = reinterpret_cast<float4*>(smem_raw + (ring - smem_u32(smem_raw)) +
-                                                  C::kRingBytes) + (warp - kDrainFirst) * (32 * 8);
-        float* cblock = p.c + ((int64_t)b * p.m + mb * BM + q * 32) * (int64_t)p.n + col0;
-#pragma unroll
-        for (int pass = 0; pass < BN / 64; ++pass) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            stage[lane * 8 + (j ^ (lane & 7))] = make_float4(sum[32 * pass + 4 * j], sum[32 * pass + 4 * j + 1],
-                                                             sum[32 * pass + 4 * j + 2], sum[32 * pass + 4 * j + 3]);
-          __syncwarp();
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int r = it * 4 + (lane >> 3), slot = lane & 7;
-            const float4 v = stage[r * 8 + (slot ^ (r & 7))];
-            *reinterpret_cast<float4*>(cblock + (int64_t)r * p.n + 32 * pass + 4 * slot) = v;
-          }
-          __syncwarp();
-        }
-      }
+      float4* stage = reinterpret_cast<float4*>(smem_raw + (ring - smem_u32(smem_raw)) + C::kRingBytes) +
+                      (warp - kDrainFirst) * (32 * 8);
+      tile_epilogue(sum, p, b, mb * BM, nb, q, half, lane, vec_ok, stage);
     }
   }
 
@@ -838,6 +551,7 @@ static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 // of writing MN-major planes.
 static bool g_mn_major = true;
 static int g_direct = 1;
+static int g_pair = -1;   // CLEAVE_CUDA_GEMM_PAIR: 1 / 0 = always / never run the padded-planes path on CTA pairs
 static void read_options() {
   static bool done = false;
   if (done) return;
@@ -846,6 +560,8 @@ static void read_options() {
   if (mn && mn[0] == '0') g_mn_major = false;
   const char* d = getenv("CLEAVE_CUDA_GEMM_DIRECT");
   if (d && (d[0] == '0' || d[0] == '2' || d[0] == '3')) g_direct = d[0] - '0';
+  const char* pr = getenv("CLEAVE_CUDA_GEMM_PAIR");
+  if (pr && (pr[0] == '0' || pr[0] == '1')) g_pair = pr[0] - '0';
 }
 
 bool gemm_3xtf32_supported(const GemmArgs& g) {
@@ -1066,8 +782,12 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     if (lo_plane_eligible(g)) return launch_lo_plane(g);
   }
   const int bk = 16;
+  // 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) for the large problems this path serves:
+  // measured 1-2 % faster at 4096^3 and 8192^3 (3.71-3.79 vs 3.74-3.84 ms); small ragged problems
+  // keep 128-row tiles, which pad less.
+  const bool pair = g_pair >= 0 ? g_pair == 1 : (int64_t)g.m * g.n > (1ll << 24);
   const int Kp = round_up(g.k, 32);
-  const int Mp = round_up(g.m, BM);
+  const int Mp = round_up(g.m, pair ? 256 : BM);
   const int Np = round_up(g.n, BN);
   // Bound the split workspace: process the batch in chunks of at most ~4 GiB of planes.
   const int64_t per_batch_bytes = 2ll * ((int64_t)Mp + Np) * Kp * 4;
@@ -1093,7 +813,7 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     if (!ok) break;
     CUtensorMap maps[4];
     ok = make_operand_map(&maps[0], wa, Mp, Kp, nb, bk, BM, a_mn) &&
-         make_operand_map(&maps[1], wb, Np, Kp, nb, bk, BN, b_mn);
+         make_operand_map(&maps[1], wb, Np, Kp, nb, bk, pair ? 128 : BN, b_mn);
     if (!ok) break;
     maps[2] = maps[0];
     maps[3] = maps[1];
@@ -1111,7 +831,12 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.a_blocked = p.b_blocked = 0;
     p.b_box_rows = BN;
     p.status = ctx().status_dev;
-    ok = run_tc_layout<kPathPlanes>(a_mn, b_mn, maps, p);
+    if (pair) {
+      p.mblks = Mp / 256;
+      ok = run_tc_pair(a_mn, b_mn, maps, p);
+    } else {
+      ok = run_tc_layout<kPathPlanes>(a_mn, b_mn, maps, p);
+    }
   }
   scratch_free(wa);
   scratch_free(wb);

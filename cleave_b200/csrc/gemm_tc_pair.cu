@@ -1,0 +1,329 @@
+// Pair form of the tcgen05 3xTF32 GEMM: the two CTAs of a 2-CTA cluster (an SM pair) compute one
+// 256 x 256 tile of C with tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its
+// own 128 of the tile's 256 B rows; the MMA reads B from both CTAs' shared memory, so per SM the
+// operand traffic into shared memory and out of it to the tensor pipe is 2/3 of the one-CTA kernel's
+// (A 128 + B 128 rows per K-block instead of 128 + 256).  Each CTA keeps the accumulator of its own
+// 128 rows in its own TMEM and drains / stores it exactly as the one-CTA kernel does.
+//
+// Operands: the padded [hi | lo] planes of the pre-pass (both operands padded to 256 rows).
+//
+// Roles per CTA (320 threads): warp 0 producer, warp 1 MMA issuer (only in the cluster's CTA 0),
+// warps 2-9 drain + epilogue.  Signals:
+//   full[s]        lives in CTA 0; CTA 0's producer arms it with the bytes of BOTH CTAs' boxes; every
+//                  TMA load of either CTA completes on it (cp.async.bulk.tensor ... .cta_group::2)
+//   empty[s]       one in each CTA; the issuer's tcgen05.commit arrives on both (CTA mask 0b11)
+//   tmem_full[a]   one in each CTA; committed on both after each K-chunk
+//   tmem_empty[a]  lives in CTA 0, 16 arrivals: the 8 drain warps of each CTA (CTA 1's arrive remotely)
+// Every wait is bounded as in the one-CTA kernel; a CTA that gives up raises its own abort flag and
+// reports; its peer then runs into its own limit.  TMEM is freed by both CTAs after a cluster barrier.
+#include "tc_common.cuh"
+
+namespace cleave {
+
+constexpr int kPairStages = 6;
+constexpr int kRingBytesPair = 192 * 1024;
+constexpr int kPairPlaneBytes = 128 * 64;                  // 128 rows x 16 floats: one plane of A, or of half of B
+constexpr int kPairStageBytes = 4 * kPairPlaneBytes;       // [A hi | A lo | B hi | B lo]
+constexpr int kPairGroupM = 8;                             // 256-row tile-rows per rasterisation group
+static_assert(kPairStages * kPairStageBytes <= kRingBytesPair, "ring");
+constexpr int kPairSmemBytes = kRingBytesPair + kEpiWarps * 32 * 128 + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in the CTA of rank `rank` (shared::cluster window).
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA loads of a CTA pair: data into this CTA's shared memory, completion on CTA 0's mbarrier.
+__device__ __forceinline__ void tma_pair_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0,
+                                                 int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0,
+                                                 int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// Arrives on the mbarrier at this offset in both CTAs once all MMAs issued so far have retired.
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// M = 256 over the pair, N = 256.
+__host__ __device__ constexpr uint32_t instr_desc_pair(bool a_mn, bool b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+// Tile index -> (batch, 256-row tile-row, 256-column tile-column), tile-rows in groups of kPairGroupM.
+__device__ __forceinline__ void decode_pair_tile(int t, const TcParams& p, int& b, int& mb, int& nb) {
+  const int per_batch = p.mblks * p.nblks;
+  b = t / per_batch;
+  int r = t - b * per_batch;
+  const int group_span = kPairGroupM * p.nblks;
+  const int gid = r / group_span;
+  const int first_m = gid * kPairGroupM;
+  const int rows_here = (p.mblks - first_m) < kPairGroupM ? (p.mblks - first_m) : kPairGroupM;
+  r -= gid * group_span;
+  mb = first_m + r % rows_here;
+  nb = r / rows_here;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        TcParams p) {
+  constexpr int BK = 16;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kPairStages];
+  __shared__ __align__(8) uint64_t bar_empty[kPairStages];
+  __shared__ __align__(8) uint64_t bar_tmem_full[kAccStages];
+  __shared__ __align__(8) uint64_t bar_tmem_empty[kAccStages];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0: issues the MMAs for the pair
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int total_tiles = p.batch * p.mblks * p.nblks;          // 256 x 256 tiles
+  const int n_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < kAccStages; ++a) {
+      mbar_init(smem_u32(&bar_tmem_full[a]), 1);
+      mbar_init(smem_u32(&bar_tmem_empty[a]), 2 * kEpiWarps);   // the drain warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    // one warp of each CTA, together: the same columns in both CTAs' TMEM
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  // both CTAs' barriers are initialised and both TMEM allocations exist before anything crosses over
+  cluster_sync_all();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed[kPairStages];
+#pragma unroll
+      for (int s = 0; s < kPairStages; ++s) armed[s] = 0;
+      bool ok = true;
+      for (int t = cluster_id; ok && t < total_tiles; t += n_clusters) {
+        int b, mb, nb;
+        decode_pair_tile(t, p, b, mb, nb);
+        const int a_row0 = mb * 256 + (int)rank * 128, b_row0 = nb * 256 + (int)rank * 128;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
+            report(p.status, 1, 100 + stage, kb);
+            ok = false;
+            break;
+          }
+          const uint32_t full_own = smem_u32(&bar_full[stage]);
+          const uint32_t full0 = map_to_cta(full_own, 0);
+          if (rank == 0) mbar_arrive_expect_tx(full_own, 2 * kPairStageBytes);
+          const uint32_t sa = ring + stage * kPairStageBytes, sb = sa + 2 * kPairPlaneBytes;
+          if (A_MN) tma_pair_load_4d(sa, &map_a, full0, 0, kb * BK, a_row0 / 32, b * 2);
+          else tma_pair_load_3d(sa, &map_a, full0, kb * BK, a_row0, b * 2);
+          if (B_MN) tma_pair_load_4d(sb, &map_b, full0, 0, kb * BK, b_row0 / 32, b * 2);
+          else tma_pair_load_3d(sb, &map_b, full0, kb * BK, b_row0, b * 2);
+#pragma unroll
+          for (int s = 0; s < kPairStages; ++s)
+            if (s == stage) armed[s]++;
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && rank == 0) {
+        // Leaving early: give the copies in flight a bounded chance to land (CTA 0 sees their completion).
+#pragma unroll
+        for (int s = 0; s < kPairStages; ++s) {
+          if (armed[s] == 0) continue;
+          const uint32_t par = (armed[s] - 1u) & 1u;
+          for (int spin = 0; spin < (1 << 20); ++spin)
+            if (mbar_try_wait(smem_u32(&bar_full[s]), par)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (CTA 0 only)
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      constexpr uint32_t idesc = instr_desc_pair(A_MN, B_MN);
+      for (int t = cluster_id; ok && t < total_tiles; t += n_clusters) {
+        for (int kb0 = 0; ok && kb0 < p.num_kb; kb0 += p.chunk_kb) {
+          if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
+            report(p.status, 2, 200 + acc, t);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+          const int kb_end = (kb0 + p.chunk_kb) < p.num_kb ? (kb0 + p.chunk_kb) : p.num_kb;
+          for (int kb = kb0; kb < kb_end; ++kb) {
+            if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
+              report(p.status, 3, 300 + stage, kb);
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+            const uint32_t a_hi = ring + stage * kPairStageBytes;
+            const uint32_t a_lo = a_hi + kPairPlaneBytes;
+            const uint32_t b_hi = a_hi + 2 * kPairPlaneBytes;
+            const uint32_t b_lo = b_hi + kPairPlaneBytes;
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              const uint32_t off_a = A_MN ? kk * 1024 : kk * UMMA_K * 4;
+              const uint32_t off_b = B_MN ? kk * 1024 : kk * UMMA_K * 4;
+              constexpr uint32_t sbo_a = A_MN ? 512u : 512u, lay_a = A_MN ? 1u : 4u;   // K-major: 8 rows x 64 bytes
+              constexpr uint32_t sbo_b = B_MN ? 512u : 512u, lay_b = B_MN ? 1u : 4u;
+              constexpr uint32_t lbo_a = A_MN ? BK * 128u : 16u, lbo_b = B_MN ? BK * 128u : 16u;
+              const uint64_t da_hi = make_smem_desc(a_hi + off_a, sbo_a, lay_a, lbo_a);
+              const uint64_t da_lo = make_smem_desc(a_lo + off_a, sbo_a, lay_a, lbo_a);
+              const uint64_t db_hi = make_smem_desc(b_hi + off_b, sbo_b, lay_b, lbo_b);
+              const uint64_t db_lo = make_smem_desc(b_lo + off_b, sbo_b, lay_b, lbo_b);
+              umma_tf32_pair(d_tmem, da_lo, db_hi, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+              umma_tf32_pair(d_tmem, da_hi, db_lo, idesc, 1u);
+              umma_tf32_pair(d_tmem, da_hi, db_hi, idesc, 1u);
+            }
+            tcgen05_commit_pair(smem_u32(&bar_empty[stage]));   // both CTAs' stage s reusable once these retire
+            if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          tcgen05_commit_pair(smem_u32(&bar_tmem_full[acc]));   // chunk complete, in both CTAs' TMEM
+          if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ drain + epilogue (warps 2..9, both CTAs)
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = (p.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0);
+    float4* stage_tile = reinterpret_cast<float4*>(smem_raw + (ring - smem_u32(smem_raw)) + kRingBytesPair) +
+                         (warp - 2) * (32 * 8);
+    bool ok = true;
+    for (int t = cluster_id; ok && t < total_tiles; t += n_clusters) {
+      int b, mb, nb;
+      decode_pair_tile(t, p, b, mb, nb);
+      float sum[BN / 2];
+#pragma unroll
+      for (int j = 0; j < BN / 2; ++j) sum[j] = 0.0f;
+      for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.chunk_kb) {
+        ok = mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, 4, 400 + acc, t);
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * (BN / 2));
+#pragma unroll
+        for (int cb = 0; cb < BN / 64; ++cb) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + cb * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[cb * 32 + j] = __fadd_rn(sum[cb * 32 + j], __uint_as_float(r[j]));
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_tmem_empty[acc]), 0));
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) break;
+      tile_epilogue(sum, p, b, mb * 256 + (int)rank * 128, nb, q, half, lane, vec_ok, stage_tile);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  // Neither CTA may free its TMEM (or exit, taking its shared memory and barriers along) while its peer
+  // can still issue an MMA into it or signal it.
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static bool run_pair(const CUtensorMap* maps, const TcParams& p) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kPairSmemBytes),
+                 "cudaFuncSetAttribute(pair gemm)"))
+      return false;
+    attr_set = true;
+  }
+  const int tiles = p.batch * p.mblks * p.nblks;
+  int clusters = ctx().sm_count / 2;
+  if (tiles < clusters) clusters = tiles;
+  profile_mark(true);
+  gemm_3xtf32_pair_kernel<A_MN, B_MN><<<2 * clusters, kGemmThreads, kPairSmemBytes, ctx().stream>>>(maps[0], maps[1], p);
+  profile_mark(false);
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "tcgen05 pair GEMM launch");
+}
+
+bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p) {
+  return a_mn ? (b_mn ? run_pair<true, true>(maps, p) : run_pair<true, false>(maps, p))
+              : (b_mn ? run_pair<false, true>(maps, p) : run_pair<false, false>(maps, p));
+}
+
+}  // namespace cleave

@@ -11,9 +11,10 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("mode", ["0", "2", "3"])
-def test_forced_operand_path(mode):
-    env = dict(os.environ, CLEAVE_CUDA_GEMM_DIRECT=mode)
+@pytest.mark.parametrize("mode,pair", [("0", "0"), ("2", "0"), ("3", "0"), ("0", "1")])
+def test_forced_operand_path(mode, pair):
+    # pair = "1": the padded-planes path runs its 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2)
+    env = dict(os.environ, CLEAVE_CUDA_GEMM_DIRECT=mode, CLEAVE_CUDA_GEMM_PAIR=pair)
     r = subprocess.run([sys.executable, os.path.join(HERE, "gemm_paths_worker.py")], env=env, capture_output=True,
                        text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
