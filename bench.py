@@ -44,7 +44,7 @@ M = N = K = 8192          # headline size; --size overrides it for profiling cap
 FLOPS = 2.0 * M * N * K
 # DRAM traffic of one tcgen05 GEMM kernel launch at 8192^3, from a one-pass ncu capture of this
 # program at full size (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 5.94e9 + 264.19e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 4.745e9 + 272.4e6
 
 
 def measured_peaks():
@@ -650,7 +650,7 @@ def main():
     peak = peaks["bf16_tflops"] / 2.0 / 3.0
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                "kernel": "gemm_3xtf32_kernel", "kernel_ms": kernel_ms, "launches_timed": n_prof.value,
+                "kernel": "gemm_3xtf32_pair_kernel", "kernel_ms": kernel_ms, "launches_timed": n_prof.value,
                 "peak_basis": f"{peaks_kind} bf16_tflops (burst) / 2 (tf32) / 3 (split); "
                               f"sustained basis {peaks['bf16_tflops_sustained'] / 6.0:.1f}"}
 

@@ -408,34 +408,52 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
 }
 
 // Source already K-major: src[b][r][k] (r < rows, k < K).  dst planes [b][2][rows_p][Kp].
-__global__ void __launch_bounds__(256) split_copy_kernel(const float* __restrict__ src, float* __restrict__ dst,
-                                                         int rows, int K, int rows_p, int Kp, int vec) {
+__global__ void __launch_bounds__(256, 4) split_copy_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                            int rows, int K, int rows_p, int Kp, int vec) {
   const int b = blockIdx.z;
   const float* s = src + (int64_t)b * rows * K;
   float* hi_p = dst + (int64_t)b * 2 * rows_p * Kp;
   float* lo_p = hi_p + (int64_t)rows_p * Kp;
   const int kq = Kp >> 2;   // Kp is a multiple of 16
   const int64_t total = (int64_t)rows_p * kq;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int r = (int)(i / kq);
-    const int k = (int)(i - (int64_t)r * kq) * 4;
-    float x[4] = {0.f, 0.f, 0.f, 0.f};
-    if (r < rows) {
-      if (vec && k + 3 < K) {
-        const float4 v = __ldcs(reinterpret_cast<const float4*>(s + (int64_t)r * K + k));
-        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-      } else {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  constexpr int U = 4;      // 16-byte words in flight per thread
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += U * stride) {
+    float4 x[U];
+    int64_t o[U];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (k + j < K) x[j] = s[(int64_t)r * K + k + j];
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      o[u] = -1;
+      if (i < total) {
+        const int r = (int)(i / kq);
+        const int k = (int)(i - (int64_t)r * kq) * 4;
+        o[u] = (int64_t)r * Kp + k;
+        if (r < rows) {
+          const float* q = s + (int64_t)r * K + k;
+          if (vec && k + 3 < K) {
+            x[u] = __ldcs(reinterpret_cast<const float4*>(q));
+          } else {
+            if (k < K) x[u].x = q[0];
+            if (k + 1 < K) x[u].y = q[1];
+            if (k + 2 < K) x[u].z = q[2];
+            if (k + 3 < K) x[u].w = q[3];
+          }
+        }
       }
     }
-    float h[4], l[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) split_tf32(x[j], h[j], l[j]);
-    const int64_t o = (int64_t)r * Kp + k;
-    *reinterpret_cast<float4*>(hi_p + o) = make_float4(h[0], h[1], h[2], h[3]);
-    *reinterpret_cast<float4*>(lo_p + o) = make_float4(l[0], l[1], l[2], l[3]);
+    for (int u = 0; u < U; ++u) {
+      if (o[u] < 0) continue;
+      float4 h, l;
+      split_tf32(x[u].x, h.x, l.x);
+      split_tf32(x[u].y, h.y, l.y);
+      split_tf32(x[u].z, h.z, l.z);
+      split_tf32(x[u].w, h.w, l.w);
+      *reinterpret_cast<float4*>(hi_p + o[u]) = h;
+      *reinterpret_cast<float4*>(lo_p + o[u]) = l;
+    }
   }
 }
 
@@ -583,7 +601,7 @@ static bool split_operand(const float* src, float* dst, int batch, int rows, int
     const int Rp = k_contiguous ? rows_p : Kp, Cp = k_contiguous ? Kp : rows_p;
     int vec = (aligned16(src) && Cc % 4 == 0) ? 1 : 0;
     int64_t items = (int64_t)Rp * (Cp / 4);
-    int grid = stream_grid(items, 256, 8);
+    int grid = stream_grid((items + 3) / 4, 256, 4);
     split_copy_kernel<<<dim3(grid, 1, batch), 256, 0, s>>>(src, dst, R, Cc, Rp, Cp, vec);
   } else {
     split_transpose_kernel<<<dim3(ceil_div(Kp, 32), ceil_div(rows_p, 32), batch), 256, 0, s>>>(src, dst, rows, K,
