@@ -73,6 +73,7 @@ SIGNATURES = {
     "cleave_cuda_gemm_tn_f32": (c_buf, [c_buf, c_buf, i32, i32, i32]),
     "cleave_cuda_gemm_batched_f32": (c_buf, [c_buf, c_buf, i32, i32, i32, i32]),
     "cleave_cuda_gemm_ex_f32": (i32, [c_buf, c_buf, c_buf, i32, i32, i32, i32, i32, i32, i32, c_buf, i32]),
+    "cleave_cuda_gemm_dact_f32": (i32, [c_buf, c_buf, c_buf, i32, i32, i32, i32, i32, i32, i32, c_buf, i32]),
     "cleave_cuda_bias_act_f32": (c_buf, [c_buf, c_buf, i32, i32, i32]),
     "cleave_cuda_mse_f32": (f32, [c_buf, c_buf, c_buf]),
     "cleave_cuda_mse_act_bwd_f32": (f32, [c_buf, c_buf, c_buf, i32]),

@@ -87,12 +87,20 @@ class MLP2:
         loss, dZ2 = nn.mse_act_bwd(Y, T, self.act2, loss_out)   # dY and act2'(Y) * dY in one pass
         # dH first: it is the last reader of W2 in this step, so once [dW2 | db2] are announced a
         # data-parallel exchange may already overwrite W2 and b2 while the rest of the pass runs.
-        dH = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True)   # dZ2 W2^T
+        # Without ``keep`` dH is never stored: dZ1 = act1'(H) * (dZ2 W2^T) leaves the GEMM's epilogue directly
+        # (bit-identical to the two-step form, one pass over H instead of three over H-sized tensors).
+        dH = None
+        if keep:
+            dH = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True)   # dZ2 W2^T
+            dZ1 = None
+        else:
+            dZ1 = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True, dact_of=H, dact=self.act1)
         gemm_into(self.dW2, H, dZ2, trans_a=True)            # H^T dZ2
         self._colsum_into(self.db2, dZ2)
         if on_grads_ready:
             on_grads_ready(0)
-        dZ1 = _ACT_BWD[self.act1](H, dH)
+        if dZ1 is None:
+            dZ1 = _ACT_BWD[self.act1](H, dH)
         gemm_into(self.dW1, X, dZ1, trans_a=True)            # X^T dZ1
         self._colsum_into(self.db1, dZ1)
         if on_grads_ready:

@@ -2,6 +2,8 @@
 #pragma once
 #include <stdint.h>
 
+#include "common.cuh"
+
 namespace cleave {
 
 // C[batch][m,n] = op(A) * op(B) (+ bias[n] per row, then activation).
@@ -14,7 +16,23 @@ struct GemmArgs {
   int trans_a, trans_b;
   const float* bias;   // may be null
   int act;             // CLEAVE_ACT_*
+  // Backward form: C = act'(y) (.) (op(A) * op(B)), the derivative of activation `dact` evaluated from its
+  // OUTPUT y (same shape as C); null for a plain product.  Not combined with bias / act.
+  const float* dact_y;
+  int dact;
 };
+
+// Derivative of an activation, from the activation's output y, times the upstream value g: the same
+// operation sequence as the elementwise tanh_bwd / sigmoid_bwd / relu_bwd kernels, so fusing it into a
+// GEMM epilogue changes no bit.
+__device__ __forceinline__ float dact_apply(float y, float g, int dact) {
+  switch (dact) {
+    case CLEAVE_ACT_TANH: return __fmul_rn(__fsub_rn(1.0f, __fmul_rn(y, y)), g);
+    case CLEAVE_ACT_SIGMOID: return __fmul_rn(__fmul_rn(y, __fsub_rn(1.0f, y)), g);
+    case CLEAVE_ACT_RELU: return y > 0.0f ? g : 0.0f;
+    default: return g;
+  }
+}
 
 bool launch_gemm_exact(const GemmArgs& g);
 bool launch_gemm_3xtf32(const GemmArgs& g);   // false + error if the problem cannot use this path

@@ -24,7 +24,7 @@ static bool run_gemm(const GemmArgs& g, int algo) {
 }
 
 static int gemm_into(Buf* C, Buf* A, Buf* B, int batch, int m, int n, int k, int ta, int tb, int algo, Buf* bias,
-                     int act) {
+                     int act, Buf* dact_y = nullptr, int dact = CLEAVE_ACT_IDENTITY) {
   if (batch <= 0 || m <= 0 || n <= 0 || k <= 0)
     return set_error(CLEAVE_CUDA_ERR_ARG, "gemm: batch, m, n, k must be positive (got %d, %d, %d, %d)", batch, m, n, k);
   if (A->len != (int64_t)batch * m * k || B->len != (int64_t)batch * k * n || C->len != (int64_t)batch * m * n)
@@ -37,7 +37,17 @@ static int gemm_into(Buf* C, Buf* A, Buf* B, int batch, int m, int n, int k, int
     return set_error(CLEAVE_CUDA_ERR_ARG, "gemm: unknown activation code %d", act);
   if (C->ptr == A->ptr || C->ptr == B->ptr)
     return set_error(CLEAVE_CUDA_ERR_ARG, "gemm: the output must not alias an operand");
-  GemmArgs g{A->ptr, B->ptr, C->ptr, batch, m, n, k, ta ? 1 : 0, tb ? 1 : 0, bias ? bias->ptr : nullptr, act};
+  if (dact_y) {
+    if (dact_y->len != C->len)
+      return set_error(CLEAVE_CUDA_ERR_SHAPE, "gemm_dact: y has %lld elements, the product %lld",
+                       (long long)dact_y->len, (long long)C->len);
+    if (dact < CLEAVE_ACT_IDENTITY || dact > CLEAVE_ACT_TANH)
+      return set_error(CLEAVE_CUDA_ERR_ARG, "gemm_dact: unknown activation code %d", dact);
+    if (dact_y->ptr == C->ptr)
+      return set_error(CLEAVE_CUDA_ERR_ARG, "gemm_dact: the output must not alias y");
+  }
+  GemmArgs g{A->ptr, B->ptr, C->ptr, batch, m, n, k, ta ? 1 : 0, tb ? 1 : 0, bias ? bias->ptr : nullptr, act,
+             dact_y ? dact_y->ptr : nullptr, dact};
   return run_gemm(g, algo) ? CLEAVE_CUDA_OK : cleave_cuda_last_error();
 }
 
@@ -92,6 +102,19 @@ int32_t cleave_cuda_gemm_ex_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_
     if (!bi) return -cleave_cuda_last_error();
   }
   int r = gemm_into(C, A, B, batch, m, n, k, trans_a, trans_b, algo, bi, act);
+  return r == CLEAVE_CUDA_OK ? CLEAVE_CUDA_OK : -r;
+}
+
+int32_t cleave_cuda_gemm_dact_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n,
+                                  int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo, cleave_buf y,
+                                  int32_t act) {
+  ApiLock lock;
+  Buf* C = as_buf(c, "gemm_dact");
+  Buf* A = as_buf(a, "gemm_dact");
+  Buf* B = as_buf(b, "gemm_dact");
+  Buf* Y = as_buf(y, "gemm_dact");
+  if (!C || !A || !B || !Y) return -cleave_cuda_last_error();
+  int r = gemm_into(C, A, B, batch, m, n, k, trans_a, trans_b, algo, nullptr, CLEAVE_ACT_IDENTITY, Y, act);
   return r == CLEAVE_CUDA_OK ? CLEAVE_CUDA_OK : -r;
 }
 

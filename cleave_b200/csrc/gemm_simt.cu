@@ -22,13 +22,15 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 // A is [m,k] (or [k,m] when ta), B is [k,n] (or [n,k] when tb); 256 threads, 4x4 outputs each.
 __global__ void __launch_bounds__(256) gemm_exact_kernel(const float* __restrict__ A, const float* __restrict__ B,
                                                          float* __restrict__ C, int m, int n, int k, int ta, int tb,
-                                                         const float* __restrict__ bias, int act) {
+                                                         const float* __restrict__ bias, int act,
+                                                         const float* __restrict__ dact_y, int dact) {
   __shared__ float As[kTK][kTM + 4];
   __shared__ float Bs[kTK][kTN + 4];
   const int64_t batch = blockIdx.z;
   A += batch * (int64_t)m * k;
   B += batch * (int64_t)k * n;
   C += batch * (int64_t)m * n;
+  if (dact_y) dact_y += batch * (int64_t)m * n;
   const int m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
   float acc[4][4];
@@ -82,14 +84,17 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(const float* __restrict
       if (gn >= n) continue;
       float v = acc[i][j];
       if (bias) v = __fadd_rn(v, bias[gn]);
-      C[(int64_t)gm * n + gn] = apply_act(v, act);
+      v = apply_act(v, act);
+      if (dact_y) v = dact_apply(dact_y[(int64_t)gm * n + gn], v, dact);
+      C[(int64_t)gm * n + gn] = v;
     }
   }
 }
 
 bool launch_gemm_exact(const GemmArgs& g) {
   dim3 grid(ceil_div(g.n, kTN), ceil_div(g.m, kTM), g.batch);
-  gemm_exact_kernel<<<grid, 256, 0, ctx().stream>>>(g.a, g.b, g.c, g.m, g.n, g.k, g.trans_a, g.trans_b, g.bias, g.act);
+  gemm_exact_kernel<<<grid, 256, 0, ctx().stream>>>(g.a, g.b, g.c, g.m, g.n, g.k, g.trans_a, g.trans_b, g.bias, g.act,
+                                                    g.dact_y, g.dact);
   count_launch();
   return cuda_ok(cudaGetLastError(), "exact GEMM launch");
 }

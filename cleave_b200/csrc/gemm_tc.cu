@@ -717,6 +717,8 @@ static bool launch_direct(const GemmArgs& g) {
   p.b_box_rows = b_box_rows;
   p.c = g.c;
   p.bias = g.bias;
+  p.dact_y = g.dact_y;
+  p.dact = g.dact;
   p.m = g.m;
   p.n = g.n;
   p.num_kb = ceil_div(g.k, 16);
@@ -766,6 +768,8 @@ static bool launch_lo_plane(const GemmArgs& g) {
     p.b_box_rows = BN;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
     p.bias = g.bias;
+    p.dact_y = g.dact_y ? g.dact_y + (int64_t)b0 * g.m * g.n : nullptr;
+    p.dact = g.dact;
     p.m = g.m;
     p.n = g.n;
     p.num_kb = ceil_div(g.k, 16);
@@ -838,6 +842,8 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     TcParams p;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
     p.bias = g.bias;
+    p.dact_y = g.dact_y ? g.dact_y + (int64_t)b0 * g.m * g.n : nullptr;
+    p.dact = g.dact;
     p.m = g.m;
     p.n = g.n;
     p.num_kb = Kp / bk;

@@ -195,6 +195,8 @@ __device__ __forceinline__ float split_lo(float x) {
 struct TcParams {
   float* c;             // [batch][m][n]
   const float* bias;    // [n] or null
+  const float* dact_y;  // [batch][m][n] or null: multiply the product by dact'(y) (backward form)
+  int dact;
   int m, n;
   int num_kb;           // K_padded / BK
   int chunk_kb;         // K-blocks per accumulation chunk (kChunkK / BK)
@@ -268,6 +270,33 @@ __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcPara
     } else if (p.act == CLEAVE_ACT_RELU) {
 #pragma unroll
       for (int j = 0; j < BN / 2; ++j) sum[j] = act_apply(sum[j], CLEAVE_ACT_RELU);
+    }
+    if (p.dact_y != nullptr) {
+      // backward form: times the activation derivative taken from the forward output y at the same place;
+      // one loop per activation, as above
+      const float* yrow = p.dact_y + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
+      const bool yvec = vec_ok && col0 + BN / 2 <= p.n && (reinterpret_cast<uintptr_t>(p.dact_y) & 15u) == 0;
+#define CLEAVE_DACT_LOOP(ACT)                                                                   \
+  if (yvec) {                                                                                   \
+    _Pragma("unroll") for (int j = 0; j < BN / 8; ++j) {                                        \
+      const float4 y = __ldg(reinterpret_cast<const float4*>(yrow) + j);                        \
+      sum[4 * j] = dact_apply(y.x, sum[4 * j], ACT);                                            \
+      sum[4 * j + 1] = dact_apply(y.y, sum[4 * j + 1], ACT);                                    \
+      sum[4 * j + 2] = dact_apply(y.z, sum[4 * j + 2], ACT);                                    \
+      sum[4 * j + 3] = dact_apply(y.w, sum[4 * j + 3], ACT);                                    \
+    }                                                                                           \
+  } else {                                                                                      \
+    _Pragma("unroll") for (int j = 0; j < BN / 2; ++j)                                          \
+      if (col0 + j < p.n) sum[j] = dact_apply(__ldg(yrow + j), sum[j], ACT);                    \
+  }
+      if (p.dact == CLEAVE_ACT_TANH) {
+        CLEAVE_DACT_LOOP(CLEAVE_ACT_TANH)
+      } else if (p.dact == CLEAVE_ACT_SIGMOID) {
+        CLEAVE_DACT_LOOP(CLEAVE_ACT_SIGMOID)
+      } else if (p.dact == CLEAVE_ACT_RELU) {
+        CLEAVE_DACT_LOOP(CLEAVE_ACT_RELU)
+      }
+#undef CLEAVE_DACT_LOOP
     }
     if (!(full_tile && vec_ok)) {
       if (vec_ok && col0 + BN / 2 <= p.n) {

@@ -189,10 +189,14 @@ ACT = {"identity": 0, "relu": 1, "sigmoid": 2, "tanh": 3}
 
 
 def gemm_into(c: Tensor, a: Tensor, b: Tensor, *, trans_a=False, trans_b=False, algo=GEMM_AUTO,
-              bias: Tensor | None = None, act: str = "identity") -> Tensor:
+              bias: Tensor | None = None, act: str = "identity", dact_of: Tensor | None = None,
+              dact: str = "identity") -> Tensor:
     """General product written into ``c`` (``cleave_cuda_gemm_ex_f32``).  Shapes follow the stored
     layouts: a is [m,k] ([k,m] if trans_a), b is [k,n] ([n,k] if trans_b); a leading batch
-    dimension on all three runs independent products."""
+    dimension on all three runs independent products.
+
+    ``dact_of=y, dact=name`` selects the backward form ``c = name'(y) * (a @ b)`` elementwise, the
+    derivative taken from the activation's forward output ``y`` (``cleave_cuda_gemm_dact_f32``)."""
     batched = len(c.dims) == 3
     batch = c.dims[0] if batched else 1
     ad, bd, cd = (t.dims[1:] if batched else t.dims for t in (a, b, c))
@@ -200,6 +204,16 @@ def gemm_into(c: Tensor, a: Tensor, b: Tensor, *, trans_a=False, trans_b=False, 
     k2, n = (bd[1], bd[0]) if trans_b else bd
     if k != k2 or tuple(cd) != (m, n) or (batched and not (a.dims[0] == b.dims[0] == batch)):
         raise TypeError(f"gemm_into: shapes {a.dims}, {b.dims} -> {c.dims} do not agree")
+    if dact_of is not None:
+        if bias is not None or act != "identity":
+            raise TypeError("gemm_into: the backward form takes no bias and no forward activation")
+        if dact_of.dims != c.dims:
+            raise TypeError(f"gemm_into: dact_of has shape {dact_of.dims}, the product {c.dims}")
+        r = lib().cleave_cuda_gemm_dact_f32(c._h, a._h, b._h, batch, m, n, k, int(trans_a), int(trans_b), algo,
+                                            dact_of._h, ACT[dact])
+        if r != 0:
+            raise_last_error("gemm_into")
+        return c
     r = lib().cleave_cuda_gemm_ex_f32(c._h, a._h, b._h, batch, m, n, k, int(trans_a), int(trans_b), algo,
                                       bias._h if bias is not None else None, ACT[act])
     if r != 0:

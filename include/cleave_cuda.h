@@ -182,6 +182,14 @@ cleave_buf cleave_cuda_gemm_batched_f32(cleave_buf a, cleave_buf b, int32_t batc
 int32_t cleave_cuda_gemm_ex_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m,
                                 int32_t n, int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo,
                                 cleave_buf bias, int32_t act);
+/* Backward form of a layer: C = act'(y) (.) (op(A) * op(B)), elementwise product of the matrix product with the
+ * derivative of activation `act` taken from that activation's forward OUTPUT y (batch*m*n elements): tanh 1 - y^2,
+ * sigmoid y (1 - y), relu y > 0 (stdlib/num/num.cleave:222-223 exp / tanh rules, stdlib/nn/nn.cleave:54-64).  It is
+ * dZ = act'(H) (.) (dZ_next * W^T) of reverse mode in one pass; the result is bit-identical to
+ * cleave_cuda_gemm_ex_f32 followed by cleave_cuda_tanh_bwd_f32 / sigmoid_bwd / relu_bwd. */
+int32_t cleave_cuda_gemm_dact_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m,
+                                  int32_t n, int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo,
+                                  cleave_buf y, int32_t act);
 
 /* ------------------------------------------------------------------ compositions the programs spell out
  * bias add: a rows x cols tensor plus a tensor whose rows all equal `bias`

@@ -171,3 +171,41 @@ def test_non_finite_and_extreme_operands():
     one[0, :] = 0.5
     got = gemm(big, one, GEMM_3XTF32)
     assert np.isfinite(got).all() and np.allclose(got, np.float32(3.4028234e38) * 0.5, rtol=1e-6)
+
+
+@pytest.mark.parametrize("algo", [GEMM_EXACT, GEMM_3XTF32])
+@pytest.mark.parametrize("act", ["tanh", "sigmoid", "relu"])
+def test_backward_form_equals_product_then_derivative(algo, act):
+    # C = act'(y) * (A B): the fused epilogue must give, bit for bit, what the product followed by the
+    # elementwise derivative kernel gives, and the oracle's composition within the GEMM tolerance.
+    from cleave_b200 import nn
+    for (m, n, k, ta, tb) in [(256, 512, 128, False, True), (130, 72, 200, False, False), (4096, 1024, 256, False, True),
+                              (200, 260, 64, True, False)]:
+        a, b = workloads.gemm_inputs(m, n, k)
+        y = getattr(ref, act)(workloads.uniform_pm1(33, m, n))          # a plausible forward output
+        A = linalg.Tensor(np.ascontiguousarray(a.T) if ta else a)
+        B = linalg.Tensor(np.ascontiguousarray(b.T) if tb else b)
+        Y = linalg.Tensor(y)
+        fused = linalg.gemm_into(linalg.Tensor.empty(m, n), A, B, trans_a=ta, trans_b=tb, algo=algo, dact_of=Y, dact=act)
+        prod = linalg.gemm_into(linalg.Tensor.empty(m, n), A, B, trans_a=ta, trans_b=tb, algo=algo)
+        two_step = getattr(nn, act + "_bwd")(Y, prod)
+        cb.sync()
+        assert np.array_equal(fused.numpy(), two_step.numpy()), (m, n, k, act)
+        want = getattr(ref, act + "_bwd")(y, ref.matmul(a, b))
+        s = ref.matmul_absdot(a, b)
+        assert np.max(np.abs(fused.numpy().astype(np.float64) - want) / np.maximum(s, 1e-30)) <= TOL
+
+
+def test_backward_form_rejects_bad_arguments():
+    a, b = workloads.gemm_inputs(64, 64, 64)
+    A, B = linalg.Tensor(a), linalg.Tensor(b)
+    with pytest.raises(TypeError):
+        linalg.gemm_into(linalg.Tensor.empty(64, 64), A, B, dact_of=linalg.Tensor.empty(64, 32), dact="tanh")
+    with pytest.raises(TypeError):
+        linalg.gemm_into(linalg.Tensor.empty(64, 64), A, B, bias=linalg.Tensor(np.zeros(64, f32)),
+                         dact_of=linalg.Tensor.empty(64, 64), dact="tanh")
+    c = linalg.Tensor.empty(64, 64)
+    L = cb.lib()
+    r = L.cleave_cuda_gemm_dact_f32(c._h, A._h, B._h, 1, 64, 64, 64, 0, 0, 0, c._h, 3)
+    assert r < 0 and b"alias" in (L.cleave_cuda_last_error_message() or b"")
+    L.cleave_cuda_clear_error()
