@@ -69,3 +69,34 @@ def test_bad_handles_are_rejected_without_touching_them(built):
     assert L.cleave_cuda_gemm_f32(None, None, 2, 2, 2) is None
     L.cleave_cuda_free(bogus)                        # must not crash
     L.cleave_cuda_clear_error()
+
+
+def _cleave_externs():
+    """(file, symbol, number of C-level arguments) for every ``extern(cleave_cuda_*) fn`` of the shipped
+    cleave-side files.  An array parameter ``[T; N]`` is two C arguments (pointer, length) and its
+    ``const N`` companion none of its own (cleave/src/mlir_lower.rs:1096-1113)."""
+    out = []
+    base = os.path.join(ROOT, "cleave_b200", "cleave")
+    for dirpath, _, files in os.walk(base):
+        for fn in files:
+            if not fn.endswith(".cleave"):
+                continue
+            with open(os.path.join(dirpath, fn)) as f:
+                text = re.sub(r"//[^\n]*", "", f.read())
+            for sym, params in re.findall(r"extern\((cleave_cuda_\w+)\)\s*fn\s+\w+\s*\(([^)]*)\)", text):
+                n = 0
+                for prm in [x.strip() for x in params.split(",") if x.strip()]:
+                    if prm.startswith("const "):
+                        continue
+                    n += 2 if re.search(r":\s*\[", prm) else 1
+                out.append((fn, sym, n))
+    return out
+
+
+def test_cleave_side_bindings_name_real_entry_points():
+    from cleave_b200 import _lib
+    externs = _cleave_externs()
+    assert len(externs) >= 25
+    for fn, sym, nargs in externs:
+        assert sym in _lib.SIGNATURES, f"{fn}: {sym} is not in the C ABI"
+        assert len(_lib.SIGNATURES[sym][1]) == nargs, f"{fn}: {sym} takes {len(_lib.SIGNATURES[sym][1])} arguments"
