@@ -386,6 +386,99 @@ def run_batched_gemm(args):
         dist.destroy_process_group()
 
 
+def run_rowblock_gemm(args):
+    """Row-block sharded large GEMM (16384^3 by default, --size overrides): A and C are split by rows over
+    the ranks on tile boundaries, B is replicated into every rank's own HBM by an NCCL broadcast, no
+    collective in the product itself.  Strong scaling; reported with and without the broadcast."""
+    import torch
+    import torch.distributed as dist
+
+    import cleave_b200 as cb
+    from cleave_b200 import dp, linalg, workloads
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = cb.lib()
+    if L.cleave_cuda_init(local) != 0:
+        cb._lib.raise_last_error("init")
+    dp.use_torch_stream()
+    sz = args.size if args.size != 8192 else 16384
+    lo, hi = dp.row_block(sz, rank, world, tile=256)
+    rows = hi - lo
+    # this rank's rows of A (seeded per 1024-row band, so the union over ranks does not depend on G)
+    a_rows = np.concatenate([workloads.uniform_pm1(500 + band, 1024, sz)
+                             for band in range(lo // 1024, (hi + 1023) // 1024)])[lo % 1024:lo % 1024 + rows]
+    ta = linalg.Tensor(np.ascontiguousarray(a_rows))
+    del a_rows
+    tb = linalg.Tensor(workloads.uniform_pm1(2, sz, sz)) if rank == 0 else linalg.Tensor.empty(sz, sz)
+    tc = linalg.Tensor.empty(rows, sz)
+    b_view = dp.as_torch(tb)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    def bcast():
+        if world > 1:
+            dist.broadcast(b_view, src=0)
+
+    def product():
+        linalg.gemm_into(tc, ta, tb)
+
+    def both():
+        bcast()
+        product()
+
+    bcast()
+    for _ in range(args.warmup):
+        product()
+    l0 = L.cleave_cuda_kernel_launches()
+    ms = timed(product, args.steps)
+    launches = L.cleave_cuda_kernel_launches() - l0
+    ms_with = timed(both, args.steps)
+    # spot check against the other ranks' view of B: a checksum of B must agree everywhere after the broadcast
+    chk = torch.tensor([float(b_view[:: max(1, b_view.numel() // 4096)].double().sum())], device="cuda",
+                       dtype=torch.float64)
+    same = True
+    if world > 1:
+        lo_t, hi_t = chk.clone(), chk.clone()
+        dist.all_reduce(lo_t, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi_t, op=dist.ReduceOp.MAX)
+        same = bool(lo_t.item() == hi_t.item())
+    if rank == 0:
+        flops = 2.0 * sz ** 3
+        print(json.dumps({"metric": f"row-block f32 GEMM TFLOP/s ({sz}^3)", "value": flops / ms / 1e9, "unit": "TFLOP/s",
+                          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                          "data": "synthetic", "gpu_launches": int(launches),
+                          "with_broadcast": {"ms_per_step": ms_with, "value": flops / ms_with / 1e9,
+                                             "broadcast_bytes": 4 * sz * sz},
+                          "b_identical_on_all_ranks": same,
+                          "config": {"workload": f"C = A B, M = N = K = {sz}; A and C split by rows over {world} rank(s) on "
+                                                 "256-row tile boundaries, B replicated by an NCCL broadcast (outside "
+                                                 "the timed region for `value`, inside for `with_broadcast`)"}}),
+              flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_dp_mlp(args):
     """Configuration 4b: the 2-layer MLP trained data-parallel, global batch 32768 split evenly over
     the ranks, SGD lr 1e-3, gradients all-reduced (mean) with NCCL each step.  Strong scaling."""
@@ -481,7 +574,8 @@ def main():
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "dp_mlp", "ops", "gemm_sweep", "batched_gemm"],
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "dp_mlp", "ops", "gemm_sweep", "batched_gemm",
+                                                            "rowblock_gemm"],
                     help="gemm = the headline; the others are secondary configurations")
     ap.add_argument("--ops-rows", type=int, default=4096, help="ops: rows of the 4096-column test tensors")
     ap.add_argument("--max-size", type=int, default=0, help="gemm_sweep: skip shapes with a dimension above this")
@@ -509,7 +603,7 @@ def main():
     os.dup2(2, 1)
     sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
     runner = {"dp_mlp": run_dp_mlp, "ops": run_ops, "gemm_sweep": run_gemm_sweep,
-              "batched_gemm": run_batched_gemm}.get(args.workload)
+              "batched_gemm": run_batched_gemm, "rowblock_gemm": run_rowblock_gemm}.get(args.workload)
     if runner:
         runner(args)
         return
