@@ -33,8 +33,10 @@ def gemm_errors(got: np.ndarray, a: np.ndarray, b: np.ndarray, ref32: np.ndarray
 def assert_gemm_close(got, a, b, ref32=None, what=""):
     e = gemm_errors(got, a, b, ref32)
     assert e["comp_vs_ref32"] <= TOL and e["norm_vs_ref32"] <= TOL, (what, e)
-    # not worse than a few times the reference loop's own distance from the exact product
-    assert e["comp_vs_f64"] <= max(4 * e["f32_vs_f64"], 1e-6), (what, e)
+    # not worse than a few times the reference loop's own distance from the exact product; the floor is the
+    # representation error of the split itself when the operands are split inside the kernel (the dropped
+    # a_lo*b_lo term, up to 2^-20 |a b|, plus the rounding of the two lo parts, 2^-21 each: ~2e-6)
+    assert e["comp_vs_f64"] <= max(4 * e["f32_vs_f64"], 2e-6), (what, e)
     return e
 
 

@@ -209,3 +209,24 @@ def test_backward_form_rejects_bad_arguments():
     r = L.cleave_cuda_gemm_dact_f32(c._h, A._h, B._h, 1, 64, 64, 64, 0, 0, 0, c._h, 3)
     assert r < 0 and b"alias" in (L.cleave_cuda_last_error_message() or b"")
     L.cleave_cuda_clear_error()
+
+
+def test_seeded_random_shapes_through_every_dispatch_decision():
+    # 40 seeded problems with arbitrary (also odd) extents, layouts and algorithms: whatever route the
+    # library picks -- exact, in-kernel split, lo planes, padded planes -- the result obeys the same bound.
+    rng = np.random.default_rng(20260)
+    for case in range(40):
+        m, n, k = (int(rng.integers(1, 700)) for _ in range(3))
+        if case % 4 == 0:            # force TMA-addressable extents now and then
+            m, n, k = (max(4, x // 4 * 4) for x in (m, n, k))
+        ta, tb = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        algo = [linalg.GEMM_AUTO, GEMM_3XTF32, GEMM_EXACT][int(rng.integers(0, 3))]
+        a = workloads.uniform_pm1(1000 + case, m, k)
+        b = workloads.uniform_pm1(2000 + case, k, n)
+        got = gemm(np.ascontiguousarray(a.T) if ta else a, np.ascontiguousarray(b.T) if tb else b, algo,
+                   trans_a=ta, trans_b=tb)
+        want = ref.matmul(a, b)
+        if algo == GEMM_EXACT:
+            assert np.array_equal(got, want), (case, m, n, k, ta, tb)
+        else:
+            assert_gemm_close(got, a, b, want, (case, m, n, k, ta, tb, algo))

@@ -44,6 +44,11 @@ def test_mlp2_forward_backward_matches_oracle(batch, d_in, d_hid, d_out):
     check(inter["dH"].numpy(), want["dH"], adZ2 @ np.abs(W2).T, "dH")
     check(net.dW1.numpy(), want["dW1"], absX.T @ adZ1, "dW1")
     check(net.db1.numpy(), want["db1"], adZ1.sum(axis=0), "db1")
+    # The production pass (no intermediates kept) fuses act1'(H) into the dH product's epilogue: same bits.
+    kept = net.grads.numpy().copy()
+    loss2 = net.forward_backward(linalg.Tensor(X), linalg.Tensor(T))
+    cb.sync()
+    assert loss2 == loss and np.array_equal(net.grads.numpy(), kept)
 
 
 def test_xor_training_through_the_device_path():
