@@ -130,10 +130,17 @@ static __device__ unsigned int g_reduce_done = 0;
 // shared memory in ty order; splits are combined by the second stage in split order.
 constexpr int kCsTx = 32, kCsTy = 8;
 
+constexpr int kCsMaxStrips = 2048;   // strips that can finish in the same launch (one completion counter each)
+static __device__ unsigned int g_colsum_done[kCsMaxStrips];
+
+// `out` != null: single launch -- the last CTA of a column strip to finish (a counter per strip, the
+// only atomic) adds the strip's partial sums in split order and writes the result.  `out` == null:
+// only the partials are written and colsum_stage2 combines them (more strips than counters).
 __global__ void __launch_bounds__(kCsTx* kCsTy) colsum_stage1(const float* __restrict__ x, int rows, int cols,
                                                                int rows_per_split, float* __restrict__ partials,
-                                                               int vec) {
+                                                               int vec, float* __restrict__ out) {
   __shared__ float4 sm[kCsTy][kCsTx];
+  __shared__ int is_last;
   const int tx = threadIdx.x % kCsTx, ty = threadIdx.x / kCsTx;
   const int c0 = (blockIdx.x * kCsTx + tx) * 4;
   const int r_lo = blockIdx.y * rows_per_split;
@@ -172,6 +179,41 @@ __global__ void __launch_bounds__(kCsTx* kCsTy) colsum_stage1(const float* __res
     if (c0 + 2 < cols) p[2] = t.z;
     if (c0 + 3 < cols) p[3] = t.w;
   }
+  if (out == nullptr) return;
+  // ---- the strip's last CTA combines the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&g_colsum_done[blockIdx.x], 1u) == gridDim.y - 1 ? 1 : 0;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int splits = gridDim.y;
+  float4 part = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c0 < cols) {
+    // thread row ty takes splits ty, ty + 8, ... in increasing order; the 8 rows are then added in ty order
+    for (int sidx = ty; sidx < splits; sidx += kCsTy) {
+      const float* p = partials + (int64_t)sidx * cols + c0;
+      part.x = __fadd_rn(part.x, __ldcg(p));
+      if (c0 + 1 < cols) part.y = __fadd_rn(part.y, __ldcg(p + 1));
+      if (c0 + 2 < cols) part.z = __fadd_rn(part.z, __ldcg(p + 2));
+      if (c0 + 3 < cols) part.w = __fadd_rn(part.w, __ldcg(p + 3));
+    }
+  }
+  sm[ty][tx] = part;
+  __syncthreads();
+  if (ty == 0 && c0 < cols) {
+    float4 t = sm[0][tx];
+#pragma unroll
+    for (int j = 1; j < kCsTy; ++j) {
+      float4 u = sm[j][tx];
+      t.x = __fadd_rn(t.x, u.x); t.y = __fadd_rn(t.y, u.y); t.z = __fadd_rn(t.z, u.z); t.w = __fadd_rn(t.w, u.w);
+    }
+    out[c0] = t.x;
+    if (c0 + 1 < cols) out[c0 + 1] = t.y;
+    if (c0 + 2 < cols) out[c0 + 2] = t.z;
+    if (c0 + 3 < cols) out[c0 + 3] = t.w;
+  }
+  if (threadIdx.x == 0) g_colsum_done[blockIdx.x] = 0;   // ready for the next launch (stream order)
 }
 
 __global__ void __launch_bounds__(kRThreads) colsum_stage2(const float* __restrict__ partials, int splits, int cols,
@@ -572,9 +614,15 @@ static bool colsum_launch(const float* x, float* out, int rows, int cols) {
   if (!partials) return false;
   int vec = (aligned16(x) && cols % 4 == 0) ? 1 : 0;
   cudaStream_t s = ctx().stream;
-  colsum_stage1<<<dim3(strips, splits), kCsTx * kCsTy, 0, s>>>(x, rows, cols, rows_per_split, partials, vec);
-  colsum_stage2<<<ceil_div(cols, kRThreads), kRThreads, 0, s>>>(partials, splits, cols, out);
-  count_launch(2);
+  if (strips <= kCsMaxStrips) {
+    colsum_stage1<<<dim3(strips, splits), kCsTx * kCsTy, 0, s>>>(x, rows, cols, rows_per_split, partials, vec, out);
+    count_launch(1);
+  } else {
+    colsum_stage1<<<dim3(strips, splits), kCsTx * kCsTy, 0, s>>>(x, rows, cols, rows_per_split, partials, vec,
+                                                                  nullptr);
+    colsum_stage2<<<ceil_div(cols, kRThreads), kRThreads, 0, s>>>(partials, splits, cols, out);
+    count_launch(2);
+  }
   bool ok = cuda_ok(cudaGetLastError(), "colsum launch");
   scratch_free(partials);
   return ok;
