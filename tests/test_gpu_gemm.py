@@ -230,3 +230,20 @@ def test_seeded_random_shapes_through_every_dispatch_decision():
             assert np.array_equal(got, want), (case, m, n, k, ta, tb)
         else:
             assert_gemm_close(got, a, b, want, (case, m, n, k, ta, tb, algo))
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True)])
+def test_pair_kernel_route_sampled_rows(trans_a, trans_b):
+    # Outputs above 4096^2 take the padded-planes route on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2).
+    # 96 sampled rows are checked as the reference loop computes them, plus the linearity checksum over
+    # the whole result; m is not a multiple of 256 so the last tile-row is ragged.
+    m, n, k = 8192 + 136, 4096, 1536
+    a, b = workloads.gemm_inputs(m, n, k)
+    got = gemm(np.ascontiguousarray(a.T) if trans_a else a, np.ascontiguousarray(b.T) if trans_b else b,
+               GEMM_3XTF32, trans_a=trans_a, trans_b=trans_b)
+    rows = np.concatenate([np.random.default_rng(1).choice(m, 88, replace=False), np.arange(m - 8, m)])
+    assert_gemm_close(np.ascontiguousarray(got[rows]), np.ascontiguousarray(a[rows]), b, what=("pair", trans_a, trans_b))
+    lhs = a.astype(np.float64).sum(axis=0) @ b.astype(np.float64)
+    rhs = got.astype(np.float64).sum(axis=0)
+    scale = np.abs(a).astype(np.float64).sum(axis=0) @ np.abs(b).astype(np.float64)
+    assert np.max(np.abs(lhs - rhs) / scale) <= TOL
