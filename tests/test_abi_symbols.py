@@ -100,3 +100,14 @@ def test_cleave_side_bindings_name_real_entry_points():
     for fn, sym, nargs in externs:
         assert sym in _lib.SIGNATURES, f"{fn}: {sym} is not in the C ABI"
         assert len(_lib.SIGNATURES[sym][1]) == nargs, f"{fn}: {sym} takes {len(_lib.SIGNATURES[sym][1])} arguments"
+
+
+def test_generated_rust_bindings_are_current_and_complete():
+    import subprocess
+    import sys
+    gen = os.path.join(ROOT, "cleave_b200", "cleave", "gen_rust_bindings.py")
+    assert subprocess.run([sys.executable, gen, "--check"]).returncode == 0, "run gen_rust_bindings.py"
+    with open(os.path.join(ROOT, "cleave_b200", "cleave", "rust", "cleave_cuda_sys.rs")) as f:
+        text = f.read()
+    for name in _declared_symbols():
+        assert f"pub fn {name}(" in text and f'register_symbol("{name}"' in text, name
