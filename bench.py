@@ -270,6 +270,16 @@ def run_ops(args):
         "sum": (lambda i: nn.sum(A[i]), 4 * n), "max_of": (lambda i: nn.max_of(A[i]), 4 * n),
         "mse_fwd_bwd": (lambda i: nn.mse(Y[i], B[i]), 12 * n),
     }
+    # the same reduction kernel with its result left on the device (no host wait per call): what the
+    # kernel alone achieves, next to the synchronous scalar-returning entry above
+    dev_out = linalg.Tensor.empty(1)
+    stream = ctypes.c_void_p(L.cleave_cuda_get_stream() or 0)
+
+    def sum_dev(i):
+        if L.cleave_cuda_sum_noalloc_f32(ctypes.c_void_p(A[i].data_ptr), n, ctypes.c_void_p(dev_out.data_ptr),
+                                         stream) != 0:
+            cb._lib.raise_last_error("sum_noalloc")
+    cases["sum_device_result"] = (sum_dev, 4 * n)
     out = {}
     for name, (fn, nbytes) in cases.items():
         def rotation():
