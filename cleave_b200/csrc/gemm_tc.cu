@@ -803,11 +803,15 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
   } else if (g_direct == 3 || (g_direct == 1 && (int64_t)g.m * g.n <= (1ll << 24))) {
     if (lo_plane_eligible(g)) return launch_lo_plane(g);
   }
-  const int bk = 16;
+  // K-block of the pair kernel: 32 (three 64 KiB stages, 128-byte rows) unless CLEAVE_CUDA_GEMM_PAIR_BK=16 asks for
+  // six 32 KiB stages; measured on one box at 8192^3: 3.85-3.90 ms against 3.97-4.04 ms
+  static const int pair_bk =
+      (getenv("CLEAVE_CUDA_GEMM_PAIR_BK") && atoi(getenv("CLEAVE_CUDA_GEMM_PAIR_BK")) == 16) ? 16 : 32;
   // 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) for the large problems this path serves:
   // measured 1-2 % faster at 4096^3 and 8192^3 (3.71-3.79 vs 3.74-3.84 ms); small ragged problems
   // keep 128-row tiles, which pad less.
   const bool pair = g_pair >= 0 ? g_pair == 1 : (int64_t)g.m * g.n > (1ll << 24);
+  const int bk = pair ? pair_bk : 16;
   const int Kp = round_up(g.k, 32);
   const int Mp = round_up(g.m, pair ? 256 : BM);
   const int Np = round_up(g.n, BN);
@@ -857,7 +861,7 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.status = ctx().status_dev;
     if (pair) {
       p.mblks = Mp / 256;
-      ok = run_tc_pair(a_mn, b_mn, maps, p);
+      ok = run_tc_pair(a_mn, b_mn, maps, p, bk);
     } else {
       ok = run_tc_layout<kPathPlanes>(a_mn, b_mn, maps, p);
     }

@@ -5,7 +5,9 @@
 // (A 128 + B 128 rows per K-block instead of 128 + 256).  Each CTA keeps the accumulator of its own
 // 128 rows in its own TMEM and drains / stores it exactly as the one-CTA kernel does.
 //
-// Operands: the padded [hi | lo] planes of the pre-pass (both operands padded to 256 rows).
+// Operands: the padded [hi | lo] planes of the pre-pass (both operands padded to 256 rows).  The K-block is a
+// template parameter: 32 (three stages of 64 KiB, K-major rows of 128 bytes in the 128-byte swizzle; the default,
+// ~3 % faster) or 16 (six stages of 32 KiB, 64-byte rows).
 //
 // Roles per CTA (320 threads): warp 0 producer, warp 1 MMA issuer (only in the cluster's CTA 0),
 // warps 2-9 drain + epilogue.  Signals:
@@ -20,12 +22,14 @@
 
 namespace cleave {
 
-constexpr int kPairStages = 6;
 constexpr int kRingBytesPair = 192 * 1024;
-constexpr int kPairPlaneBytes = 128 * 64;                  // 128 rows x 16 floats: one plane of A, or of half of B
-constexpr int kPairStageBytes = 4 * kPairPlaneBytes;       // [A hi | A lo | B hi | B lo]
+template <int BK>
+struct PairCfg {
+  static constexpr int kPlaneBytes = 128 * BK * 4;         // 128 rows x BK floats: one plane of A, or of half of B
+  static constexpr int kStageBytes = 4 * kPlaneBytes;      // [A hi | A lo | B hi | B lo]
+  static constexpr int kStages = kRingBytesPair / kStageBytes;   // 6 (BK 16) or 3 (BK 32)
+};
 constexpr int kPairGroupM = 8;                             // 256-row tile-rows per rasterisation group
-static_assert(kPairStages * kPairStageBytes <= kRingBytesPair, "ring");
 constexpr int kPairSmemBytes = kRingBytesPair + kEpiWarps * 32 * 128 + 1024;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -97,11 +101,13 @@ __device__ __forceinline__ void decode_pair_tile(int t, const TcParams& p, int& 
   nb = r / rows_here;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int BK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         TcParams p) {
-  constexpr int BK = 16;
+  constexpr int kPairStages = PairCfg<BK>::kStages;
+  constexpr int kPairPlaneBytes = PairCfg<BK>::kPlaneBytes;
+  constexpr int kPairStageBytes = PairCfg<BK>::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kPairStages];
   __shared__ __align__(8) uint64_t bar_empty[kPairStages];
@@ -224,8 +230,10 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
               const uint32_t off_a = A_MN ? kk * 1024 : kk * UMMA_K * 4;
               const uint32_t off_b = B_MN ? kk * 1024 : kk * UMMA_K * 4;
-              constexpr uint32_t sbo_a = A_MN ? 512u : 512u, lay_a = A_MN ? 1u : 4u;   // K-major: 8 rows x 64 bytes
-              constexpr uint32_t sbo_b = B_MN ? 512u : 512u, lay_b = B_MN ? 1u : 4u;
+              // K-major rows are BK * 4 bytes: 64-byte swizzle (BK 16) or 128-byte swizzle (BK 32), 8-row groups
+              constexpr uint32_t kmaj_sbo = 8 * BK * 4, kmaj_lay = BK == 32 ? 2u : 4u;
+              constexpr uint32_t sbo_a = A_MN ? 512u : kmaj_sbo, lay_a = A_MN ? 1u : kmaj_lay;
+              constexpr uint32_t sbo_b = B_MN ? 512u : kmaj_sbo, lay_b = B_MN ? 1u : kmaj_lay;
               constexpr uint32_t lbo_a = A_MN ? BK * 128u : 16u, lbo_b = B_MN ? BK * 128u : 16u;
               const uint64_t da_hi = make_smem_desc(a_hi + off_a, sbo_a, lay_a, lbo_a);
               const uint64_t da_lo = make_smem_desc(a_lo + off_a, sbo_a, lay_a, lbo_a);
@@ -301,12 +309,12 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   }
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int BK>
 static bool run_pair(const CUtensorMap* maps, const TcParams& p) {
   static bool attr_set = false;
   if (!attr_set) {
-    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kPairSmemBytes),
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_pair_kernel<A_MN, B_MN, BK>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes),
                  "cudaFuncSetAttribute(pair gemm)"))
       return false;
     attr_set = true;
@@ -315,15 +323,21 @@ static bool run_pair(const CUtensorMap* maps, const TcParams& p) {
   int clusters = ctx().sm_count / 2;
   if (tiles < clusters) clusters = tiles;
   profile_mark(true);
-  gemm_3xtf32_pair_kernel<A_MN, B_MN><<<2 * clusters, kGemmThreads, kPairSmemBytes, ctx().stream>>>(maps[0], maps[1], p);
+  gemm_3xtf32_pair_kernel<A_MN, B_MN, BK>
+      <<<2 * clusters, kGemmThreads, kPairSmemBytes, ctx().stream>>>(maps[0], maps[1], p);
   profile_mark(false);
   count_launch();
   return cuda_ok(cudaGetLastError(), "tcgen05 pair GEMM launch");
 }
 
-bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p) {
-  return a_mn ? (b_mn ? run_pair<true, true>(maps, p) : run_pair<true, false>(maps, p))
-              : (b_mn ? run_pair<false, true>(maps, p) : run_pair<false, false>(maps, p));
+template <int BK>
+static bool run_pair_bk(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p) {
+  return a_mn ? (b_mn ? run_pair<true, true, BK>(maps, p) : run_pair<true, false, BK>(maps, p))
+              : (b_mn ? run_pair<false, true, BK>(maps, p) : run_pair<false, false, BK>(maps, p));
+}
+
+bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk) {
+  return bk == 32 ? run_pair_bk<32>(a_mn, b_mn, maps, p) : run_pair_bk<16>(a_mn, b_mn, maps, p);
 }
 
 }  // namespace cleave

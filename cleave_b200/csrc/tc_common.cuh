@@ -337,6 +337,6 @@ __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcPara
 
 // Pair kernel (gemm_tc_pair.cu): two CTAs of a cluster share one 256 x 256 tile (tcgen05 cta_group::2).
 // `maps` = {A planes, B planes}; the planes must be padded to 256 rows for both operands.
-bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p);
+bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk);
 
 }  // namespace cleave
