@@ -44,7 +44,7 @@ M = N = K = 8192          # headline size; --size overrides it for profiling cap
 FLOPS = 2.0 * M * N * K
 # DRAM traffic of one tcgen05 GEMM kernel launch at 8192^3, from a one-pass ncu capture of this
 # program at full size (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 4.745e9 + 272.4e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 7.599e9 + 277.6e6
 
 
 def measured_peaks():
