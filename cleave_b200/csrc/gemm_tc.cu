@@ -714,6 +714,7 @@ static bool launch_direct(const GemmArgs& g) {
   TcParams p;
   p.a_blocked = a_blocked;
   p.b_blocked = b_blocked;
+  p.c_tma = 0;
   p.b_box_rows = b_box_rows;
   p.c = g.c;
   p.bias = g.bias;
@@ -765,6 +766,7 @@ static bool launch_lo_plane(const GemmArgs& g) {
     TcParams p;
     p.a_blocked = a_mn;
     p.b_blocked = b_mn;
+    p.c_tma = 0;
     p.b_box_rows = BN;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
     p.bias = g.bias;
@@ -784,6 +786,20 @@ static bool launch_lo_plane(const GemmArgs& g) {
   scratch_free(wa);
   scratch_free(wb);
   return ok;
+}
+
+// Tensor map over the output for TMA stores: dims {n, m, batch}, box 32 x 32 floats, 128-byte swizzle (the layout
+// of the drain warps' shared staging tile).  Needs a 16-byte aligned C and n a multiple of 4.
+static bool make_c_map(CUtensorMap* map, float* c, int m, int n, int batch) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)n * 4, (cuuint64_t)m * n * 4};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+         CUDA_SUCCESS;
 }
 
 bool launch_gemm_3xtf32(const GemmArgs& g) {
@@ -857,10 +873,14 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.nblks = Np / BN;
     p.act = g.act;
     p.a_blocked = p.b_blocked = 0;
+    p.c_tma = 0;
     p.b_box_rows = BN;
     p.status = ctx().status_dev;
     if (pair) {
       p.mblks = Mp / 256;
+      // full tiles leave through TMA stores when a tensor map can describe C
+      static const bool tma_store = !(getenv("CLEAVE_CUDA_GEMM_TMA_STORE") && getenv("CLEAVE_CUDA_GEMM_TMA_STORE")[0] == '0');
+      p.c_tma = (tma_store && aligned16(p.c) && g.n % 4 == 0 && make_c_map(&maps[2], p.c, g.m, g.n, nb)) ? 1 : 0;
       ok = run_tc_pair(a_mn, b_mn, maps, p, bk);
     } else {
       ok = run_tc_layout<kPathPlanes>(a_mn, b_mn, maps, p);

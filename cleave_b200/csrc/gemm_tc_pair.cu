@@ -3,7 +3,8 @@
 // own 128 of the tile's 256 B rows; the MMA reads B from both CTAs' shared memory, so per SM the
 // operand traffic into shared memory and out of it to the tensor pipe is 2/3 of the one-CTA kernel's
 // (A 128 + B 128 rows per K-block instead of 128 + 256).  Each CTA keeps the accumulator of its own
-// 128 rows in its own TMEM and drains / stores it exactly as the one-CTA kernel does.
+// 128 rows in its own TMEM and drains it exactly as the one-CTA kernel does; full tiles are stored with TMA
+// (32 x 32 bulk tensor stores from the drain warps' swizzled staging tiles), ragged ones with plain stores.
 //
 // Operands: the padded [hi | lo] planes of the pre-pass (both operands padded to 256 rows).  The K-block is a
 // template parameter: 32 (three stages of 64 KiB, K-major rows of 128 bytes in the 128-byte swizzle; the default,
@@ -104,7 +105,7 @@ __device__ __forceinline__ void decode_pair_tile(int t, const TcParams& p, int& 
 template <bool A_MN, bool B_MN, int BK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        TcParams p) {
+                        const __grid_constant__ CUtensorMap map_c, TcParams p) {
   constexpr int kPairStages = PairCfg<BK>::kStages;
   constexpr int kPairPlaneBytes = PairCfg<BK>::kPlaneBytes;
   constexpr int kPairStageBytes = PairCfg<BK>::kStageBytes;
@@ -291,8 +292,11 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) break;
-      tile_epilogue(sum, p, b, mb * 256 + (int)rank * 128, nb, q, half, lane, vec_ok, stage_tile);
+      tile_epilogue(sum, p, b, mb * 256 + (int)rank * 128, nb, q, half, lane, vec_ok, stage_tile,
+                    p.c_tma ? &map_c : nullptr);
     }
+    // this warp's bulk stores have reached memory before the CTA may exit
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ------------------------------------------------------------------ teardown
@@ -324,7 +328,7 @@ static bool run_pair(const CUtensorMap* maps, const TcParams& p) {
   if (tiles < clusters) clusters = tiles;
   profile_mark(true);
   gemm_3xtf32_pair_kernel<A_MN, B_MN, BK>
-      <<<2 * clusters, kGemmThreads, kPairSmemBytes, ctx().stream>>>(maps[0], maps[1], p);
+      <<<2 * clusters, kGemmThreads, kPairSmemBytes, ctx().stream>>>(maps[0], maps[1], maps[2], p);
   profile_mark(false);
   count_launch();
   return cuda_ok(cudaGetLastError(), "tcgen05 pair GEMM launch");

@@ -204,6 +204,7 @@ struct TcParams {
   int act;
   int a_blocked, b_blocked;   // direct path, MN-major operand: one 4-D box per stage instead of 32-wide boxes
   int b_box_rows;             // direct path: rows of B fetched and split per stage (BN, less when n is small)
+  int c_tma;                  // pair kernel: a tensor map over C exists (16-byte aligned, n a multiple of 4): TMA stores
   DeviceStatus* status;
 };
 
@@ -235,8 +236,11 @@ __device__ __forceinline__ void report(DeviceStatus* st, int code, int where, in
 // Epilogue of one drain warp: its 32 rows x 128 columns of a tile (rows tile_row0 + 32q .., columns
 // nb*BN + 128*half ..), one row per lane in `sum`: + bias[col], activation, store to C.
 // `stage`: this warp's 4 KiB of shared memory for the coalesced store.
+// `map_c` (may be null): tensor map over C {n, m, batch}, box 32 x 32, 128-byte swizzle; with it a full tile
+// leaves through TMA stores issued by one lane per warp instead of the warp's own loads and stores.
 __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcParams& p, int b, int tile_row0, int nb,
-                                              int q, int half, int lane, bool vec_ok, float4* stage) {
+                                              int q, int half, int lane, bool vec_ok, float4* stage,
+                                              const CUtensorMap* map_c = nullptr) {
   const int row = tile_row0 + q * 32 + lane;
   const int col0 = nb * BN + half * (BN / 2);
   const bool full_tile = (tile_row0 + BM <= p.m) && (nb * BN + BN <= p.n);   // uniform over the warps of a tile
@@ -316,6 +320,30 @@ __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcPara
     // lines.  So, 32 columns at a time, every thread parks its 8 16-byte words in a
     // warp-private shared tile (word j of row r at slot j ^ (r & 7): conflict free both ways)
     // and the warp then writes 4 rows x 128 bytes per instruction.
+    if (map_c != nullptr) {
+      // The shared tile (word j of row r at slot j ^ (r & 7), rows of 128 bytes, 1024-byte aligned) is exactly
+      // TMA's 128-byte swizzle, so each 32 x 32 block goes out as one bulk tensor store.
+      const uint32_t stage_addr = smem_u32(stage);
+#pragma unroll
+      for (int pass = 0; pass < BN / 64; ++pass) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          stage[lane * 8 + (j ^ (lane & 7))] = make_float4(sum[32 * pass + 4 * j], sum[32 * pass + 4 * j + 1],
+                                                           sum[32 * pass + 4 * j + 2], sum[32 * pass + 4 * j + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the copy engine
+        __syncwarp();
+        if (lane == 0) {
+          asm volatile(
+              "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+              ::"l"(map_c), "r"(stage_addr), "r"(col0 + 32 * pass), "r"(tile_row0 + q * 32), "r"(b)
+              : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the tile may be overwritten
+        }
+        __syncwarp();
+      }
+      return;
+    }
     float* cblock = p.c + ((int64_t)b * p.m + tile_row0 + q * 32) * (int64_t)p.n + col0;
 #pragma unroll
     for (int pass = 0; pass < BN / 64; ++pass) {
@@ -336,7 +364,8 @@ __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcPara
 }
 
 // Pair kernel (gemm_tc_pair.cu): two CTAs of a cluster share one 256 x 256 tile (tcgen05 cta_group::2).
-// `maps` = {A planes, B planes}; the planes must be padded to 256 rows for both operands.
+// `maps` = {A planes, B planes, C}; the planes must be padded to 256 rows for both operands; the map over C
+// ({n, m, batch}, box 32 x 32, 128-byte swizzle) is read only when p.c_tma is set.
 bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk);
 
 }  // namespace cleave
