@@ -29,7 +29,7 @@ SHAPES = [(128, 256, 16), (128, 256, 64), (256, 512, 128), (100, 200, 52), (132,
           (129, 257, 33), (5, 300, 7)]
 
 
-CALLS = {"gemms": 0, "unaddressable": 0}
+CALLS = {"gemms": 0, "unaddressable": 0, "other": 0}
 
 
 def run(a, b, trans_a=False, trans_b=False, bias=None, act="identity", batch=None):
@@ -78,6 +78,19 @@ def main() -> int:
         got = run(a, b, bias=bias, act=act)
         assert np.max(np.abs(got.astype(np.float64) - want) / np.maximum(s, 1e-30)) <= TOL, act
         cases += 1
+    # backward form: act'(y) * (a b) in the epilogue equals the product followed by the derivative kernel
+    from cleave_b200 import nn
+    y = ref.tanh(workloads.uniform_pm1(33, 256, 512))
+    ta_, tb_, ty_ = linalg.Tensor(a), linalg.Tensor(b), linalg.Tensor(y)
+    fused = linalg.gemm_into(linalg.Tensor.empty(256, 512), ta_, tb_, algo=GEMM_3XTF32, dact_of=ty_, dact="tanh")
+    prod = linalg.gemm_into(linalg.Tensor.empty(256, 512), ta_, tb_, algo=GEMM_3XTF32)
+    CALLS["gemms"] += 2
+    before = cb.lib().cleave_cuda_kernel_launches()
+    two_step = nn.tanh_bwd(ty_, prod)
+    CALLS["other"] = cb.lib().cleave_cuda_kernel_launches() - before      # not a GEMM launch
+    cb.sync()
+    assert np.array_equal(fused.numpy(), two_step.numpy())
+    cases += 1
     # exactly representable data: both paths must reproduce the reference loop bit for bit
     rng = np.random.default_rng(0)
     a = rng.integers(-8, 9, (256, 384)).astype(f32)
@@ -95,7 +108,7 @@ def main() -> int:
     got = run(a, b)
     assert np.isnan(got[3]).all() and not np.isnan(np.delete(got, 3, axis=0)).any()
     cases += 3
-    print("OK", cases, CALLS["gemms"], CALLS["unaddressable"], cb.lib().cleave_cuda_kernel_launches())
+    print("OK", cases, CALLS["gemms"], CALLS["unaddressable"], cb.lib().cleave_cuda_kernel_launches() - CALLS["other"])
     return 0
 
 
