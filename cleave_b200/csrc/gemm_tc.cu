@@ -173,6 +173,9 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 for (int j = 0; j < BN / 32; ++j)
                   if (j * 32 < p.b_box_rows) tma_load_3d(sb + j * (BK * 128), &map_b, full, nb * BN + j * 32, kb * BK, b);
               }
+            } else if (p.b_sliced) {
+              // K-sliced view of a row-major operand: the map's dimensions are {k in slice, slice, row}
+              tma_load_3d(sb, &map_b, full, kb * BK, b, nb * BN);
             } else {
               tma_load_3d(sb, &map_b, full, kb * BK, nb * BN, b);
             }
@@ -569,6 +572,7 @@ static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 // of writing MN-major planes.
 static bool g_mn_major = true;
 static int g_direct = 1;
+static bool g_narrow = true;   // CLEAVE_CUDA_GEMM_NARROW=0: no transposed split-K route for narrow outputs
 static int g_pair = -1;   // CLEAVE_CUDA_GEMM_PAIR: 1 / 0 = always / never run the padded-planes path on CTA pairs
 static void read_options() {
   static bool done = false;
@@ -578,6 +582,8 @@ static void read_options() {
   if (mn && mn[0] == '0') g_mn_major = false;
   const char* d = getenv("CLEAVE_CUDA_GEMM_DIRECT");
   if (d && (d[0] == '0' || d[0] == '2' || d[0] == '3')) g_direct = d[0] - '0';
+  const char* nr = getenv("CLEAVE_CUDA_GEMM_NARROW");
+  if (nr && nr[0] == '0') g_narrow = false;
   const char* pr = getenv("CLEAVE_CUDA_GEMM_PAIR");
   if (pr && (pr[0] == '0' || pr[0] == '1')) g_pair = pr[0] - '0';
 }
@@ -715,6 +721,7 @@ static bool launch_direct(const GemmArgs& g) {
   p.a_blocked = a_blocked;
   p.b_blocked = b_blocked;
   p.c_tma = 0;
+  p.b_sliced = 0;
   p.b_box_rows = b_box_rows;
   p.c = g.c;
   p.bias = g.bias;
@@ -730,6 +737,112 @@ static bool launch_direct(const GemmArgs& g) {
   p.act = g.act;
   p.status = ctx().status_dev;
   return run_tc_layout<kPathDirect>(a_mn, b_mn, maps, p);
+}
+
+// ---- narrow C (n <= 128): transposed, split-K ---------------------------------------------------------------
+// A tcgen05.mma with M = 128 takes about as long at N = 64 as at N = 256 (measured), so with C's narrow
+// dimension on N the kernel is bound by its MMA count.  Here C^T = B^T A^T is computed instead: the narrow
+// dimension lies on M (one tile row, padded to 128) and the long one runs along N in full 256-wide
+// tiles -- half as many MMAs or fewer.  That leaves only m/256 tiles, so K is cut into S slices that run as the S
+// entries of a batch (B is [k, n]: a K-slice of it is a dense block; A is [m, k]: a K-slice is a strided
+// view, which a tensor map expresses), and a last pass adds the S partial results in slice order and
+// transposes them into C.
+__global__ void __launch_bounds__(256) sum_transpose_kernel(const float* __restrict__ part, float* __restrict__ c,
+                                                            int slices, int n, int m) {
+  // part: [slices][n][m]; c: [m][n].  32 x 32 tiles through shared memory, both sides coalesced.
+  __shared__ float tile[32][33];
+  const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 32;      // i along m, j along n
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;    // 32 x 8
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int j = j0 + ty + 8 * r, i = i0 + tx;
+    float acc = 0.0f;
+    if (j < n && i < m)
+      for (int sl = 0; sl < slices; ++sl) acc = __fadd_rn(acc, part[((int64_t)sl * n + j) * m + i]);
+    tile[ty + 8 * r][tx] = acc;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = i0 + ty + 8 * r, j = j0 + tx;
+    if (i < m && j < n) c[(int64_t)i * n + j] = tile[tx][ty + 8 * r];
+  }
+}
+
+// Number of K slices for the transposed route, 0 if it does not apply.
+static int narrow_slices(const GemmArgs& g) {
+  if (g.batch != 1 || g.trans_a || g.trans_b || g.bias || g.dact_y || g.act != CLEAVE_ACT_IDENTITY) return 0;
+  if (g.n > BM || g.n % 4 != 0 || g.m < 2048 || g.k < 2048 || g.k % 16 != 0) return 0;
+  if (!aligned16(g.a) || !aligned16(g.b) || !aligned16(g.c)) return 0;
+  const int tiles = ceil_div(g.m, BN);
+  int s = ctx().sm_count / tiles;
+  if (s < 1) s = 1;
+  if (s > 16) s = 16;
+  while (s > 1 && (g.k % s != 0 || (g.k / s) % 16 != 0 || g.k / s < 512)) --s;
+  return s;
+}
+
+static bool launch_narrow_transposed(const GemmArgs& g, int slices) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  const int ks = g.k / slices;
+  float* part = scratch_alloc((int64_t)slices * g.n * g.m * 4);
+  if (!part) return false;
+  CUtensorMap maps[4];
+  // operand "A" of the transposed product is B: stored [k, n], read MN-major; its K slices are the batch
+  const bool a_blocked = g.n % 32 == 0;
+  bool ok = make_direct_map(&maps[0], g.b, g.n, ks, slices, false, BM, a_blocked);
+  if (ok) {
+    // operand "B" is A: stored [m, k], K-major; slice sl is the view A[:, sl*ks : (sl+1)*ks]
+    // (dimensions ordered by stride: k within the slice, slice, row)
+    cuuint64_t dims[3] = {(cuuint64_t)ks, (cuuint64_t)slices, (cuuint64_t)g.m};
+    cuuint64_t strides[2] = {(cuuint64_t)ks * 4, (cuuint64_t)g.k * 4};
+    cuuint32_t box[3] = {16, 1, (cuuint32_t)BN};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(&maps[1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(g.a), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (K-sliced operand %d x %d / %d)", (int)r,
+                g.m, g.k, slices);
+      ok = false;
+    }
+  }
+  if (ok) {
+    maps[2] = maps[0];
+    maps[3] = maps[1];
+    TcParams p;
+    p.a_blocked = a_blocked;
+    p.b_blocked = 0;
+    p.b_sliced = 1;
+    p.c_tma = 0;
+    p.b_box_rows = BN;
+    p.c = part;
+    p.bias = nullptr;
+    p.dact_y = nullptr;
+    p.dact = CLEAVE_ACT_IDENTITY;
+    p.m = g.n;                 // the transposed product is [n, m]
+    p.n = g.m;
+    p.num_kb = ceil_div(ks, 16);
+    p.chunk_kb = kChunkK / 16;
+    p.batch = slices;
+    p.mblks = ceil_div(g.n, BM);
+    p.nblks = ceil_div(g.m, BN);
+    p.act = CLEAVE_ACT_IDENTITY;
+    p.status = ctx().status_dev;
+    ok = run_tc_layout<kPathDirect>(true, false, maps, p);
+  }
+  if (ok) {
+    sum_transpose_kernel<<<dim3(ceil_div(g.m, 32), ceil_div(g.n, 32)), 256, 0, ctx().stream>>>(part, g.c, slices, g.n,
+                                                                                              g.m);
+    count_launch();
+    ok = cuda_ok(cudaGetLastError(), "sum-transpose launch");
+  }
+  scratch_free(part);
+  return ok;
 }
 
 // hi planes are the caller's tensors, lo planes come from one streaming pass per operand.
@@ -767,6 +880,7 @@ static bool launch_lo_plane(const GemmArgs& g) {
     p.a_blocked = a_mn;
     p.b_blocked = b_mn;
     p.c_tma = 0;
+    p.b_sliced = 0;
     p.b_box_rows = BN;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
     p.bias = g.bias;
@@ -815,6 +929,10 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
   // 3-5 % slower when its hi operand is the raw tensor (low mantissa bits that the tensor pipe ignores
   // still travel through shared memory; the kernel runs under the power cap).
   if (g_direct == 2 || (g_direct == 1 && prefer_direct(g))) {
+    if (g_direct == 1 && g_narrow) {
+      const int slices = narrow_slices(g);
+      if (slices > 0) return launch_narrow_transposed(g, slices);
+    }
     if (addressable(g)) return launch_direct(g);
   } else if (g_direct == 3 || (g_direct == 1 && (int64_t)g.m * g.n <= (1ll << 24))) {
     if (lo_plane_eligible(g)) return launch_lo_plane(g);
@@ -874,6 +992,7 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.act = g.act;
     p.a_blocked = p.b_blocked = 0;
     p.c_tma = 0;
+    p.b_sliced = 0;
     p.b_box_rows = BN;
     p.status = ctx().status_dev;
     if (pair) {

@@ -247,3 +247,15 @@ def test_pair_kernel_route_sampled_rows(trans_a, trans_b):
     rhs = got.astype(np.float64).sum(axis=0)
     scale = np.abs(a).astype(np.float64).sum(axis=0) @ np.abs(b).astype(np.float64)
     assert np.max(np.abs(lhs - rhs) / scale) <= TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 64, 4096), (2048, 40, 2048), (8192, 8, 2048), (2304, 64, 6144), (4096, 128, 4096),
+                                   (2048, 100, 2560)])
+def test_narrow_output_takes_the_transposed_split_k_route(m, n, k):
+    # n <= 128 with long m and k: C^T = B^T A^T with K cut into slices, then one sum-and-transpose pass.
+    a, b = workloads.gemm_inputs(m, n, k)
+    L = cb.lib()
+    before = L.cleave_cuda_kernel_launches()
+    got = gemm(a, b, GEMM_3XTF32)
+    assert L.cleave_cuda_kernel_launches() - before == 2          # the GEMM kernel and the sum-transpose pass
+    assert_gemm_close(got, a, b, what=("narrow", m, n, k))
