@@ -32,6 +32,7 @@ SIGNATURES = {
     "cleave_cuda_trim": (None, []),
     "cleave_cuda_live_bytes": (i64, []),
     "cleave_cuda_kernel_launches": (i64, []),
+    "cleave_cuda_test_hook": (i64, [i32, i64]),
     "cleave_cuda_profile_begin": (None, []),
     "cleave_cuda_profile_end": (ctypes.c_double, [ctypes.POINTER(i32)]),
     "cleave_cuda_host_alloc": (ctypes.c_void_p, [i64]),
@@ -79,6 +80,9 @@ SIGNATURES = {
     "cleave_cuda_mse_act_bwd_f32": (f32, [c_buf, c_buf, c_buf, i32]),
     "cleave_cuda_mse_act_bwd_dev_f32": (i32, [c_buf, c_buf, c_buf, i32, c_buf]),
     "cleave_cuda_sgd_f32": (i32, [c_buf, c_buf, f32, f32]),
+    "cleave_cuda_host_gemm_f32": (i64, [c_f32p, i64, c_f32p, i64, c_f32p, i64, i32, i32, i32]),
+    "cleave_cuda_host_binary_f32": (i64, [i32, c_f32p, i64, c_f32p, i64, c_f32p, i64]),
+    "cleave_cuda_host_unary_f32": (i64, [i32, c_f32p, i64, c_f32p, i64]),
     "cleave_cuda_alloc_f64": (c_buf, [i64]),
     "cleave_cuda_upload_f64": (c_buf, [c_f64p, i64]),
     "cleave_cuda_download_f64": (i64, [c_buf, c_f64p, i64]),

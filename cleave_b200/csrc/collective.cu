@@ -19,19 +19,30 @@
 // rank's writes have landed") taken by the last CTA to finish.  Every wait is bounded; a wait
 // that gives up records a status code for the host and lets the kernel return.
 //
+// An entry barrier that gives up ABORTS the launch: CTA 0 tells every peer (an abort word in each
+// rank's signal block) and its own CTAs (a local abort word published before the release), and no
+// CTA then reads a gradient, writes a weight or waits at the exit barrier.  A rank that passes its own
+// entry wait but finds a peer's abort mark for this epoch aborts as well.  So when a rank never
+// arrives, every live rank returns with its weights exactly as they were; the host sees
+// CLEAVE_CUDA_ERR_DEVICE_TIMEOUT at its next synchronisation.
+//
 // Ranks must be one process per GPU: kernels that wait on each other never share a GPU.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cleave {
 
 constexpr int kMaxRanks = 8;
 constexpr int kDpThreads = 256;
-constexpr unsigned long long kDpWaitLimitNs = 2000000000ull;   // 2 s
+constexpr unsigned long long kDpWaitLimitNs = 2000000000ull;   // 2 s across GPUs unless CLEAVE_CUDA_DP_WAIT_MS is set
 
 // Signal-word layout inside each rank's flag buffer (uint32 words).
 constexpr int kFlagFromRank = 0;    // [0, 8): last epoch signalled by rank s
+constexpr int kFlagAbortFrom = 8;   // [8, 16): epoch of the last launch that rank s abandoned at its entry barrier
 constexpr int kFlagGo = 16;         // CTA 0 -> other CTAs of the same launch
 constexpr int kFlagDone = 17;       // CTAs finished in this launch
+constexpr int kFlagAbort = 18;      // CTA 0 -> other CTAs: epoch of the last launch abandoned on this rank
 
 struct DpArgs {
   float* params[kMaxRanks];         // every rank's parameter buffer (peer pointers)
@@ -43,6 +54,7 @@ struct DpArgs {
   int64_t word_lo, word_hi;         // this rank's slice, in 16-byte words
   float lr, gscale;
   uint32_t epoch;                   // entry barrier uses epoch, exit barrier epoch + 1
+  unsigned long long wait_ns;       // limit of a cross-GPU wait; the CTAs' wait for CTA 0 gets twice that and a second
   DeviceStatus* status;
 };
 
@@ -70,13 +82,13 @@ __device__ __forceinline__ unsigned long long dp_timer_ns() {
 
 // Spin until *p has reached `want` (epochs only grow; the signed difference tolerates wrap-around).
 template <bool kSys>
-__device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t want) {
+__device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t want, unsigned long long limit_ns) {
   const unsigned long long t0 = dp_timer_ns();
   uint32_t spins = 0;
   for (;;) {
     const uint32_t v = kSys ? ld_acquire_sys(p) : ld_acquire_gpu(p);
     if ((int32_t)(v - want) >= 0) return true;
-    if ((++spins & 0x3Fu) == 0 && dp_timer_ns() - t0 > kDpWaitLimitNs) return false;
+    if ((++spins & 0x3Fu) == 0 && dp_timer_ns() - t0 > limit_ns) return false;
   }
 }
 
@@ -125,25 +137,55 @@ __global__ void __launch_bounds__(kDpThreads) dp_sgd_allreduce_kernel(DpArgs a) 
   uint32_t* mine = a.flags[a.rank];
 
   // ---- entry barrier: every rank's gradients are final ------------------------------------
+  __shared__ int s_abort;
   if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
     if (threadIdx.x < a.world) {
       __threadfence_system();
       st_release_sys(a.flags[threadIdx.x] + kFlagFromRank + a.rank, a.epoch);
-      if (!wait_epoch<true>(mine + kFlagFromRank + threadIdx.x, a.epoch))
+      if (!wait_epoch<true>(mine + kFlagFromRank + threadIdx.x, a.epoch, a.wait_ns)) {
         dp_report(a.status, 10, 1000 + threadIdx.x, (int)a.epoch);
+        s_abort = 1;
+      }
     }
     __syncthreads();
-    if (threadIdx.x == 0) st_release_gpu(mine + kFlagGo, a.epoch);   // released even after a timeout: no CTA may hang
+    const int entry_failed = s_abort;   // read by all threads before anyone may set it again below
+    __syncthreads();
+    if (entry_failed) {
+      // tell every peer that this rank abandons the launch (a late rank must not update alone) ...
+      if (threadIdx.x < a.world) st_release_sys(a.flags[threadIdx.x] + kFlagAbortFrom + a.rank, a.epoch);
+    } else if (threadIdx.x < a.world && ld_acquire_sys(mine + kFlagAbortFrom + threadIdx.x) == a.epoch) {
+      // ... and a rank whose own wait succeeded still stands down when a peer has given up on this epoch
+      dp_report(a.status, 13, 1300 + threadIdx.x, (int)a.epoch);
+      s_abort = 1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (s_abort) st_release_gpu(mine + kFlagAbort, a.epoch);
+      st_release_gpu(mine + kFlagGo, a.epoch);   // always released, so that no CTA of this launch is left waiting
+    }
   } else {
-    if (threadIdx.x == 0 && !wait_epoch<false>(mine + kFlagGo, a.epoch)) dp_report(a.status, 11, 1100, (int)a.epoch);
+    if (threadIdx.x == 0) {
+      s_abort = 0;
+      if (!wait_epoch<false>(mine + kFlagGo, a.epoch, 2 * a.wait_ns + 1000000000ull)) {
+        dp_report(a.status, 11, 1100, (int)a.epoch);
+        s_abort = 1;
+      } else if (ld_acquire_gpu(mine + kFlagAbort) == a.epoch) {
+        s_abort = 1;
+      }
+    }
     __syncthreads();
   }
+  const bool aborted = s_abort != 0;   // uniform over the CTA
   __threadfence_system();
 
   // ---- this rank's slice: reduce, update, replicate ------------------------------------------
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const float* w_local = a.params[a.rank];
-  if (a.grads_mc != nullptr && a.params_mc != nullptr) {
+  if (aborted) {
+    // nothing is read from or written to any rank
+  } else if (a.grads_mc != nullptr && a.params_mc != nullptr) {
     // Four reduced loads in flight per thread: the round trip through the switch is long and the
     // grid is deliberately small.
     constexpr int kU = 4;
@@ -202,11 +244,13 @@ __global__ void __launch_bounds__(kDpThreads) dp_sgd_allreduce_kernel(DpArgs a) 
   }
   __syncthreads();
   if (s_last) {
-    if (threadIdx.x == 0) mine[kFlagDone] = 0;   // ready for the next launch
+    if (threadIdx.x == 0) mine[kFlagDone] = 0;   // ready for the next launch, also after an abandoned one
+    // The exit epoch is signalled even by an abandoned launch (a peer that did run must not wait out its limit
+    // for this rank); an abandoned launch has written nothing and waits for nobody.
     if (threadIdx.x < a.world) {
       __threadfence_system();
       st_release_sys(a.flags[threadIdx.x] + kFlagFromRank + a.rank, a.epoch + 1u);
-      if (!wait_epoch<true>(mine + kFlagFromRank + threadIdx.x, a.epoch + 1u))
+      if (!aborted && !wait_epoch<true>(mine + kFlagFromRank + threadIdx.x, a.epoch + 1u, a.wait_ns))
         dp_report(a.status, 12, 1200 + threadIdx.x, (int)a.epoch);
     }
   }
@@ -247,6 +291,14 @@ extern "C" int32_t cleave_cuda_dp_sgd_allreduce_f32(void* const* params_peers, v
   a.lr = lr;
   a.gscale = 1.0f / (float)world;
   a.epoch = epoch;
+  // Cross-GPU wait limit: 2 s, or CLEAVE_CUDA_DP_WAIT_MS (1 .. 60000) read once.  Host-side skew between the
+  // ranks' launches (module loading, a data loader, a garbage collection) counts against it.
+  static const unsigned long long wait_ns = [] {
+    const char* e = getenv("CLEAVE_CUDA_DP_WAIT_MS");
+    const long ms = e ? atol(e) : 0;
+    return (ms >= 1 && ms <= 60000) ? (unsigned long long)ms * 1000000ull : kDpWaitLimitNs;
+  }();
+  a.wait_ns = wait_ns;
   a.status = ctx().status_dev;
   // A light grid: the kernel is bound by NVLink, not by SMs, and all of its CTAs must be able to
   // become resident next to whatever else is running (CTAs other than 0 wait for CTA 0).
@@ -254,6 +306,7 @@ extern "C" int32_t cleave_cuda_dp_sgd_allreduce_f32(void* const* params_peers, v
   if (grid > ctx().sm_count) grid = ctx().sm_count;
   if (grid < 1) grid = 1;
   cudaStream_t s = cuda_stream ? (cudaStream_t)cuda_stream : ctx().stream;
+  Trace tr("dp_sgd_allreduce", "offset=%lld len=%lld rank=%d world=%d", (long long)offset, (long long)len, rank, world);
   dp_sgd_allreduce_kernel<<<grid, kDpThreads, 0, s>>>(a);
   count_launch();
   if (!cuda_ok(cudaGetLastError(), "dp_sgd_allreduce launch")) return -cleave_cuda_last_error();

@@ -75,6 +75,7 @@ void release_buf(Buf* b);
 float* scratch_alloc(int64_t bytes);   // pooled scratch (stream-ordered reuse); pair with scratch_free
 void scratch_free(float* p);
 void count_launch(int n = 1);
+bool noalloc_poke_completion_word(unsigned long long value);   // test hook: overwrite sum_noalloc's completion word
 
 // Reads one f32 produced on the device at `dev_scalar`: copies to pinned memory, syncs,
 // checks the status word.  Returns NaN on failure.
@@ -92,6 +93,19 @@ float wait_scalar();
 void profile_begin();
 double profile_end(int* pairs);
 void profile_mark(bool begin);
+
+// ---- optional call trace --------------------------------------------------------------------------
+// With CLEAVE_CUDA_TRACE=1 in the environment every traced entry point prints one line to stderr when it
+// returns: operation, shape, and the device time of what it queued (a CUDA event pair on the library's
+// stream; the call then waits for its own work, so a traced run is serialised).  Nested scopes (an entry
+// point implemented through another) print only the outermost.  Without the variable a Trace costs one
+// load and a branch.
+struct Trace {
+  bool on;
+  char text[120];
+  Trace(const char* op, const char* fmt, ...);
+  ~Trace();
+};
 
 // ---- launch geometry -------------------------------------------------------------------
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }

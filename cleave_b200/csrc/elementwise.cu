@@ -198,6 +198,7 @@ static cleave_buf unary_api(cleave_buf x, const char* name, Op op) {
   ApiLock lock;
   Buf* a = as_buf(x, name);
   if (!a) return nullptr;
+  Trace tr(name, "n=%lld", (long long)a->len);
   Buf* o = new_buf(a->len);
   if (!o) return nullptr;
   if (!launch_unary(a->ptr, o->ptr, a->len, op)) { release_buf(o); return nullptr; }
@@ -215,6 +216,7 @@ static cleave_buf binary_api(cleave_buf x, cleave_buf y, const char* name, Op op
               name, (long long)a->len, (long long)b->len);
     return nullptr;
   }
+  Trace tr(name, "n=%lld", (long long)a->len);
   Buf* o = new_buf(a->len);
   if (!o) return nullptr;
   if (!launch_binary(a->ptr, b->ptr, o->ptr, a->len, op)) { release_buf(o); return nullptr; }
@@ -271,6 +273,7 @@ cleave_buf cleave_cuda_fill_f32(float value, int64_t len) {
   ApiLock lock;
   Buf* o = new_buf(len);
   if (!o) return nullptr;
+  Trace tr("fill", "n=%lld", (long long)len);
   if (!launch_fill(o->ptr, len, value)) { release_buf(o); return nullptr; }
   return (cleave_buf)o;
 }
@@ -287,6 +290,7 @@ cleave_buf cleave_cuda_bias_act_f32(cleave_buf x, cleave_buf bias, int32_t rows,
               (long long)a->len, (long long)b->len, rows, cols);
     return nullptr;
   }
+  Trace tr("bias_act", "rows=%d cols=%d act=%d", rows, cols, act);
   Buf* o = new_buf(a->len);
   if (!o) return nullptr;
   if (!launch_bias_act(a->ptr, b->ptr, o->ptr, rows, cols, act)) { release_buf(o); return nullptr; }
@@ -301,6 +305,7 @@ int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale) 
   if (a->len != b->len)
     return -set_error(CLEAVE_CUDA_ERR_SHAPE, "sgd: weights have %lld elements, gradient %lld", (long long)a->len,
                       (long long)b->len);
+  Trace tr("sgd", "n=%lld", (long long)a->len);
   if (!launch_binary(a->ptr, b->ptr, a->ptr, a->len, SgdOp{lr, gscale})) return -cleave_cuda_last_error();
   return CLEAVE_CUDA_OK;
 }

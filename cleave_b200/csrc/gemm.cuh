@@ -37,5 +37,6 @@ __device__ __forceinline__ float dact_apply(float y, float g, int dact) {
 bool launch_gemm_exact(const GemmArgs& g);
 bool launch_gemm_3xtf32(const GemmArgs& g);   // false + error if the problem cannot use this path
 bool gemm_3xtf32_supported(const GemmArgs& g);
+int gemm_batch_chunk(int64_t bytes_per_entry, int batch);   // batch entries per pass (workspace and grid limits)
 
 }  // namespace cleave

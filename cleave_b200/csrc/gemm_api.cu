@@ -46,6 +46,8 @@ static int gemm_into(Buf* C, Buf* A, Buf* B, int batch, int m, int n, int k, int
     if (dact_y->ptr == C->ptr)
       return set_error(CLEAVE_CUDA_ERR_ARG, "gemm_dact: the output must not alias y");
   }
+  Trace tr(dact_y ? "gemm_dact" : "gemm", "batch=%d m=%d n=%d k=%d ta=%d tb=%d algo=%d act=%d", batch, m, n, k, ta ? 1 : 0,
+           tb ? 1 : 0, algo, dact_y ? dact : act);
   GemmArgs g{A->ptr, B->ptr, C->ptr, batch, m, n, k, ta ? 1 : 0, tb ? 1 : 0, bias ? bias->ptr : nullptr, act,
              dact_y ? dact_y->ptr : nullptr, dact};
   return run_gemm(g, algo) ? CLEAVE_CUDA_OK : cleave_cuda_last_error();

@@ -92,10 +92,34 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(const float* __restrict
 }
 
 bool launch_gemm_exact(const GemmArgs& g) {
-  dim3 grid(ceil_div(g.n, kTN), ceil_div(g.m, kTM), g.batch);
-  gemm_exact_kernel<<<grid, 256, 0, ctx().stream>>>(g.a, g.b, g.c, g.m, g.n, g.k, g.trans_a, g.trans_b, g.bias, g.act,
-                                                    g.dact_y, g.dact);
-  count_launch();
+  // gridDim.y and .z hold at most 65535: a tall problem is cut into row bands (whole 64-row tiles, so every
+  // element is computed exactly as in one launch) and a long batch into runs of entries.
+  constexpr int kMaxGridYZ = 65535;
+  const int band_rows = kMaxGridYZ * kTM;
+  for (int b0 = 0; b0 < g.batch; b0 += kMaxGridYZ) {
+    const int nb = (g.batch - b0) < kMaxGridYZ ? (g.batch - b0) : kMaxGridYZ;
+    if (g.m > band_rows && nb > 1) {
+      set_error(CLEAVE_CUDA_ERR_UNSUPPORTED, "exact GEMM: %d rows with a batch of %d is out of range", g.m, g.batch);
+      return false;
+    }
+    for (int r0 = 0; r0 < g.m; r0 += band_rows) {
+      const int rows = (g.m - r0) < band_rows ? (g.m - r0) : band_rows;
+      // A band of a transposed A ([k, m], rows contiguous) is a column range: same leading dimension, so the
+      // kernel would need a stride argument; such a shape (m > 4 Mi rows, trans_a) is refused instead.
+      if (r0 > 0 && g.trans_a) {
+        set_error(CLEAVE_CUDA_ERR_UNSUPPORTED, "exact GEMM: a transposed A with more than %d rows is out of range",
+                  band_rows);
+        return false;
+      }
+      const int64_t a_off = (int64_t)b0 * g.m * g.k + (int64_t)r0 * g.k;
+      const int64_t c_off = (int64_t)b0 * g.m * g.n + (int64_t)r0 * g.n;
+      dim3 grid(ceil_div(g.n, kTN), ceil_div(rows, kTM), nb);
+      gemm_exact_kernel<<<grid, 256, 0, ctx().stream>>>(g.a + a_off, g.b + (int64_t)b0 * g.k * g.n, g.c + c_off, rows,
+                                                        g.n, g.k, g.trans_a, g.trans_b, g.bias, g.act,
+                                                        g.dact_y ? g.dact_y + c_off : nullptr, g.dact);
+      count_launch();
+    }
+  }
   return cuda_ok(cudaGetLastError(), "exact GEMM launch");
 }
 

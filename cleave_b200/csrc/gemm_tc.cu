@@ -566,6 +566,21 @@ static bool make_operand_map(CUtensorMap* map, float* planes, int rows_p, int Kp
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+// Batch entries processed per pass: as many as fit the operand workspace (4 GiB unless
+// CLEAVE_CUDA_GEMM_WORKSPACE_MB says otherwise; read at every call so a test can lower it), at least one,
+// and never more than a grid's z dimension can index (the pre-pass kernels put the batch there).
+constexpr int kMaxGridZ = 65535;
+int gemm_batch_chunk(int64_t bytes_per_entry, int batch) {
+  int64_t limit = 4ll << 30;
+  const char* e = getenv("CLEAVE_CUDA_GEMM_WORKSPACE_MB");
+  if (e && atoll(e) > 0) limit = atoll(e) << 20;
+  int64_t chunk = limit / (bytes_per_entry > 0 ? bytes_per_entry : 1);
+  if (chunk < 1) chunk = 1;
+  if (chunk > batch) chunk = batch;
+  if (chunk > kMaxGridZ) chunk = kMaxGridZ;
+  return (int)chunk;
+}
+
 // Switches for measurements (read once).  CLEAVE_CUDA_GEMM_DIRECT forces one operand path for every
 // problem it can serve: 0 = padded [hi | lo] planes, 2 = split in the kernel, 3 = lo planes; otherwise
 // the choice in launch_gemm_3xtf32.  CLEAVE_CUDA_GEMM_MN=0 makes the planes pre-pass transpose instead
@@ -849,9 +864,7 @@ static bool launch_narrow_transposed(const GemmArgs& g, int slices) {
 static bool launch_lo_plane(const GemmArgs& g) {
   const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
   const int64_t a_elems = (int64_t)g.m * g.k, b_elems = (int64_t)g.n * g.k;
-  int chunk = (int)((4ll << 30) / ((a_elems + b_elems) * 4));
-  if (chunk < 1) chunk = 1;
-  if (chunk > g.batch) chunk = g.batch;
+  const int chunk = gemm_batch_chunk((a_elems + b_elems) * 4, g.batch);
   float* wa = scratch_alloc(chunk * a_elems * 4);
   if (!wa) return false;
   float* wb = scratch_alloc(chunk * b_elems * 4);
@@ -951,9 +964,7 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
   const int Np = round_up(g.n, BN);
   // Bound the split workspace: process the batch in chunks of at most ~4 GiB of planes.
   const int64_t per_batch_bytes = 2ll * ((int64_t)Mp + Np) * Kp * 4;
-  int chunk = (int)((4ll << 30) / per_batch_bytes);
-  if (chunk < 1) chunk = 1;
-  if (chunk > g.batch) chunk = g.batch;
+  const int chunk = gemm_batch_chunk(per_batch_bytes, g.batch);
 
   float* wa = scratch_alloc((int64_t)chunk * 2 * Mp * Kp * 4);
   if (!wa) return false;

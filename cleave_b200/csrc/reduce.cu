@@ -59,18 +59,36 @@ struct Finish {
   int mode;
   const float* first;
   unsigned int* done;   // completion counter of this launch family: zero between launches
+  // Ticketed completion word (used instead of `done` when non-null): high half = ticket of the launch that
+  // is counting, low half = CTAs arrived.  A launch whose ticket differs from the stored one restarts the
+  // count, so a word left non-zero by a launch that never finished cannot stall later launches.
+  unsigned long long* ticket_word = nullptr;
+  unsigned int ticket = 0;
 };
 
 // Publishes partials[blockIdx.x] = value (thread 0's) and tells, in every thread, whether this CTA
 // is the last of the grid to do so.  The last CTA re-arms the counter for the next launch.
-__device__ __forceinline__ bool publish_and_check_last(float* partials, float value, unsigned int* done) {
+__device__ __forceinline__ bool publish_and_check_last(float* partials, float value, const Finish& f) {
   __shared__ int s_last;
   if (threadIdx.x == 0) {
     partials[blockIdx.x] = value;
     __threadfence();
-    const unsigned int prev = atomicAdd(done, 1u);
-    s_last = (prev == gridDim.x - 1) ? 1 : 0;
-    if (s_last) *done = 0;
+    if (f.ticket_word != nullptr) {
+      unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(f.ticket_word);
+      unsigned int count;
+      for (;;) {   // ends after at most gridDim.x rounds: every failed exchange means another CTA arrived
+        count = ((unsigned int)(seen >> 32) == f.ticket) ? (unsigned int)seen + 1u : 1u;
+        const unsigned long long want = ((unsigned long long)f.ticket << 32) | count;
+        const unsigned long long prev = atomicCAS(f.ticket_word, seen, want);
+        if (prev == seen) break;
+        seen = prev;
+      }
+      s_last = (count == gridDim.x) ? 1 : 0;
+    } else {
+      const unsigned int prev = atomicAdd(f.done, 1u);
+      s_last = (prev == gridDim.x - 1) ? 1 : 0;
+      if (s_last) *f.done = 0;
+    }
   }
   __syncthreads();
   if (s_last) __threadfence();
@@ -118,7 +136,7 @@ __global__ void __launch_bounds__(kRThreads) reduce_kernel(const float* __restri
   }
   float t = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
   t = block_reduce<R>(t);
-  if (publish_and_check_last(partials, t, fin.done)) finish_reduction<R>(partials, gridDim.x, fin);
+  if (publish_and_check_last(partials, t, fin)) finish_reduction<R>(partials, gridDim.x, fin);
 }
 
 // Completion counters of the pooled entry points (one reduction runs at a time: single stream).
@@ -274,7 +292,7 @@ __global__ void __launch_bounds__(kRThreads) mse_stage1(const float* __restrict_
     }
   }
   acc = block_reduce<SumRed>(acc);
-  if (publish_and_check_last(partials, acc, fin.done)) finish_reduction<SumRed>(partials, gridDim.x, fin);
+  if (publish_and_check_last(partials, acc, fin)) finish_reduction<SumRed>(partials, gridDim.x, fin);
 }
 
 // ---- linear-regression step: one sweep over X[rows, feat] ------------------------------------
@@ -552,6 +570,7 @@ static float reduce_scalar(const float* v, int64_t n, int64_t first, float divis
   // Elements [first, n) are reduced; for max_of (mode 1) the result is combined with v[0].
   const float* base = v + first;
   int64_t cnt = n - first;
+  Trace tr(mode == 1 ? "max_of" : (divisor == 1.0f ? "sum" : "mean"), "n=%lld", (long long)cnt);
   float* partials = scratch_alloc((kMaxPartials + 4) * sizeof(float));
   if (!partials) return NAN;
   float* out = scalar_slot();
@@ -602,6 +621,7 @@ float cleave_cuda_max_f32(cleave_buf v) {
 }
 
 static bool colsum_launch(const float* x, float* out, int rows, int cols) {
+  Trace tr("colsum", "rows=%d cols=%d", rows, cols);
   const int strips = ceil_div(cols, kCsTx * 4);
   // Row splits: enough CTAs to fill the machine, at least 64 rows each; a function of the shape only.
   int splits = ceil_div((int64_t)ctx().sm_count * 4, strips);
@@ -685,6 +705,7 @@ static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, co
     return NAN;
   }
   const int64_t n = a->len;
+  Trace tr(name, "n=%lld act=%d", (long long)n, bwd_act);
   float* partials = scratch_alloc((kMaxPartials + 4) * sizeof(float));
   if (!partials) return NAN;
   int64_t slab;
@@ -749,6 +770,7 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
     set_error(CLEAVE_CUDA_ERR_SHAPE, "linreg_step: operand lengths do not match rows=%d feat=%d", rows, feat);
     return NAN;
   }
+  Trace tr("linreg_step", "rows=%d feat=%d", rows, feat);
   // Row slabs: one resident wave of CTAs, at least 1024 rows each, a multiple of 256 rows (8 warps x 32).
   const bool fast = (feat == 4 || feat == 8 || feat == 16 || feat == 32) && aligned16(X->ptr);
   const size_t dyn = fast ? linreg_smem_bytes(feat) : 0;
@@ -810,11 +832,14 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
 // are already at their memory budget.  cleave_cuda_sum_f32 takes its partial-sum buffer from the
 // library's pool, which may call cudaMalloc; the variant below keeps that buffer in a fixed
 // device-resident array instead and touches neither the pool, the handle table nor the library
-// context.  The cost is that every GPU that loads the library carries the array until exit.
+// context's memory (it reads the SM count and bumps the launch counter, nothing else).  The cost is that every
+// GPU that loads the library carries the array until exit.
 // ------------------------------------------------------------------------------------------------
 namespace cleave {
 
-constexpr int kNoAllocScratchFloats = kMaxPartials + 4;     // 1188 floats, 4752 bytes: partials, then the counter
+constexpr int kNoAllocScratchFloats = kMaxPartials + 4;     // 1188 floats, 4752 bytes: partials, then the 8-byte
+                                                            // completion word (byte offset 4736)
+static_assert((kMaxPartials * sizeof(float)) % 8 == 0, "the completion word must be 8-byte aligned");
 constexpr int64_t kNoAllocMaxLen = 2147483647ll;             // largest tensor an i32 shape can describe
 constexpr int kNoAllocMaxDevices = 64;
 
@@ -840,6 +865,13 @@ static float* noalloc_scratch_for_current_device() {
   return g_noalloc_ptr[dev];
 }
 
+bool noalloc_poke_completion_word(unsigned long long value) {
+  float* scratch = noalloc_scratch_for_current_device();
+  if (!scratch) return false;
+  return cuda_ok(cudaMemcpy(scratch + kMaxPartials, &value, sizeof(value), cudaMemcpyHostToDevice),
+                 "cudaMemcpy(completion word)");
+}
+
 }  // namespace cleave
 
 extern "C" int32_t cleave_cuda_sum_noalloc_f32(const float* x_dev, int64_t len, float* out_dev, void* cuda_stream) {
@@ -860,16 +892,22 @@ extern "C" int32_t cleave_cuda_sum_noalloc_f32(const float* x_dev, int64_t len, 
   // Same slab rule and the same kernel as cleave_cuda_sum_f32, so the summation tree and
   // therefore the result are identical.  The CTAs write partials [0, ctas) and the last one to
   // finish reads exactly those, so no value left in the array by an earlier call is ever read.
-  // The one word that must start at zero is the completion counter behind the partials: the
-  // array is zero when the library is loaded and the last CTA of every call sets it back to zero.
+  // Nothing in the array has to start at zero: the completion word behind the partials carries the
+  // ticket of the call that is counting in it (tickets start at 1 and grow with every call of this
+  // process), and a call that finds another ticket there restarts the count.  So a word left behind by
+  // a call whose kernel never finished -- or by two calls that overlapped, which is a caller error --
+  // cannot make a later, correctly ordered call skip its final step.
   int64_t slab;
   int ctas;
   // The occupancy query reads kernel attributes only; it allocates nothing.
   static const int max_ctas = resident_ctas(reduce_kernel<SumRed>);
   slab_for(len, max_ctas, &slab, &ctas);
-  unsigned int* done = reinterpret_cast<unsigned int*>(scratch + kMaxPartials);
-  reduce_kernel<SumRed><<<ctas, kRThreads, 0, s>>>(x_dev, len, slab, scratch, aligned16(x_dev) ? 1 : 0,
-                                                   Finish{out_dev, 1.0f, 0, nullptr, done});
+  static unsigned int next_ticket = 0;   // guarded by the API lock
+  if (++next_ticket == 0) ++next_ticket;
+  Finish fin{out_dev, 1.0f, 0, nullptr, nullptr};
+  fin.ticket_word = reinterpret_cast<unsigned long long*>(scratch + kMaxPartials);
+  fin.ticket = next_ticket;
+  reduce_kernel<SumRed><<<ctas, kRThreads, 0, s>>>(x_dev, len, slab, scratch, aligned16(x_dev) ? 1 : 0, fin);
   count_launch();
   if (!cuda_ok(cudaGetLastError(), "sum_noalloc launch")) return -cleave_cuda_last_error();
   return CLEAVE_CUDA_OK;

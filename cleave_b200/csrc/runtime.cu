@@ -121,6 +121,79 @@ int check_device_status() {
 
 void count_launch(int n) { g_launches += n; }
 
+// ---- call trace (CLEAVE_CUDA_TRACE=1) -------------------------------------------------------------------
+static int g_trace_mode = -1;     // -1: environment not read yet
+static int g_trace_depth = 0;
+static cudaEvent_t g_trace_ev[2] = {nullptr, nullptr};
+
+Trace::Trace(const char* op, const char* fmt, ...) : on(false) {
+  if (g_trace_mode < 0) {
+    const char* e = getenv("CLEAVE_CUDA_TRACE");
+    g_trace_mode = (e && e[0] == '1') ? 1 : 0;
+  }
+  if (!g_trace_mode || !g_ctx.ready) return;
+  if (g_trace_depth++ > 0) return;
+  if (!g_trace_ev[0] && (cudaEventCreate(&g_trace_ev[0]) != cudaSuccess || cudaEventCreate(&g_trace_ev[1]) != cudaSuccess)) {
+    cudaGetLastError();
+    g_trace_ev[0] = nullptr;
+    return;
+  }
+  int n = snprintf(text, sizeof(text), "%-16s ", op);
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(text + n, sizeof(text) - (size_t)n, fmt, ap);
+  va_end(ap);
+  on = cudaEventRecord(g_trace_ev[0], g_ctx.stream) == cudaSuccess;
+}
+
+Trace::~Trace() {
+  if (!g_trace_mode || !g_ctx.ready) return;
+  if (--g_trace_depth > 0 || !on) return;
+  float ms = 0.f;
+  if (cudaEventRecord(g_trace_ev[1], g_ctx.stream) == cudaSuccess && cudaEventSynchronize(g_trace_ev[1]) == cudaSuccess &&
+      cudaEventElapsedTime(&ms, g_trace_ev[0], g_trace_ev[1]) == cudaSuccess)
+    fprintf(stderr, "cleave_cuda trace: %s  %.1f us\n", text, ms * 1e3);
+  else
+    cudaGetLastError();
+}
+
+// ---- guard words behind every pool block (CLEAVE_CUDA_DEBUG=1) ----------------------------------------------
+// In debug mode each block handed out by the pool is followed by kGuardBytes of a fixed pattern, written when the
+// block is handed out and compared when it comes back: a kernel that wrote past the end of a tensor or of a
+// scratch buffer is reported (error code CLEAVE_CUDA_ERR_CUDA, message naming the block) at the free that
+// follows it.  The check waits for the stream, so a debug run is slow; nothing changes without the variable.
+constexpr int64_t kGuardBytes = 512;
+constexpr unsigned char kGuardByte = 0xA5;
+static int g_debug_mode = -1;
+static int64_t g_guard_failures = 0;
+static bool debug_mode() {
+  if (g_debug_mode < 0) {
+    const char* e = getenv("CLEAVE_CUDA_DEBUG");
+    g_debug_mode = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_debug_mode == 1;
+}
+static void guard_arm(void* block, int64_t bs) {
+  if (debug_mode()) cudaMemsetAsync((char*)block + bs, kGuardByte, (size_t)kGuardBytes, g_ctx.stream);
+}
+static void guard_check(void* block, int64_t bs) {
+  if (!debug_mode()) return;
+  unsigned char host[kGuardBytes];
+  if (cudaMemcpyAsync(host, (char*)block + bs, (size_t)kGuardBytes, cudaMemcpyDeviceToHost, g_ctx.stream) != cudaSuccess ||
+      cudaStreamSynchronize(g_ctx.stream) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  for (int64_t i = 0; i < kGuardBytes; ++i)
+    if (host[i] != kGuardByte) {
+      ++g_guard_failures;
+      set_error(CLEAVE_CUDA_ERR_CUDA, "debug: %lld-byte block at %p was overrun (guard byte %lld behind its end changed)",
+                (long long)bs, block, (long long)i);
+      fprintf(stderr, "libcleave_cuda: %s\n", t_err_msg);
+      return;
+    }
+}
+
 // ---- pool ----------------------------------------------------------------------------
 static int64_t block_size_for(int64_t bytes) {
   if (bytes < 512) bytes = 512;
@@ -141,10 +214,12 @@ static void* pool_alloc(int64_t bytes, int64_t* block_bytes) {
     void* p = it->second.back();
     it->second.pop_back();
     g_cached_bytes -= bs;
+    guard_arm(p, bs);
     return p;
   }
+  const size_t real = (size_t)bs + (debug_mode() ? (size_t)kGuardBytes : 0);
   void* p = nullptr;
-  cudaError_t e = cudaMalloc(&p, (size_t)bs);
+  cudaError_t e = cudaMalloc(&p, real);
   if (e != cudaSuccess) {
     // Give cached blocks back to the driver and retry once.
     cudaGetLastError();
@@ -154,19 +229,21 @@ static void* pool_alloc(int64_t bytes, int64_t* block_bytes) {
       kv.second.clear();
     }
     g_cached_bytes = 0;
-    e = cudaMalloc(&p, (size_t)bs);
+    e = cudaMalloc(&p, real);
   }
   if (e != cudaSuccess) {
     cudaGetLastError();
     set_error(CLEAVE_CUDA_ERR_OOM, "device allocation of %lld bytes failed: %s", (long long)bs, cudaGetErrorString(e));
     return nullptr;
   }
+  guard_arm(p, bs);
   return p;
 }
 
 // Blocks go straight back to the free list: all work of this library runs on one stream,
 // so a later user of the block is ordered after every kernel that touched it.
 static void pool_free(void* p, int64_t block_bytes) {
+  guard_check(p, block_bytes);
   g_free_blocks[block_bytes].push_back(p);
   g_cached_bytes += block_bytes;
 }
@@ -402,6 +479,26 @@ int64_t cleave_cuda_kernel_launches(void) {
   return g_launches;
 }
 
+int64_t cleave_cuda_test_hook(int32_t what, int64_t arg) {
+  ApiLock lock;
+  if (!ensure_init()) return -t_err_code;
+  switch (what) {
+    case CLEAVE_HOOK_SET_DEVICE_STATUS:
+      // what a kernel does when a bounded wait runs out, done from the host
+      g_ctx.status_host->where = 9000;
+      g_ctx.status_host->block = 0;
+      g_ctx.status_host->detail = 0;
+      g_ctx.status_host->code = (int)arg;
+      return 0;
+    case CLEAVE_HOOK_POISON_NOALLOC_WORD:
+      return noalloc_poke_completion_word((unsigned long long)arg) ? 0 : -t_err_code;
+    case CLEAVE_HOOK_GUARD_FAILURES:
+      return g_guard_failures;
+    default:
+      return -set_error(CLEAVE_CUDA_ERR_ARG, "test_hook: unknown selector %d", what);
+  }
+}
+
 void* cleave_cuda_host_alloc(int64_t bytes) {
   ApiLock lock;
   if (bytes <= 0) {
@@ -436,6 +533,7 @@ int32_t cleave_cuda_upload_into_f32(cleave_buf t, const float* host, int64_t len
   if (!b) return -t_err_code;
   if (!host || len != b->len) return -set_error(CLEAVE_CUDA_ERR_SHAPE, "upload_into: %lld elements given, tensor has %lld",
                                                 (long long)len, (long long)b->len);
+  Trace tr("upload_into", "n=%lld", (long long)len);
   if (!cuda_ok(cudaMemcpyAsync(b->ptr, host, (size_t)len * sizeof(float), cudaMemcpyHostToDevice, g_ctx.stream),
                "cudaMemcpyAsync(H2D)"))
     return -t_err_code;
@@ -450,6 +548,7 @@ cleave_buf cleave_cuda_upload_f32(const float* host, int64_t len) {
   }
   Buf* b = new_buf(len);
   if (!b) return nullptr;
+  Trace tr("upload", "n=%lld", (long long)len);
   if (!cuda_ok(cudaMemcpyAsync(b->ptr, host, (size_t)len * sizeof(float), cudaMemcpyHostToDevice, g_ctx.stream),
                "cudaMemcpyAsync(H2D)")) {
     release_buf(b);
@@ -472,6 +571,7 @@ int64_t cleave_cuda_download_f32(cleave_buf t, float* host, int64_t len) {
   if (!host || len != b->len)
     return -set_error(CLEAVE_CUDA_ERR_SHAPE, "download: room for %lld elements, tensor has %lld", (long long)len,
                       (long long)b->len);
+  Trace tr("download", "n=%lld", (long long)len);
   if (!cuda_ok(cudaMemcpyAsync(host, b->ptr, (size_t)len * sizeof(float), cudaMemcpyDeviceToHost, g_ctx.stream),
                "cudaMemcpyAsync(D2H)"))
     return -t_err_code;

@@ -83,6 +83,19 @@ int64_t cleave_cuda_kernel_launches(void);           /* kernels launched by this
  * milliseconds and, through `launches`, how many pairs there were. */
 void cleave_cuda_profile_begin(void);
 double cleave_cuda_profile_end(int32_t* launches);
+/* Diagnostics (environment, read once):
+ *   CLEAVE_CUDA_TRACE=1  every compute / transfer entry point prints "operation shape microseconds" to stderr
+ *                        (device time of what the call queued; the call waits for it, so the run is serialised)
+ *   CLEAVE_CUDA_DEBUG=1  every pool block is followed by guard bytes that are checked when the block is freed;
+ *                        an overrun is reported through the error channel and on stderr
+ * Test hook: lets a test put the library into states that otherwise need a misbehaving kernel.  It never
+ * launches anything.  Selectors: */
+enum {
+  CLEAVE_HOOK_SET_DEVICE_STATUS = 1,   /* arg = status code: as if a kernel's bounded wait had run out */
+  CLEAVE_HOOK_POISON_NOALLOC_WORD = 2, /* arg = 64-bit value stored into cleave_cuda_sum_noalloc_f32's completion word */
+  CLEAVE_HOOK_GUARD_FAILURES = 3       /* returns the number of guard-byte mismatches seen so far (debug mode) */
+};
+int64_t cleave_cuda_test_hook(int32_t what, int64_t arg);
 void* cleave_cuda_host_alloc(int64_t bytes);         /* pinned host memory for fast transfers */
 void cleave_cuda_host_free(void* p);
 
@@ -150,13 +163,18 @@ float cleave_cuda_max_f32(cleave_buf v);
  * where a cudaMalloc stall is not acceptable, processes already at their memory budget.
  * x_dev (len f32 values) and out_dev (one f32) are raw device pointers owned by the caller; the
  * kernel is queued on cuda_stream (NULL = the default stream) of the CURRENT device and the
- * call returns without waiting.  The partial sums and a completion counter live in a 4752-byte array that is part of the
- * library image on every GPU; len may be at most 2^31 - 1 (larger is rejected with
+ * call returns without waiting.  The partial sums and a completion word live in a 4752-byte array that is
+ * part of the library image on every GPU; len may be at most 2^31 - 1 (larger is rejected with
  * CLEAVE_CUDA_ERR_UNSUPPORTED).  The first call on each device looks up the array's device
  * address, so make that first call outside any stream capture.  All calls on one device share
- * the array: calls whose kernels may overlap on the GPU (different streams) race on it; calls
- * on one stream do not.  The value equals cleave_cuda_sum_f32 of the same data bit for bit.
- * It uses no handle, no pool and no library context, and never calls cudaMalloc or cudaFree. */
+ * the array: calls whose kernels may overlap on the GPU (different streams) race on it and their
+ * results are undefined; calls on one stream do not.  The completion word is keyed by a per-call ticket,
+ * so a call that was cut short (or an overlapped pair) leaves nothing behind that a later, properly
+ * ordered call could trip over.  The value equals cleave_cuda_sum_f32 of the same data bit for bit.
+ * It uses no handle and no pool, never calls cudaMalloc or cudaFree, and takes from the library context
+ * only the SM count.  x_dev must stay valid until the kernel has run: when it comes from
+ * cleave_cuda_data_ptr and the call is on a stream other than the library's, do not free the handle
+ * before that stream has been synchronised (the pool hands freed blocks to later library work at once). */
 int32_t cleave_cuda_sum_noalloc_f32(const float* x_dev, int64_t len, float* out_dev, void* cuda_stream);
 /* Sum applied to each column of a rows x cols matrix (bias gradients). */
 cleave_buf cleave_cuda_colsum_f32(cleave_buf x, int32_t rows, int32_t cols);
@@ -214,6 +232,25 @@ int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale);
 float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out,
                                   cleave_buf grad_out, int32_t rows, int32_t feat);
 
+/* ------------------------------------------------------------------ host-array forms (the lowering hook's targets)
+ * What a name-based exception in lower_raw_mlir_op (cleave/src/mlir_lower.rs:2004-2068; the two existing ones
+ * are at :2031-2039 and :2062-2064) calls for an operation on NATIVE tensors: `linalg.matmul`, and tensor-typed
+ * `arith.addf/subf/mulf/divf/negf` and `math.exp/tanh` (stdlib/linalg/matrix.cleave:59-60,
+ * stdlib/linalg/tensor.cleave:66-80, stdlib/nn/nn.cleave:82-95).  A native tensor is a host memref after
+ * bufferisation (mlir_lower.rs:223-226) and crosses the call as every array does, (pointer, i64 total length)
+ * (mlir_lower.rs:1096-1113, :1720-1751); static dims follow as i32.  Each call uploads its operands, runs the
+ * same kernels as the handle forms above, writes the result into the caller's `out` array and returns its
+ * length (or a negative error code) once the array is complete.  The matmul form pipelines products of 2^33
+ * multiply-adds and more over row blocks (upload, product and download of consecutive blocks overlap) when
+ * a and c are pinned host memory (cleave_cuda_host_alloc). */
+enum { CLEAVE_OP_ADD = 1, CLEAVE_OP_SUB = 2, CLEAVE_OP_MUL = 3, CLEAVE_OP_DIV = 4,              /* binary */
+       CLEAVE_OP_NEG = 5, CLEAVE_OP_EXP = 6, CLEAVE_OP_TANH = 7, CLEAVE_OP_RELU = 8, CLEAVE_OP_SIGMOID = 9 };
+int64_t cleave_cuda_host_gemm_f32(const float* a, int64_t a_len, const float* b, int64_t b_len, float* c, int64_t c_len,
+                                  int32_t m, int32_t n, int32_t k);
+int64_t cleave_cuda_host_binary_f32(int32_t op, const float* a, int64_t a_len, const float* b, int64_t b_len, float* out,
+                                    int64_t out_len);
+int64_t cleave_cuda_host_unary_f32(int32_t op, const float* a, int64_t a_len, float* out, int64_t out_len);
+
 /* ------------------------------------------------------------------ f64 instances
  * The reference's algebras are declared for every T: Float (Ring<f64> stdlib/num/num.cleave:189-196,
  * Activation<f64> stdlib/nn/nn.cleave:60-64, Tensor<T, Dims...> stdlib/linalg/tensor.cleave:40), so
@@ -257,8 +294,13 @@ cleave_buf cleave_cuda_gemm_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n
  * identical on every rank.  cuda_stream: the stream to launch on (NULL = the library's), so a
  * bucket can overlap the rest of the backward pass.  Every rank must make the same calls, one
  * process per GPU.  A bucket may only be exchanged once no rank reads its WEIGHTS any more in
- * this step.  A barrier that times out (2 s) is reported as CLEAVE_CUDA_ERR_DEVICE_TIMEOUT at
- * the next synchronisation. */
+ * this step.  A barrier that times out is reported as CLEAVE_CUDA_ERR_DEVICE_TIMEOUT at the next
+ * synchronisation; when it is the ENTRY barrier (a rank's gradients never arrived, limit 2 s, or
+ * CLEAVE_CUDA_DP_WAIT_MS milliseconds if that is set when the library initialises) the kernel
+ * touches neither weights nor gradients on any rank: every replica still holds the weights it had
+ * before the call.  Buffers passed here on a stream other than the library's must stay alive until
+ * that stream has been synchronised.  The pointer tables are host arrays: this entry point is meant
+ * for a host framework, it has no cleave-source binding (no cleave type lowers to a bare pointer table). */
 int32_t cleave_cuda_dp_sgd_allreduce_f32(void* const* params_peers, void* const* grads_peers,
                                          void* const* flags_peers, void* params_multicast, void* grads_multicast,
                                          int64_t offset, int64_t len, int32_t rank, int32_t world, float lr,

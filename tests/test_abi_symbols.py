@@ -73,8 +73,9 @@ def test_bad_handles_are_rejected_without_touching_them(built):
 
 def _cleave_externs():
     """(file, symbol, number of C-level arguments) for every ``extern(cleave_cuda_*) fn`` of the shipped
-    cleave-side files.  An array parameter ``[T; N]`` is two C arguments (pointer, length) and its
-    ``const N`` companion none of its own (cleave/src/mlir_lower.rs:1096-1113)."""
+    cleave-side files.  An array parameter ``[T; N]`` is two C arguments, pointer and length
+    (cleave/src/mlir_lower.rs:1096-1113); ``const`` is not valid inside a parameter list
+    (cleave/src/grammar.pest:116) and is refused here."""
     out = []
     base = os.path.join(ROOT, "cleave_b200", "cleave")
     for dirpath, _, files in os.walk(base):
@@ -86,8 +87,7 @@ def _cleave_externs():
             for sym, params in re.findall(r"extern\((cleave_cuda_\w+)\)\s*fn\s+\w+\s*\(([^)]*)\)", text):
                 n = 0
                 for prm in [x.strip() for x in params.split(",") if x.strip()]:
-                    if prm.startswith("const "):
-                        continue
+                    assert not prm.startswith("const "), f"{fn}: `{prm}`: const generics belong on the impl"
                     n += 2 if re.search(r":\s*\[", prm) else 1
                 out.append((fn, sym, n))
     return out
