@@ -14,9 +14,15 @@ Rank 0 prints ONE JSON line.
   roofline  the tcgen05 kernel alone (CUDA events around each launch on the launching stream)
             against the 3xTF32-effective tensor peak
   cpu_baseline  the CPU oracle (restatement of the reference's loop) on a bounded row slice of the
-            same problem, all host threads
-  secondary the other two single-GPU configurations: MLP forward+backward samples/s and the
-            linear-regression step in GB/s (not part of the headline)
+            same problem: all host threads, and one thread (the reference itself is single-threaded)
+  mlp_fwd_bwd   the second half of the metric, "MLP fwd+bwd samples/s vs host CPU" (configuration 2):
+            device-resident and end-to-end samples/s, its own roofline and its own CPU baseline; the same
+            record is repeated under roofline / cpu_baseline / e2e as `mlp_fwd_bwd`
+  sharded   the workloads that shard over GPUs, run by the same ranks after the headline: batched
+            64 x 4096^3 by batch index, 16384^3 by row blocks, data-parallel MLP training at global batch
+            32768 (fused exchange kernel and NCCL); at N = 1 the same workloads on one rank, so every
+            N > 1 line has its one-GPU time from the same series of runs
+  secondary the linear-regression step in GB/s (configuration 1)
 
 `--impl reference` times the reference's CPU arithmetic (the oracle; the reference itself is Rust +
 MLIR and cannot be built here) on the same workload, each step a bounded row slice.
@@ -42,9 +48,14 @@ if ROOT not in sys.path:
 
 M = N = K = 8192          # headline size; --size overrides it for profiling captures only
 FLOPS = 2.0 * M * N * K
-# DRAM traffic of one tcgen05 GEMM kernel launch at 8192^3, from a one-pass ncu capture of this
-# program at full size (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 7.599e9 + 277.6e6
+# DRAM traffic of one tcgen05 GEMM kernel launch at 8192^3: not measured by this program (it needs a
+# profiler) but taken from a one-pass ncu capture of it at full size (dram__bytes_read.sum +
+# dram__bytes_write.sum).  The record names the capture, so a value that no longer matches the kernel shows.
+NCU_TRAFFIC = {"bytes_per_launch": 7.599e9 + 277.6e6,
+               "kernel": "gemm_3xtf32_pair_kernel<0, 1, 32> (256x256 tiles on CTA pairs, K-block 32, 3 stages)",
+               "summary": "profiles/gemm_3xtf32_pair_kernel_8192x4096x4096_ncu_full.md"}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = NCU_TRAFFIC["bytes_per_launch"]
+NOMINAL_TF32_DENSE_TFLOPS = 1125.0   # datasheet, dense (half the 2:4-sparse figure), at the 1965 MHz boost clock
 
 
 def measured_peaks():
@@ -99,21 +110,28 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_gemm_sample(a: np.ndarray, b: np.ndarray, target_s: float = 12.0):
+def cpu_gemm_sample(a: np.ndarray, b: np.ndarray, target_s: float = 10.0, threads: int | None = None):
     """Times the oracle GEMM on a row slice of the problem sized for ~target_s of CPU work."""
     from oracle import ref
-    ref.set_num_threads(_host_threads())   # torchrun exports OMP_NUM_THREADS=1; use every core we may
-    rows = 32
+    # torchrun exports OMP_NUM_THREADS=1; use every core we may unless a thread count is asked for
+    ref.set_num_threads(threads if threads else _host_threads())
+    rows = 8 if threads == 1 else 32
     t0 = time.perf_counter()
     ref.matmul_rows(a, b, 0, rows)
     dt = time.perf_counter() - t0
-    rows = int(max(32, min(a.shape[0], rows * target_s / max(dt, 1e-3))))
+    rows = int(max(8, min(a.shape[0], rows * target_s / max(dt, 1e-3))))
     rows -= rows % 8
     t0 = time.perf_counter()
     ref.matmul_rows(a, b, 0, rows)
     dt = time.perf_counter() - t0
     tflops = 2.0 * rows * b.shape[0] * b.shape[1] / dt / 1e12
     return tflops, rows, dt, ref.num_threads()
+
+
+def headline_config(world: int) -> dict:
+    """The workload description, identical in both arms (`--impl reference` times the same problem)."""
+    return {"workload": f"f32 GEMM C=A*B, M=N=K={M}, uniform[-1,1), row-major; one problem per GPU per step",
+            "l2": f"operands {M * K * 4 >> 20} MiB each (L2 is 126 MB)", "parallelism": f"replicas x{world}"}
 
 
 def run_reference(args):
@@ -134,45 +152,139 @@ def run_reference(args):
     dt = time.perf_counter() - t0
     tflops = 2.0 * rows * N * K * args.steps / dt / 1e12
     line = {
-        "impl": "reference", "metric": "f32 GEMM TFLOP/s (8192^3)", "value": tflops, "unit": "TFLOP/s",
+        "impl": "reference", "metric": f"f32 GEMM TFLOP/s ({M}^3)", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "f32 GEMM C=A*B, M=N=K=8192, uniform[-1,1), row-major",
-                   "note": "reference CPU arithmetic (oracle restatement; the Rust+MLIR reference cannot be "
-                           "built here); each step = a 64-row slice of the 8192^3 product"},
+        "config": headline_config(args.gpus),
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": ref.num_threads(), "kind": "port",
-                         "sample": f"{rows} of {M} rows per step, {args.steps} steps"},
+                         "sample": f"{rows} of {M} rows of the product per step, {args.steps} steps; the reference's CPU "
+                                   "arithmetic as restated by the oracle (the Rust + MLIR reference cannot be built "
+                                   "here), OpenMP over rows"},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
+MLP_DIMS = (4096, 1024, 4096, 1024)   # batch, d_in, d_hid, d_out of configuration 2
+MLP_GEMM_FLOPS = 5 * 2.0 * 4096 * 4096 * 1024   # two forward products, dZ1, dW2, dW1
+# streaming passes of the step if nothing were fused: bias adds 128 + 32 MiB, tanh 128, sigmoid 32, MSE + dY 48,
+# sigmoid' 48, tanh' 192, column sums 80 (read + write bytes)
+MLP_STREAM_BYTES_UNFUSED = 688 * (1 << 20)
+
+
+def mlp_record(cb, torch, L, peaks, peaks_kind, do_cpu=True, do_e2e=True, steps=30):
+    """Configuration 2, "MLP fwd+bwd samples/s vs host CPU": batch 4096, 1024 -> 4096 (tanh) -> 1024 (sigmoid),
+    MSE, all weight and bias gradients.  Returns {value.., roofline, cpu_baseline, e2e}."""
+    from cleave_b200 import autodiff, linalg, workloads
+    from cleave_b200._lib import c_f32p
+    batch, d_in, d_hid, d_out = MLP_DIMS
+    X, W1, b1, W2, b2, T = workloads.mlp_inputs()
+    net = autodiff.MLP2(d_in, d_hid, d_out)
+    net.load(W1, b1, W2, b2)
+    tX, tT = linalg.Tensor(X), linalg.Tensor(T)
+    loss_dev = linalg.Tensor.zero(1)
+    for _ in range(3):
+        net.forward_backward(tX, tT, loss_out=loss_dev)
+    cb.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = L.cleave_cuda_kernel_launches()
+    L.cleave_cuda_profile_begin()
+    e0.record()
+    for i in range(steps):
+        net.forward_backward(tX, tT, loss_out=loss_dev)     # the loss stays on the device ...
+        if (i + 1) % 10 == 0:
+            loss = loss_dev[0]                                # ... and is read back as a training loop logs it
+    e1.record()
+    e1.synchronize()
+    cnt = ctypes.c_int32(0)
+    gemm_ms = L.cleave_cuda_profile_end(ctypes.byref(cnt)) / steps
+    launches = (L.cleave_cuda_kernel_launches() - l0) / steps
+    ms = e0.elapsed_time(e1) / steps
+    tensor_peak = peaks["bf16_tflops_sustained"] / 6.0     # a step is a long sequence of kernels: sustained basis
+    rec = {"metric": "MLP fwd+bwd samples/s", "value": batch / (ms * 1e-3), "unit": "samples/s", "ms_per_step": ms,
+           "steps": steps, "loss": loss, "gpu_launches_per_step": launches,
+           "config": "batch 4096, 1024->4096 tanh->1024 sigmoid, MSE vs uniform[0,1) targets, Xavier weights, f32; loss "
+                     "read back every 10 steps",
+           "roofline": {"bound": "tensor", "achieved": MLP_GEMM_FLOPS / (ms * 1e-3) / 1e12, "peak": tensor_peak,
+                        "unit": "TFLOP/s", "frac": MLP_GEMM_FLOPS / (ms * 1e-3) / 1e12 / tensor_peak,
+                        "frac_of_burst_basis": MLP_GEMM_FLOPS / (ms * 1e-3) / 1e12 / (peaks["bf16_tflops"] / 6.0),
+                        "gemm_kernels_ms_per_step": gemm_ms,
+                        "other_kernels_ms_per_step": max(ms - gemm_ms, 0.0),
+                        "stream_bytes_unfused": MLP_STREAM_BYTES_UNFUSED,
+                        "peak_basis": f"{peaks_kind} bf16_tflops_sustained / 2 (tf32) / 3 (split); 5 GEMMs x 34.36 GFLOP "
+                                      "per step are the algorithmic work, the streaming passes ride in the remainder",
+                        "traffic": None}}
+    # ---- end to end: every step uploads that step's inputs (X and T, pinned host memory) on the copy engine,
+    # runs forward + backward and reads the loss back on the host; two input sets alternate so step i's compute
+    # overlaps step i+1's upload.
+    if do_e2e:
+        nX, nT = X.size, T.size
+        pins = [L.cleave_cuda_host_alloc(4 * n) for n in (nX, nT)]
+        if not all(pins):
+            cb._lib.raise_last_error("pinned host allocation")
+        hX = np.ctypeslib.as_array(ctypes.cast(pins[0], c_f32p), shape=(nX,))
+        hT = np.ctypeslib.as_array(ctypes.cast(pins[1], c_f32p), shape=(nT,))
+        hX[:] = X.ravel()
+        hT[:] = T.ravel()
+        sets = [(tX, tT), (linalg.Tensor.empty(batch, d_in), linalg.Tensor.empty(batch, d_out))]
+
+        def up(k):
+            if L.cleave_cuda_upload_async_f32(sets[k][0]._h, hX.ctypes.data_as(c_f32p), nX) != 0 or \
+                    L.cleave_cuda_upload_async_f32(sets[k][1]._h, hT.ctypes.data_as(c_f32p), nT) != 0:
+                cb._lib.raise_last_error("upload_async")
+
+        def run(n):
+            up(0)
+            for i in range(n):
+                if i + 1 < n:
+                    up((i + 1) & 1)
+                last = net.forward_backward(sets[i & 1][0], sets[i & 1][1])    # returns the loss: a host read
+            return last
+
+        run(3)
+        L.cleave_cuda_transfers_sync()
+        e0.record()
+        e2e_loss = run(steps)
+        e1.record()
+        e1.synchronize()
+        L.cleave_cuda_transfers_sync()
+        e2e_ms = e0.elapsed_time(e1) / steps
+        rec["e2e"] = {"value": batch / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                      "h2d_bytes_per_step": 4 * (nX + nT), "d2h_bytes_per_step": 4, "steps": steps, "loss": e2e_loss}
+        del sets
+        for p in pins:
+            L.cleave_cuda_host_free(p)
+    del net, tX, tT
+    # ---- the reference's CPU arithmetic for the same step (oracle), on this box's host cores
+    if do_cpu:
+        from oracle import ref
+        ref.set_num_threads(_host_threads())
+        t0 = time.perf_counter()
+        r = ref.mlp2_fwd_bwd(X, W1, b1, W2, b2, T)
+        dt = time.perf_counter() - t0
+        cores = ref.num_threads()
+        ref.set_num_threads(1)
+        sl = 64
+        t0 = time.perf_counter()
+        ref.mlp2_fwd_bwd(X[:sl], W1, b1, W2, b2, T[:sl])
+        dt1 = time.perf_counter() - t0
+        ref.set_num_threads(_host_threads())
+        rec["cpu_baseline"] = {"value": batch / dt, "unit": "samples/s", "cores": cores, "kind": "port",
+                               "sample": f"one full forward+backward step of configuration 2 ({dt:.1f} s), the oracle's "
+                                         "restatement of the reference loops, OpenMP over rows",
+                               "loss": float(r["loss"]),
+                               "single_thread": {"value": sl / dt1, "unit": "samples/s", "cores": 1,
+                                                 "sample": f"a {sl}-sample batch slice ({dt1:.1f} s); the reference "
+                                                           "itself runs on one thread"}}
+    return rec
+
+
 def secondary_configs(cb, torch, peaks):
-    """MLP forward+backward (configuration 2) and linear-regression step (configuration 1)."""
+    """Linear-regression step (configuration 1)."""
     from cleave_b200 import autodiff, linalg, workloads
     out = {}
     L = cb.lib()
-    # --- MLP 4096 x (1024 -> 4096 tanh -> 1024 sigmoid), MSE, all grads
-    X, W1, b1, W2, b2, T = workloads.mlp_inputs()
-    net = autodiff.MLP2(1024, 4096, 1024)
-    net.load(W1, b1, W2, b2)
-    tX, tT = linalg.Tensor(X), linalg.Tensor(T)
-    for _ in range(3):
-        net.forward_backward(tX, tT)
-    cb.sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    steps = 10
-    e0.record()
-    for _ in range(steps):
-        loss = net.forward_backward(tX, tT)
-    e1.record()
-    e1.synchronize()
-    ms = e0.elapsed_time(e1) / steps
-    gemm_flops = 5 * 2.0 * 4096 * 4096 * 1024
-    out["mlp_fwd_bwd"] = {"samples_per_s": 4096 / (ms * 1e-3), "ms_per_step": ms, "loss": loss,
-                          "gemm_tflops": gemm_flops / (ms * 1e-3) / 1e12,
-                          "config": "batch 4096, 1024->4096 tanh->1024 sigmoid, MSE, f32"}
-    del net, tX, tT
     # --- linear regression 1,048,576 x 16.  One operand set is 72 MiB and would sit in the 126 MB L2,
     # so four distinct sets are used in rotation (288 MiB touched per rotation).
     sets = []
@@ -333,117 +445,101 @@ def run_gemm_sweep(args):
           flush=True)
 
 
-def run_batched_gemm(args):
-    """Configuration 4a: 64 independent 4096^3 products sharded by batch index over the ranks
-    (b -> rank b mod G), no collective.  Strong scaling: total work fixed."""
+def _dist_setup():
+    """torch + process group (NCCL, one rank per GPU) + the library on torch's current stream; idempotent."""
     import torch
     import torch.distributed as dist
 
     import cleave_b200 as cb
-    from cleave_b200 import dp, linalg, workloads
+    from cleave_b200 import dp
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     L = cb.lib()
     if L.cleave_cuda_init(local) != 0:
         cb._lib.raise_last_error("init")
-    dp.use_torch_stream()
-    batch, sz = 64, 4096
-    mine = list(dp.batch_shard(batch, rank, world))
-    # every problem of this rank is distinct data (seed 100 + b); a shared pair of generators keeps
-    # host set-up time bounded: problem b uses rows of one long seeded stream
-    A = np.stack([workloads.uniform_pm1(100 + b, sz, sz) for b in mine[:2]] * ((len(mine) + 1) // 2))[:len(mine)]
-    B = np.stack([workloads.uniform_pm1(300 + b, sz, sz) for b in mine[:2]] * ((len(mine) + 1) // 2))[:len(mine)]
-    ta, tb = linalg.Tensor(A), linalg.Tensor(B)
-    tc = linalg.Tensor.empty(len(mine), sz, sz)
-    del A, B
+    if (L.cleave_cuda_get_stream() or 0) != torch.cuda.current_stream().cuda_stream or \
+            torch.cuda.current_stream().cuda_stream == 0:
+        dp.use_torch_stream()
+    return torch, dist, cb, L, rank, world, local
 
+
+def _timed_max_over_ranks(torch, dist, world, fn, steps):
+    """Average device time of fn() over `steps` calls between barriers, as the maximum over the ranks."""
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()) / steps
+
+
+def _device_uniform_pm1(torch, tensor, seed):
+    """Fills a library tensor in place with seeded iid uniform[-1, 1) values generated on the device (torch's
+    Philox generator: set-up plumbing for inputs too large to draw on the host inside a bench run)."""
+    from cleave_b200 import dp
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    dp.as_torch(tensor).uniform_(-1.0, 1.0, generator=g)
+
+
+def measure_batched_gemm(env, steps, warmup):
+    """Configuration 4a: 64 independent 4096^3 products, batch index b on rank b mod G, no collective.
+    Every problem is distinct seeded data (seed 100 + b for A, 300 + b for B), generated on the device."""
+    torch, dist, cb, L, rank, world, _ = env
+    from cleave_b200 import dp, linalg
+    batch, sz = 64, 4096
+    mine = list(dp.batch_shard(batch, rank, world))
+    ta, tb = linalg.Tensor.empty(len(mine), sz, sz), linalg.Tensor.empty(len(mine), sz, sz)
+    tc = linalg.Tensor.empty(len(mine), sz, sz)
+    for i, b in enumerate(mine):
+        for t, seed in ((ta, 100 + b), (tb, 300 + b)):
+            view = linalg.Tensor.from_device_ptr(t.data_ptr + 4 * i * sz * sz, sz, sz)
+            _device_uniform_pm1(torch, view, seed)
 
     def step():
         linalg.gemm_into(tc, ta, tb)
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     l0 = L.cleave_cuda_kernel_launches()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
+    ms = _timed_max_over_ranks(torch, dist, world, step, steps)
     launches = L.cleave_cuda_kernel_launches() - l0
-    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / args.steps
-    if rank == 0:
-        print(json.dumps({"metric": "batched f32 GEMM TFLOP/s (64 x 4096^3)", "value": batch * 2.0 * sz ** 3 / ms / 1e9,
-                          "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                          "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                          "dtype": "f32", "data": "synthetic", "gpu_launches": int(launches),
-                          "config": {"workload": f"64 independent 4096^3 products, batch index b on rank b mod {world}; "
-                                                 "two distinct seeded problems per rank repeated to fill its share"}}),
-              flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if L.cleave_cuda_sync() != 0:
+        cb._lib.raise_last_error("batched gemm")
+    del ta, tb, tc
+    L.cleave_cuda_trim()
+    return {"workload": f"64 independent 4096^3 products (distinct seeded data), batch index b on rank b mod {world}",
+            "ms_per_step": ms, "tflops": batch * 2.0 * sz ** 3 / ms / 1e9, "steps": steps, "scaling": "strong",
+            "problems_per_rank": len(mine), "gpu_launches": int(launches)}
 
 
-def run_rowblock_gemm(args):
-    """Row-block sharded large GEMM (16384^3 by default, --size overrides): A and C are split by rows over
-    the ranks on tile boundaries, B is replicated into every rank's own HBM by an NCCL broadcast, no
-    collective in the product itself.  Strong scaling; reported with and without the broadcast."""
-    import torch
-    import torch.distributed as dist
-
-    import cleave_b200 as cb
-    from cleave_b200 import dp, linalg, workloads
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    L = cb.lib()
-    if L.cleave_cuda_init(local) != 0:
-        cb._lib.raise_last_error("init")
-    dp.use_torch_stream()
-    sz = args.size if args.size != 8192 else 16384
+def measure_rowblock_gemm(env, steps, warmup, sz=16384):
+    """Row-block sharded large GEMM: A and C split by rows over the ranks on 256-row tile boundaries, B
+    replicated into every rank's own HBM by an NCCL broadcast (timed without and with that broadcast)."""
+    torch, dist, cb, L, rank, world, _ = env
+    from cleave_b200 import dp, linalg
     lo, hi = dp.row_block(sz, rank, world, tile=256)
     rows = hi - lo
-    # this rank's rows of A (seeded per 1024-row band, so the union over ranks does not depend on G)
-    a_rows = np.concatenate([workloads.uniform_pm1(500 + band, 1024, sz)
-                             for band in range(lo // 1024, (hi + 1023) // 1024)])[lo % 1024:lo % 1024 + rows]
-    ta = linalg.Tensor(np.ascontiguousarray(a_rows))
-    del a_rows
-    tb = linalg.Tensor(workloads.uniform_pm1(2, sz, sz)) if rank == 0 else linalg.Tensor.empty(sz, sz)
+    ta = linalg.Tensor.empty(rows, sz)
+    _device_uniform_pm1(torch, ta, 500 + rank)
+    tb = linalg.Tensor.empty(sz, sz)
+    if rank == 0:
+        _device_uniform_pm1(torch, tb, 2)
     tc = linalg.Tensor.empty(rows, sz)
     b_view = dp.as_torch(tb)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) / steps
 
     def bcast():
         if world > 1:
@@ -457,13 +553,12 @@ def run_rowblock_gemm(args):
         product()
 
     bcast()
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         product()
     l0 = L.cleave_cuda_kernel_launches()
-    ms = timed(product, args.steps)
+    ms = _timed_max_over_ranks(torch, dist, world, product, steps)
     launches = L.cleave_cuda_kernel_launches() - l0
-    ms_with = timed(both, args.steps)
-    # spot check against the other ranks' view of B: a checksum of B must agree everywhere after the broadcast
+    ms_with = _timed_max_over_ranks(torch, dist, world, both, steps)
     chk = torch.tensor([float(b_view[:: max(1, b_view.numel() // 4096)].double().sum())], device="cuda",
                        dtype=torch.float64)
     same = True
@@ -472,107 +567,169 @@ def run_rowblock_gemm(args):
         dist.all_reduce(lo_t, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi_t, op=dist.ReduceOp.MAX)
         same = bool(lo_t.item() == hi_t.item())
-    if rank == 0:
-        flops = 2.0 * sz ** 3
-        print(json.dumps({"metric": f"row-block f32 GEMM TFLOP/s ({sz}^3)", "value": flops / ms / 1e9, "unit": "TFLOP/s",
-                          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-                          "data": "synthetic", "gpu_launches": int(launches),
-                          "with_broadcast": {"ms_per_step": ms_with, "value": flops / ms_with / 1e9,
-                                             "broadcast_bytes": 4 * sz * sz},
-                          "b_identical_on_all_ranks": same,
-                          "config": {"workload": f"C = A B, M = N = K = {sz}; A and C split by rows over {world} rank(s) on "
-                                                 "256-row tile boundaries, B replicated by an NCCL broadcast (outside "
-                                                 "the timed region for `value`, inside for `with_broadcast`)"}}),
-              flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if L.cleave_cuda_sync() != 0:
+        cb._lib.raise_last_error("row-block gemm")
+    del ta, tb, tc, b_view
+    L.cleave_cuda_trim()
+    flops = 2.0 * sz ** 3
+    return {"workload": f"C = A B, M = N = K = {sz}; A and C split by rows over {world} rank(s), B replicated by an "
+                        "NCCL broadcast", "ms_per_step": ms, "tflops": flops / ms / 1e9, "steps": steps,
+            "scaling": "strong", "gpu_launches": int(launches),
+            "with_broadcast": {"ms_per_step": ms_with, "tflops": flops / ms_with / 1e9, "broadcast_bytes": 4 * sz * sz},
+            "b_identical_on_all_ranks": same}
 
 
-def run_dp_mlp(args):
-    """Configuration 4b: the 2-layer MLP trained data-parallel, global batch 32768 split evenly over
-    the ranks, SGD lr 1e-3, gradients all-reduced (mean) with NCCL each step.  Strong scaling."""
-    import torch
-    import torch.distributed as dist
-
-    import cleave_b200 as cb
-    from cleave_b200 import autodiff, dp, linalg, workloads
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    L = cb.lib()
-    if L.cleave_cuda_init(local) != 0:
-        cb._lib.raise_last_error("init")
-    dp.use_torch_stream()
-    global_batch, d_in, d_hid, d_out = args.global_batch, 1024, 4096, 1024
-    _, W1, b1, W2, b2, _ = workloads.mlp_inputs(1, d_in, d_hid, d_out)
-    if args.dp_mode == "nccl" or world == 1:
+def _make_dp_trainer(env, mode, d_in, d_hid, d_out, overlap=True):
+    torch, dist, cb, L, rank, world, _ = env
+    from cleave_b200 import autodiff, dp
+    if mode == "nccl" or world == 1:
         net = autodiff.MLP2(d_in, d_hid, d_out)
-        trainer = dp.DataParallel(dp.MLP2Replica(net), overlap=not args.no_overlap)
-        mode = "nccl all-reduce + fused 1/G SGD pass" if world > 1 else "single rank"
+        trainer = dp.DataParallel(dp.MLP2Replica(net), overlap=overlap)
+        how = "nccl all-reduce + fused 1/G SGD pass" if world > 1 else "single rank"
     else:
         n_params = d_in * d_hid + d_hid + d_hid * d_out + d_out
         trainer = dp.FusedDataParallel(n_params, lambda p, g: autodiff.MLP2(d_in, d_hid, d_out, params=p, grads=g),
-                                       multimem=args.dp_mode == "fused")
+                                       multimem=mode == "fused")
         net = trainer.net
-        mode = "one kernel: " + ("multimem.ld_reduce in NVSwitch" if trainer.multimem else "peer loads") + \
-               " + SGD + replication of the new weights"
+        how = "one kernel: " + ("multimem.ld_reduce in NVSwitch" if trainer.multimem else "peer loads") + \
+              " + SGD + replication of the new weights"
+    return trainer, net, how
+
+
+def _dp_small_case_deviation(env, mode):
+    """Trains a small perceptron for 5 steps through the same trainer and compares the weights with
+    whole-batch SGD evaluated in float64 on the host: max |w - w64| / max |w64|."""
+    torch, dist, cb, L, rank, world, _ = env
+    from cleave_b200 import dp, linalg, workloads
+    d_in, d_hid, d_out, per_rank, lr = 32, 64, 16, 64, 0.5
+    gb = per_rank * world
+    _, W1, b1, W2, b2, _ = workloads.mlp_inputs(1, d_in, d_hid, d_out)
+    trainer, net, _ = _make_dp_trainer(env, mode, d_in, d_hid, d_out)
+    net.load(W1, b1, W2, b2)
+    Xg = workloads.normal(1000, gb, d_in)
+    Tg = workloads.uniform01(2000, gb, d_out)
+    lo, hi = dp.shard(gb, rank, world)
+    tX, tT = linalg.Tensor(np.ascontiguousarray(Xg[lo:hi])), linalg.Tensor(np.ascontiguousarray(Tg[lo:hi]))
+    loss_dev = linalg.Tensor.zero(1)
+    for _ in range(5):
+        trainer.step(tX, tT, lr, loss_out=loss_dev)
+    torch.cuda.synchronize()
+    got = net.params.numpy().astype(np.float64)
+    w = [a.astype(np.float64) for a in (W1, b1, W2, b2)]
+    X64, T64 = Xg.astype(np.float64), Tg.astype(np.float64)
+    for _ in range(5):
+        H = np.tanh(X64 @ w[0] + w[1])
+        Y = 1.0 / (1.0 + np.exp(-(H @ w[2] + w[3])))
+        dZ2 = Y * (1.0 - Y) * 2.0 * (Y - T64) / Y.size   # the mean over ranks of per-rank means is the global mean
+        dZ1 = (1.0 - H * H) * (dZ2 @ w[2].T)
+        g = [X64.T @ dZ1, dZ1.sum(0), H.T @ dZ2, dZ2.sum(0)]
+        w = [a - lr * b for a, b in zip(w, g)]
+    want = np.concatenate([a.ravel() for a in w])
+    del trainer, net
+    return float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
+
+
+def measure_dp_mlp(env, mode, steps, warmup, global_batch=32768, overlap=True, log_every=10, clocks=False):
+    """Configuration 4b: the 2-layer MLP trained data-parallel, global batch split evenly over the ranks,
+    SGD lr 1e-3, gradients averaged over the ranks every step."""
+    torch, dist, cb, L, rank, world, local = env
+    from cleave_b200 import dp, linalg, workloads
+    d_in, d_hid, d_out = 1024, 4096, 1024
+    _, W1, b1, W2, b2, _ = workloads.mlp_inputs(1, d_in, d_hid, d_out)
+    trainer, net, how = _make_dp_trainer(env, mode, d_in, d_hid, d_out, overlap)
     net.load(W1, b1, W2, b2)
     X, T = dp.dp_batch_inputs(global_batch, rank, world, d_in, d_out)
     tX, tT = linalg.Tensor(X), linalg.Tensor(T)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # The loss of every step is computed on the device; the host reads it back every `log_every`
-    # steps (as a training loop logs), so the queue of kernels is not drained after each step.
+    del X, T
     loss_dev = linalg.Tensor.zero(1)
-    log_every = max(1, args.log_every)
-    for _ in range(args.warmup):
+    state = {"loss": None, "i": 0}
+
+    def step():
         trainer.step(tX, tT, 1e-3, loss_out=loss_dev)
-    barrier()
-    launches0 = L.cleave_cuda_kernel_launches()
-    sampler = ClockSampler(local) if rank == 0 else None
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
+        state["i"] += 1
+        if state["i"] % log_every == 0:
+            state["loss"] = loss_dev[0]      # the host reads the loss back as a training loop logs it
+
+    for _ in range(warmup):
         trainer.step(tX, tT, 1e-3, loss_out=loss_dev)
-        if (i + 1) % log_every == 0 or i + 1 == args.steps:
-            loss = loss_dev[0]
-    e1.record()
-    barrier()
-    clocks = sampler.stop() if sampler else None
-    launches = L.cleave_cuda_kernel_launches() - launches0
-    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    l0 = L.cleave_cuda_kernel_launches()
+    sampler = ClockSampler(local) if (clocks and rank == 0) else None
+    ms = _timed_max_over_ranks(torch, dist, world, step, steps)
+    clk = sampler.stop() if sampler else None
+    launches = L.cleave_cuda_kernel_launches() - l0
+    state["loss"] = loss_dev[0]
     psum = torch.tensor([float(dp.as_torch(net.params).double().sum())], device="cuda", dtype=torch.float64)
     pmin, pmax = psum.clone(), psum.clone()
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(pmin, op=dist.ReduceOp.MIN)
         dist.all_reduce(pmax, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / args.steps
-    if rank == 0:
-        nparams = net.n_params
-        print(json.dumps({
-            "metric": "MLP data-parallel training samples/s", "value": global_batch / (ms * 1e-3), "unit": "samples/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"2-layer MLP 1024->4096 tanh->1024 sigmoid, MSE, SGD lr 1e-3, global batch "
-                                   f"{global_batch} split over {world} rank(s), gradient all-reduce (mean) every step",
-                       "allreduce_bytes_per_step": 4 * nparams, "exchange": mode, "loss_read_back_every": log_every,
-                       "overlap": not args.no_overlap},
-            "gpu_launches": int(launches), "clocks": clocks, "loss": loss,
-            "replicas_identical": bool(pmin.item() == pmax.item()),
-            "gemm_tflops_per_gpu": 5 * 2.0 * (global_batch / world) * d_hid * d_in / (ms * 1e-3) / 1e12,
-        }), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if L.cleave_cuda_sync() != 0:
+        cb._lib.raise_last_error("dp_mlp")
+    rec = {"workload": f"2-layer MLP 1024->4096 tanh->1024 sigmoid, MSE, SGD lr 1e-3, global batch {global_batch} over "
+                       f"{world} rank(s), gradient mean every step", "exchange": how, "ms_per_step": ms,
+           "samples_per_s": global_batch / (ms * 1e-3), "steps": steps, "scaling": "strong",
+           "allreduce_bytes_per_step": 4 * net.n_params, "loss": state["loss"], "gpu_launches": int(launches),
+           "replicas_identical": bool(pmin.item() == pmax.item()),
+           "gemm_tflops_per_gpu": 5 * 2.0 * (global_batch / world) * d_hid * d_in / (ms * 1e-3) / 1e12}
+    if clk:
+        rec["clocks"] = clk
+    del trainer, net, tX, tT
+    L.cleave_cuda_trim()
+    return rec
+
+
+def sharded_record(env, args):
+    """The three workloads that shard over GPUs, run by the ranks of this job one after the other.  At one
+    rank these are the one-GPU times the N > 1 lines of the same series of runs are compared with."""
+    torch, dist, cb, L, rank, world, _ = env
+    out = {"batched_gemm_64x4096": measure_batched_gemm(env, steps=5, warmup=3),
+           "rowblock_gemm_16384": measure_rowblock_gemm(env, steps=3, warmup=3)}
+    modes = ["single"] if world == 1 else ["fused", "nccl"]
+    for mode in modes:
+        rec = measure_dp_mlp(env, mode, steps=20, warmup=3)
+        rec["small_case_max_rel_deviation_from_f64_sgd"] = _dp_small_case_deviation(env, mode)
+        out["dp_mlp_32768" + ("" if mode == "single" else "_" + mode)] = rec
+    return out
+
+
+def run_batched_gemm(args):
+    env = _dist_setup()
+    rec = measure_batched_gemm(env, args.steps, args.warmup)
+    if env[4] == 0:
+        print(json.dumps({"metric": "batched f32 GEMM TFLOP/s (64 x 4096^3)", "value": rec["tflops"], "unit": "TFLOP/s",
+                          "n_gpus": env[5], "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic", "config": {"workload": rec["workload"]}, **rec}),
+              flush=True)
+    if env[5] > 1:
+        env[1].destroy_process_group()
+
+
+def run_rowblock_gemm(args):
+    env = _dist_setup()
+    sz = args.size if args.size != 8192 else 16384
+    rec = measure_rowblock_gemm(env, args.steps, args.warmup, sz)
+    if env[4] == 0:
+        print(json.dumps({"metric": f"row-block f32 GEMM TFLOP/s ({sz}^3)", "value": rec["tflops"], "unit": "TFLOP/s",
+                          "n_gpus": env[5], "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic", "config": {"workload": rec["workload"]}, **rec}),
+              flush=True)
+    if env[5] > 1:
+        env[1].destroy_process_group()
+
+
+def run_dp_mlp(args):
+    env = _dist_setup()
+    mode = "single" if env[5] == 1 else args.dp_mode
+    rec = measure_dp_mlp(env, mode, args.steps, args.warmup, args.global_batch, not args.no_overlap,
+                         max(1, args.log_every), clocks=True)
+    if env[4] == 0:
+        print(json.dumps({"metric": "MLP data-parallel training samples/s", "value": rec["samples_per_s"],
+                          "unit": "samples/s", "n_gpus": env[5], "warmup": args.warmup, "higher_is_better": True,
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": rec["workload"], "exchange": rec["exchange"],
+                                     "overlap": not args.no_overlap}, **rec}), flush=True)
+    if env[5] > 1:
+        env[1].destroy_process_group()
 
 
 def main():

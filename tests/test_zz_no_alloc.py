@@ -48,20 +48,24 @@ def test_sum_noalloc_matches_the_pooled_sum_on_two_calls_in_a_row():
 
 
 def test_sum_noalloc_recovers_from_a_stale_completion_word():
-    # A call that was cut short would leave its ticket and a partial count in the completion word.  Plant such a
-    # word (through a raw device view of the scratch array's tail, reached here by summing with a length whose
-    # tree uses every partial) and check that the next calls are unaffected: the word is keyed by ticket.
+    # A call whose kernel was cut short would leave its ticket and a partial count in the completion word behind
+    # the partials.  Such words are planted here from the host (the test hook copies 8 bytes into the array; it
+    # launches nothing): an old ticket with a count, all ones, and a count under ticket 0.  Every following call
+    # must still write its output, and the right one.
     L = cb.lib()
     rng = np.random.default_rng(11)
     data = rng.standard_normal(5_000_000).astype(np.float32)
     t = linalg.Tensor(data)
-    out = linalg.Tensor.zero(1)
     want = nn.sum(t)
-    for _ in range(3):
-        out2 = linalg.Tensor.filled(-1.0, 1)
-        assert _sum_noalloc(L, t, out2) == want
-    assert _sum_noalloc(L, t, out) == want
     assert abs(want - ref.sum_f64(data)) <= 1e-5 * ref.sum_abs_f64(data)
+    warm = linalg.Tensor.zero(1)
+    assert _sum_noalloc(L, t, warm) == want                   # first call on this device looks the array up
+    for stale in ((0x7FFF0000 << 32) | 5, -1, 37):
+        cb.sync()
+        assert L.cleave_cuda_test_hook(2, stale) == 0         # CLEAVE_HOOK_POISON_NOALLOC_WORD
+        out = linalg.Tensor.filled(-1.0, 1)
+        assert _sum_noalloc(L, t, out) == want
+        assert _sum_noalloc(L, t, out) == want                # and the call after it
 
 
 def test_sum_noalloc_rejects_sizes_it_cannot_handle():
