@@ -77,7 +77,7 @@ class ClockSampler:
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.p = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}",
-                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                       "--format=csv,noheader,nounits", "-lms", "25"],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
@@ -457,7 +457,9 @@ def _dist_setup():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1 and not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a collective that a failed rank never joins ends with an error after 5 minutes instead of hanging the job
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=300))
     L = cb.lib()
     if L.cleave_cuda_init(local) != 0:
         cb._lib.raise_last_error("init")
@@ -682,13 +684,24 @@ def sharded_record(env, args):
     """The three workloads that shard over GPUs, run by the ranks of this job one after the other.  At one
     rank these are the one-GPU times the N > 1 lines of the same series of runs are compared with."""
     torch, dist, cb, L, rank, world, _ = env
-    out = {"batched_gemm_64x4096": measure_batched_gemm(env, steps=5, warmup=3),
-           "rowblock_gemm_16384": measure_rowblock_gemm(env, steps=3, warmup=3)}
+    out = {}
     modes = ["single"] if world == 1 else ["fused", "nccl"]
+    jobs = [("batched_gemm_64x4096", lambda: measure_batched_gemm(env, steps=5, warmup=3)),
+            ("rowblock_gemm_16384", lambda: measure_rowblock_gemm(env, steps=3, warmup=3))]
     for mode in modes:
-        rec = measure_dp_mlp(env, mode, steps=20, warmup=3)
-        rec["small_case_max_rel_deviation_from_f64_sgd"] = _dp_small_case_deviation(env, mode)
-        out["dp_mlp_32768" + ("" if mode == "single" else "_" + mode)] = rec
+        def dp_job(mode=mode):
+            rec = measure_dp_mlp(env, mode, steps=20, warmup=3)
+            rec["small_case_max_rel_deviation_from_f64_sgd"] = _dp_small_case_deviation(env, mode)
+            return rec
+        jobs.append(("dp_mlp_32768" + ("" if mode == "single" else "_" + mode), dp_job))
+    for name, job in jobs:
+        try:
+            out[name] = job()
+        except Exception as e:   # noqa: BLE001 - the headline line must still be printed
+            # after a failure the ranks may no longer be in step: record it and leave the remaining workloads out
+            out[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            out["aborted_after"] = name
+            break
     return out
 
 
@@ -741,6 +754,8 @@ def main():
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the sharded workloads that follow the headline")
+    ap.add_argument("--no-mlp", action="store_true", help="skip the MLP forward+backward record")
     ap.add_argument("--workload", default="gemm", choices=["gemm", "dp_mlp", "ops", "gemm_sweep", "batched_gemm",
                                                             "rowblock_gemm"],
                     help="gemm = the headline; the others are secondary configurations")
@@ -775,29 +790,14 @@ def main():
         runner(args)
         return
 
-    import torch
-    import torch.distributed as dist
-
-    import cleave_b200 as cb
     from cleave_b200 import linalg, workloads
     from cleave_b200._lib import c_f32p
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    L = cb.lib()
-    if L.cleave_cuda_init(local) != 0:
-        cb._lib.raise_last_error("init")
-    # Run the library on a torch-owned stream, made current, so torch CUDA events (which record on
+    # The library runs on a torch-owned stream, made current, so torch CUDA events (which record on
     # the current stream) bracket exactly the kernels and copies the library enqueues.
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
-    assert stream.cuda_stream != 0
-    L.cleave_cuda_set_stream(ctypes.c_void_p(stream.cuda_stream))
-    assert L.cleave_cuda_get_stream() == stream.cuda_stream
+    env = _dist_setup()
+    torch, dist, cb, L, rank, world, local = env
+    assert L.cleave_cuda_get_stream() == torch.cuda.current_stream().cuda_stream != 0
     peaks, peaks_kind = measured_peaks()
 
     def barrier():
@@ -874,33 +874,73 @@ def main():
         L.cleave_cuda_data_ptr(C2[0]._h)
         L.cleave_cuda_data_ptr(C2[1]._h)
 
+    def copies_only(steps):
+        # the same transfers on the same buffers and copy engines, no product: what the host <-> device path
+        # allows at this number of ranks (all ranks copy at the same time and share the host's memory and PCIe)
+        for i in range(steps):
+            cur = i & 1
+            up(cur)
+            if L.cleave_cuda_download_async_f32(C2[cur]._h, hcs[cur].ctypes.data_as(c_f32p), hcs[cur].size) != 0:
+                cb._lib.raise_last_error("download_async")
+        L.cleave_cuda_data_ptr(C2[0]._h)
+        L.cleave_cuda_data_ptr(C2[1]._h)
+        for t in A2 + B2:
+            L.cleave_cuda_data_ptr(t._h)
+
+    def timed_region(fn, steps):
+        barrier()
+        e0.record()
+        fn(steps)
+        e1.record()
+        if L.cleave_cuda_transfers_sync() != 0:
+            cb._lib.raise_last_error("transfers")
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
     # as many steps as the device-resident measurement (the fill of the first upload and the drain of the last
     # download are inside the timed region and amortise over the steps)
-    e2e_steps = 0 if args.no_e2e else max(4, min(args.steps, 40))
-    if e2e_steps:
+    e2e_steps = max(4, min(args.steps, 40))
+    e2e_ms = copy_ms = float("nan")
+    if not args.no_e2e:
         e2e_run(3)
         L.cleave_cuda_transfers_sync()
-    barrier()
-    e0.record()
-    if e2e_steps:
-        e2e_run(e2e_steps)
-    e1.record()
-    if L.cleave_cuda_transfers_sync() != 0:
-        cb._lib.raise_last_error("transfers")
-    barrier()
-    e2e_steps = max(e2e_steps, 1)
-    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
+        e2e_ms = timed_region(e2e_run, e2e_steps)
+        copy_ms = timed_region(copies_only, e2e_steps)
     e2e_value = world * FLOPS / (e2e_ms * 1e-3) / 1e12
     checksum = float(hcs[(e2e_steps - 1) & 1][:4096].astype(np.float64).sum())
+    # One synchronous call with host arrays (the entry point a lowering hook targets): upload, product and
+    # download pipelined over row blocks inside the call.
+    single_call_ms = None
+    if not args.no_e2e:
+        def single_call(steps):
+            for _ in range(steps):
+                if L.cleave_cuda_host_gemm_f32(ha.ctypes.data_as(c_f32p), ha.size, hb.ctypes.data_as(c_f32p), hb.size,
+                                               hc0.ctypes.data_as(c_f32p), hc0.size, M, N, K) != hc0.size:
+                    cb._lib.raise_last_error("host_gemm")
+        single_call(1)
+        single_call_ms = timed_region(single_call, 4)
     del A2, B2, C2
     for p in pin:
         L.cleave_cuda_host_free(p)
 
+    # ---- second half of the metric and the sharded workloads (every rank takes part in the latter)
+    del ta, tb, tc
+    L.cleave_cuda_trim()
+    peak_burst = peaks["bf16_tflops"] / 2.0 / 3.0
+    mlp = None
+    if not args.no_mlp and world == 1:
+        mlp = mlp_record(cb, torch, L, peaks, peaks_kind, do_cpu=not args.no_cpu_baseline, do_e2e=not args.no_e2e)
+    sharded = None
+    if not args.no_sharded:
+        sharded = sharded_record(env, args)
+
     if rank != 0:
         if world > 1:
+            if sharded and "aborted_after" in sharded:
+                os._exit(0)
             dist.destroy_process_group()
         return
 
@@ -909,42 +949,70 @@ def main():
     achieved = FLOPS / (kernel_ms * 1e-3) / 1e12
     # 3xTF32-effective tensor peak: dense TF32 runs at half the bf16 rate, and the split issues
     # three MMAs per product.  The kernel is timed alone, launch by launch, so the burst bf16
-    # figure is the denominator; the sustained one is quoted beside it.
-    peak = peaks["bf16_tflops"] / 2.0 / 3.0
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+    # figure is the denominator.  That figure comes from a cuBLAS run at whatever clock the measuring box
+    # held under its power cap, so it is not a hard ceiling: two clock-independent bases are printed beside it.
+    sm_mhz = (clocks or {}).get("sm_mhz") or 0.0
+    nominal = NOMINAL_TF32_DENSE_TFLOPS / 3.0
+    at_clock = nominal * sm_mhz / 1965.0 if sm_mhz else None
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s",
+                "frac": achieved / peak_burst, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_source": NCU_TRAFFIC,
                 "kernel": "gemm_3xtf32_pair_kernel", "kernel_ms": kernel_ms, "launches_timed": n_prof.value,
                 "peak_basis": f"{peaks_kind} bf16_tflops (burst) / 2 (tf32) / 3 (split); "
-                              f"sustained basis {peaks['bf16_tflops_sustained'] / 6.0:.1f}"}
+                              f"sustained basis {peaks['bf16_tflops_sustained'] / 6.0:.1f}",
+                "frac_of_nominal": achieved / nominal,
+                "frac_at_sampled_clock": achieved / at_clock if at_clock else None,
+                "nominal_basis": f"datasheet dense TF32 {NOMINAL_TF32_DENSE_TFLOPS:.0f} TFLOP/s at 1965 MHz / 3 = "
+                                 f"{nominal:.0f}; scaled to the SM clock sampled during the timed region "
+                                 f"({sm_mhz:.0f} MHz): {at_clock if at_clock else float('nan'):.0f}"}
+    if roofline["frac"] > 1.0:
+        roofline["note"] = ("frac > 1: the measured-peak basis (a cuBLAS bf16 run on another box and clock) is not a "
+                            "ceiling for this kernel on this box; read frac_at_sampled_clock / frac_of_nominal")
 
     cpu = None
     if not args.no_cpu_baseline:
         v, rows, dt, cores = cpu_gemm_sample(a_host, b_host)
+        v1, rows1, dt1, _ = cpu_gemm_sample(a_host, b_host, target_s=5.0, threads=1)
         cpu = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-               "sample": f"rows 0..{rows} of the 8192^3 product ({dt:.1f} s), bit-identical restatement of the "
-                         "reference loop, OpenMP over rows"}
+               "sample": f"rows 0..{rows} of the {M}^3 product ({dt:.1f} s), bit-identical restatement of the "
+                         "reference loop, OpenMP over rows",
+               "single_thread": {"value": v1, "unit": "TFLOP/s", "cores": 1,
+                                 "sample": f"rows 0..{rows1} ({dt1:.1f} s); the reference itself runs on one thread "
+                                           "(cleave/src/main.rs:150-152)"}}
 
+    cfg = headline_config(world)   # identical to the reference arm's
+    roofline["arithmetic"] = "3xTF32 split on tcgen05, f32 accumulate, K chunks of 256 summed in f32"
+    e2e = {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 2 * nbytes,
+           "d2h_bytes_per_step": nbytes, "steps": e2e_steps, "checksum": checksum,
+           "copy_ceiling_ms": copy_ms, "frac_of_copy_ceiling": copy_ms / e2e_ms if e2e_ms == e2e_ms else None,
+           "single_call_ms": single_call_ms,
+           "note": "copies on the copy engines, two tensor sets alternating: compute of step i overlaps the upload of "
+                   "step i+1 and the download of step i-1; copy_ceiling_ms = the same copies with no product, all "
+                   "ranks at once; single_call_ms = one synchronous cleave_cuda_host_gemm_f32 call per step"}
     line = {
         "metric": f"f32 GEMM TFLOP/s ({M}^3)", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"f32 GEMM C=A*B, M=N=K={M}, uniform[-1,1), row-major; one problem per GPU per step",
-                   "arithmetic": "3xTF32 split on tcgen05, f32 accumulate, K chunks of 256 summed in f32",
-                   "l2": f"operands {M * K * 4 >> 20} MiB each (L2 is 126 MB)", "parallelism": f"replicas x{world}"},
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 2 * nbytes,
-                "d2h_bytes_per_step": nbytes, "steps": e2e_steps, "checksum": checksum,
-                "note": "copies on the copy engines, two tensor sets alternating: compute of step i overlaps the "
-                        "upload of step i+1 and the download of step i-1"},
-        "gpu_launches": int(launches),
-        "clocks": clocks,
-        "roofline": roofline,
+        "config": cfg, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
         "cpu_baseline": cpu,
     }
+    if mlp is not None:
+        # the second half of the metric, also nested where a reader of roofline / cpu_baseline / e2e looks for it
+        line["mlp_fwd_bwd"] = mlp
+        roofline["mlp_fwd_bwd"] = dict(mlp["roofline"], samples_per_s=mlp["value"], ms_per_step=mlp["ms_per_step"])
+        if cpu is not None and "cpu_baseline" in mlp:
+            cpu["mlp_fwd_bwd"] = mlp["cpu_baseline"]
+        if "e2e" in mlp:
+            e2e["mlp_fwd_bwd"] = mlp["e2e"]
+    if sharded is not None:
+        line["sharded"] = sharded
+        roofline["sharded"] = {k: {kk: v[kk] for kk in ("ms_per_step", "tflops", "samples_per_s", "replicas_identical", "error")
+                              if kk in v} for k, v in sharded.items() if isinstance(v, dict)}
     if not args.no_secondary and world == 1:
-        del ta, tb, tc
         line["secondary"] = secondary_configs(cb, torch, peaks)
     print(json.dumps(line), flush=True)
     if world > 1:
+        if sharded and "aborted_after" in sharded:
+            os._exit(0)   # a rank that failed mid-collective cannot take part in an orderly shutdown
         dist.destroy_process_group()
 
 
