@@ -469,8 +469,9 @@ def _dist_setup():
     return torch, dist, cb, L, rank, world, local
 
 
-def _timed_max_over_ranks(torch, dist, world, fn, steps):
-    """Average device time of fn() over `steps` calls between barriers, as the maximum over the ranks."""
+def _timed_max_over_ranks(torch, dist, world, fn, steps, finish=None):
+    """Average device time of fn() over `steps` calls between barriers, as the maximum over the ranks.
+    `finish()` runs before the closing event (work of the last step that another stream still holds)."""
     def barrier():
         if world > 1:
             dist.barrier()
@@ -480,6 +481,8 @@ def _timed_max_over_ranks(torch, dist, world, fn, steps):
     e0.record()
     for _ in range(steps):
         fn()
+    if finish:
+        finish()
     e1.record()
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
@@ -615,6 +618,8 @@ def _dp_small_case_deviation(env, mode):
     loss_dev = linalg.Tensor.zero(1)
     for _ in range(5):
         trainer.step(tX, tT, lr, loss_out=loss_dev)
+    if hasattr(trainer, "flush"):
+        trainer.flush()
     torch.cuda.synchronize()
     got = net.params.numpy().astype(np.float64)
     w = [a.astype(np.float64) for a in (W1, b1, W2, b2)]
@@ -652,11 +657,14 @@ def measure_dp_mlp(env, mode, steps, warmup, global_batch=32768, overlap=True, l
         if state["i"] % log_every == 0:
             state["loss"] = loss_dev[0]      # the host reads the loss back as a training loop logs it
 
+    flush = getattr(trainer, "flush", None)
     for _ in range(warmup):
         trainer.step(tX, tT, 1e-3, loss_out=loss_dev)
+    if flush:
+        flush()
     l0 = L.cleave_cuda_kernel_launches()
     sampler = ClockSampler(local) if (clocks and rank == 0) else None
-    ms = _timed_max_over_ranks(torch, dist, world, step, steps)
+    ms = _timed_max_over_ranks(torch, dist, world, step, steps, finish=flush)
     clk = sampler.stop() if sampler else None
     launches = L.cleave_cuda_kernel_launches() - l0
     state["loss"] = loss_dev[0]

@@ -75,10 +75,14 @@ SIGNATURES = {
     "cleave_cuda_gemm_batched_f32": (c_buf, [c_buf, c_buf, i32, i32, i32, i32]),
     "cleave_cuda_gemm_ex_f32": (i32, [c_buf, c_buf, c_buf, i32, i32, i32, i32, i32, i32, i32, c_buf, i32]),
     "cleave_cuda_gemm_dact_f32": (i32, [c_buf, c_buf, c_buf, i32, i32, i32, i32, i32, i32, i32, c_buf, i32]),
+    "cleave_cuda_gemm_fused_f32": (i32, [c_buf, c_buf, c_buf, i32, i32, i32, i32, i32, i32, i32, c_buf, i32, c_buf, i32,
+                                         c_buf, c_buf, c_buf]),
+    "cleave_cuda_split_lo_f32": (c_buf, [c_buf]),
     "cleave_cuda_bias_act_f32": (c_buf, [c_buf, c_buf, i32, i32, i32]),
     "cleave_cuda_mse_f32": (f32, [c_buf, c_buf, c_buf]),
     "cleave_cuda_mse_act_bwd_f32": (f32, [c_buf, c_buf, c_buf, i32]),
     "cleave_cuda_mse_act_bwd_dev_f32": (i32, [c_buf, c_buf, c_buf, i32, c_buf]),
+    "cleave_cuda_mse_act_bwd_lo_f32": (i32, [c_buf, c_buf, c_buf, i32, c_buf, c_buf]),
     "cleave_cuda_sgd_f32": (i32, [c_buf, c_buf, f32, f32]),
     "cleave_cuda_host_gemm_f32": (i64, [c_f32p, i64, c_f32p, i64, c_f32p, i64, i32, i32, i32]),
     "cleave_cuda_host_binary_f32": (i64, [i32, c_f32p, i64, c_f32p, i64, c_f32p, i64]),

@@ -22,7 +22,7 @@ import numpy as np
 
 from . import nn
 from ._lib import lib, raise_last_error
-from .linalg import Tensor, gemm_into
+from .linalg import Tensor, gemm_into, split_lo
 
 _ACT_BWD = {"tanh": nn.tanh_bwd, "sigmoid": nn.sigmoid_bwd}
 
@@ -35,12 +35,17 @@ class MLP2:
     """
 
     def __init__(self, d_in: int, d_hid: int, d_out: int, act1: str = "tanh", act2: str = "sigmoid",
-                 params: Tensor | None = None, grads: Tensor | None = None):
+                 params: Tensor | None = None, grads: Tensor | None = None, chain_lo: bool | None = None):
         """``params`` / ``grads``: optional caller-provided flat buffers (e.g. views of symmetric
-        memory shared with the other data-parallel ranks); allocated here when omitted."""
+        memory shared with the other data-parallel ranks); allocated here when omitted.
+        ``chain_lo``: hand the lo planes of the tensor-core split from one product to the next (each GEMM's
+        epilogue writes the plane its consumer needs) instead of letting every product split its operands
+        again; default: on for layer sizes that are multiples of 32 (what the tensor-core route needs to read
+        the tensors in place).  The gradients are bit-identical either way."""
         if act1 not in _ACT_BWD or act2 not in _ACT_BWD:
             raise ValueError("activations with a declared derivative rule: tanh, sigmoid")
         self.d_in, self.d_hid, self.d_out, self.act1, self.act2 = d_in, d_hid, d_out, act1, act2
+        self.chain_lo = all(d % 32 == 0 for d in (d_in, d_hid, d_out)) if chain_lo is None else bool(chain_lo)
         sizes = [d_in * d_hid, d_hid, d_hid * d_out, d_out]
         shapes = [(d_in, d_hid), (d_hid,), (d_hid, d_out), (d_out,)]
         self.n_params = sum(sizes)
@@ -78,33 +83,60 @@ class MLP2:
         return H, Y
 
     def forward_backward(self, X: Tensor, T: Tensor, keep: bool = False, on_grads_ready=None,
-                         loss_out: Tensor | None = None):
+                         loss_out: Tensor | None = None, before_layer=None):
         """One forward + backward pass; gradients land in ``self.grads``.  Returns the loss
         (and, with ``keep``, the intermediates for inspection).  ``on_grads_ready(i)`` is called
-        when a gradient bucket is final: 0 = [dW2 | db2], 1 = [dW1 | db1].  With ``loss_out`` (a
-        one-element tensor) the loss is left on the device, nothing waits and ``None`` is returned."""
-        H, Y = self.forward(X)
-        loss, dZ2 = nn.mse_act_bwd(Y, T, self.act2, loss_out)   # dY and act2'(Y) * dY in one pass
-        # dH first: it is the last reader of W2 in this step, so once [dW2 | db2] are announced a
-        # data-parallel exchange may already overwrite W2 and b2 while the rest of the pass runs.
+        when a gradient bucket is final and its weights are no longer read in this pass:
+        1 = [dW1 | db1] first, then 0 = [dW2 | db2].  ``before_layer(i)`` is called just before the
+        first kernel that reads layer i's weights (1: W1, b1; 2: W2, b2), so a data-parallel driver can
+        let the previous step's exchange of that layer run beside the kernels queued before it.
+        With ``loss_out`` (a one-element tensor) the loss is left on the device, nothing waits and
+        ``None`` is returned."""
+        if before_layer:
+            before_layer(1)
+        batch = X.dims[0]
+        # Lo planes travel with their tensors through the chain when the products are large enough for the
+        # tensor cores (each plane is one extra store in a producer's epilogue, or one streaming pass).
+        chain = self.chain_lo and batch % 32 == 0 and batch * self.d_in * self.d_hid >= (1 << 24)
+        lo = (lambda t: split_lo(t)) if chain else (lambda t: None)
+        new = (lambda *dims: Tensor.empty(*dims)) if chain else (lambda *dims: None)
+        X_lo, W1_lo = lo(X), lo(self.W1)
+        H_lo = new(batch, self.d_hid)
+        H = gemm_into(Tensor.empty(batch, self.d_hid), X, self.W1, bias=self.b1, act=self.act1,
+                      a_lo=X_lo, b_lo=W1_lo, c_lo=H_lo)
+        if before_layer:
+            before_layer(2)
+        W2_lo = lo(self.W2)
+        Y = gemm_into(Tensor.empty(batch, self.d_out), H, self.W2, bias=self.b2, act=self.act2, a_lo=H_lo, b_lo=W2_lo)
+        if chain:
+            dev_loss = loss_out if loss_out is not None else Tensor.empty(1)
+            dZ2, dZ2_lo = nn.mse_act_bwd_lo(Y, T, self.act2, dev_loss)
+            loss = None if loss_out is not None else dev_loss[0]
+        else:
+            loss, dZ2 = nn.mse_act_bwd(Y, T, self.act2, loss_out)   # dY and act2'(Y) * dY in one pass
+            dZ2_lo = None
         # Without ``keep`` dH is never stored: dZ1 = act1'(H) * (dZ2 W2^T) leaves the GEMM's epilogue directly
         # (bit-identical to the two-step form, one pass over H instead of three over H-sized tensors).
         dH = None
+        dZ1_lo = None
         if keep:
-            dH = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True)   # dZ2 W2^T
-            dZ1 = None
-        else:
-            dZ1 = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True, dact_of=H, dact=self.act1)
-        gemm_into(self.dW2, H, dZ2, trans_a=True)            # H^T dZ2
-        self._colsum_into(self.db2, dZ2)
-        if on_grads_ready:
-            on_grads_ready(0)
-        if dZ1 is None:
+            dH = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True, a_lo=dZ2_lo, b_lo=W2_lo)   # dZ2 W2^T
             dZ1 = _ACT_BWD[self.act1](H, dH)
-        gemm_into(self.dW1, X, dZ1, trans_a=True)            # X^T dZ1
+        else:
+            dZ1_lo = new(*H.dims)
+            dZ1 = gemm_into(Tensor.empty(*H.dims), dZ2, self.W2, trans_b=True, dact_of=H, dact=self.act1,
+                            a_lo=dZ2_lo, b_lo=W2_lo, c_lo=dZ1_lo)
+        # Layer 1's gradients first: W1 was last read by the forward product, so its exchange can run beside
+        # the dW2 product, and layer 2's exchange beside the NEXT step's first forward product (which needs
+        # only W1).  dZ1 above was the last reader of W2 in this pass.
+        gemm_into(self.dW1, X, dZ1, trans_a=True, a_lo=X_lo, b_lo=dZ1_lo)            # X^T dZ1
         self._colsum_into(self.db1, dZ1)
         if on_grads_ready:
             on_grads_ready(1)
+        gemm_into(self.dW2, H, dZ2, trans_a=True, a_lo=H_lo, b_lo=dZ2_lo)            # H^T dZ2
+        self._colsum_into(self.db2, dZ2)
+        if on_grads_ready:
+            on_grads_ready(0)
         if keep:
             return loss, dict(H=H, Y=Y, dZ2=dZ2, dH=dH, dZ1=dZ1)
         return loss

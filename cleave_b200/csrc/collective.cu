@@ -34,7 +34,7 @@
 namespace cleave {
 
 constexpr int kMaxRanks = 8;
-constexpr int kDpThreads = 256;
+constexpr int kDpThreads = 128;   // small CTAs: one fits beside a resident tensor-core GEMM CTA (registers)
 constexpr unsigned long long kDpWaitLimitNs = 2000000000ull;   // 2 s across GPUs unless CLEAVE_CUDA_DP_WAIT_MS is set
 
 // Signal-word layout inside each rank's flag buffer (uint32 words).
@@ -300,10 +300,17 @@ extern "C" int32_t cleave_cuda_dp_sgd_allreduce_f32(void* const* params_peers, v
   }();
   a.wait_ns = wait_ns;
   a.status = ctx().status_dev;
-  // A light grid: the kernel is bound by NVLink, not by SMs, and all of its CTAs must be able to
-  // become resident next to whatever else is running (CTAs other than 0 wait for CTA 0).
+  // A light grid of small CTAs: the kernel is bound by NVLink round trips, not by SMs, and it is meant to run
+  // BESIDE a tensor-core GEMM (whose persistent CTAs leave about 11 K registers per SM: room for one 128-thread
+  // CTA of this kernel).  CTAs other than 0 wait only for CTA 0, which is dispatched first.
+  static const int max_ctas = [] {
+    const char* e = getenv("CLEAVE_CUDA_DP_CTAS");
+    const int v = e ? atoi(e) : 0;
+    return (v >= 1 && v <= 1024) ? v : 0;
+  }();
   int grid = ceil_div(a.word_hi - a.word_lo, kDpThreads * 4);
-  if (grid > ctx().sm_count) grid = ctx().sm_count;
+  const int cap = max_ctas ? max_ctas : ctx().sm_count;
+  if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   cudaStream_t s = cuda_stream ? (cudaStream_t)cuda_stream : ctx().stream;
   Trace tr("dp_sgd_allreduce", "offset=%lld len=%lld rank=%d world=%d", (long long)offset, (long long)len, rank, world);

@@ -20,6 +20,12 @@ struct GemmArgs {
   // OUTPUT y (same shape as C); null for a plain product.  Not combined with bias / act.
   const float* dact_y;
   int dact;
+  // Optional low split parts (see split_lo in tc_common.cuh), each the shape of its tensor.  a_lo / b_lo: planes
+  // the caller already holds for the operands (written by an earlier GEMM's c_lo or by split_lo_plane), so the
+  // tensor-core path needs no operand pre-pass; c_lo: receives the low part of every value stored to C.
+  const float* a_lo = nullptr;
+  const float* b_lo = nullptr;
+  float* c_lo = nullptr;
 };
 
 // Derivative of an activation, from the activation's output y, times the upstream value g: the same
@@ -35,6 +41,7 @@ __device__ __forceinline__ float dact_apply(float y, float g, int dact) {
 }
 
 bool launch_gemm_exact(const GemmArgs& g);
+bool split_lo_plane(const float* src, float* dst, int64_t n);   // dst[i] = low split part of src[i]
 bool launch_gemm_3xtf32(const GemmArgs& g);   // false + error if the problem cannot use this path
 bool gemm_3xtf32_supported(const GemmArgs& g);
 int gemm_batch_chunk(int64_t bytes_per_entry, int batch);   // batch entries per pass (workspace and grid limits)

@@ -17,14 +17,17 @@ static bool run_gemm(const GemmArgs& g, int algo) {
     algo = (macs >= kTensorCoreMinMacs && g.m >= 64 && g.n >= 64 && gemm_3xtf32_supported(g)) ? CLEAVE_GEMM_3XTF32
                                                                                               : CLEAVE_GEMM_EXACT;
   }
-  if (algo == CLEAVE_GEMM_EXACT) return launch_gemm_exact(g);
+  // The exact kernel has no lo-plane output of its own: the plane is written by a pass over the finished C.
+  if (algo == CLEAVE_GEMM_EXACT)
+    return launch_gemm_exact(g) && (!g.c_lo || split_lo_plane(g.c, g.c_lo, (int64_t)g.batch * g.m * g.n));
   if (algo == CLEAVE_GEMM_3XTF32) return launch_gemm_3xtf32(g);
   set_error(CLEAVE_CUDA_ERR_ARG, "gemm: unknown algorithm code %d", algo);
   return false;
 }
 
 static int gemm_into(Buf* C, Buf* A, Buf* B, int batch, int m, int n, int k, int ta, int tb, int algo, Buf* bias,
-                     int act, Buf* dact_y = nullptr, int dact = CLEAVE_ACT_IDENTITY) {
+                     int act, Buf* dact_y = nullptr, int dact = CLEAVE_ACT_IDENTITY, Buf* a_lo = nullptr,
+                     Buf* b_lo = nullptr, Buf* c_lo = nullptr) {
   if (batch <= 0 || m <= 0 || n <= 0 || k <= 0)
     return set_error(CLEAVE_CUDA_ERR_ARG, "gemm: batch, m, n, k must be positive (got %d, %d, %d, %d)", batch, m, n, k);
   if (A->len != (int64_t)batch * m * k || B->len != (int64_t)batch * k * n || C->len != (int64_t)batch * m * n)
@@ -48,9 +51,17 @@ static int gemm_into(Buf* C, Buf* A, Buf* B, int batch, int m, int n, int k, int
   }
   Trace tr(dact_y ? "gemm_dact" : "gemm", "batch=%d m=%d n=%d k=%d ta=%d tb=%d algo=%d act=%d", batch, m, n, k, ta ? 1 : 0,
            tb ? 1 : 0, algo, dact_y ? dact : act);
+  if ((a_lo && a_lo->len != A->len) || (b_lo && b_lo->len != B->len) || (c_lo && c_lo->len != C->len))
+    return set_error(CLEAVE_CUDA_ERR_SHAPE, "gemm_fused: a lo plane must have as many elements as its tensor");
+  if (c_lo && (c_lo->ptr == C->ptr || c_lo->ptr == A->ptr || c_lo->ptr == B->ptr))
+    return set_error(CLEAVE_CUDA_ERR_ARG, "gemm_fused: the output lo plane must not alias C or an operand");
   GemmArgs g{A->ptr, B->ptr, C->ptr, batch, m, n, k, ta ? 1 : 0, tb ? 1 : 0, bias ? bias->ptr : nullptr, act,
              dact_y ? dact_y->ptr : nullptr, dact};
-  return run_gemm(g, algo) ? CLEAVE_CUDA_OK : cleave_cuda_last_error();
+  g.a_lo = a_lo ? a_lo->ptr : nullptr;
+  g.b_lo = b_lo ? b_lo->ptr : nullptr;
+  g.c_lo = c_lo ? c_lo->ptr : nullptr;
+  if (!run_gemm(g, algo)) return cleave_cuda_last_error();
+  return CLEAVE_CUDA_OK;
 }
 
 static cleave_buf gemm_new(cleave_buf a, cleave_buf b, int batch, int m, int n, int k, int ta, int tb) {
@@ -118,6 +129,42 @@ int32_t cleave_cuda_gemm_dact_f32(cleave_buf c, cleave_buf a, cleave_buf b, int3
   if (!C || !A || !B || !Y) return -cleave_cuda_last_error();
   int r = gemm_into(C, A, B, batch, m, n, k, trans_a, trans_b, algo, nullptr, CLEAVE_ACT_IDENTITY, Y, act);
   return r == CLEAVE_CUDA_OK ? CLEAVE_CUDA_OK : -r;
+}
+
+int32_t cleave_cuda_gemm_fused_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n,
+                                   int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo, cleave_buf bias,
+                                   int32_t act, cleave_buf y, int32_t dact, cleave_buf a_lo, cleave_buf b_lo,
+                                   cleave_buf c_lo) {
+  ApiLock lock;
+  Buf* C = as_buf(c, "gemm_fused");
+  Buf* A = as_buf(a, "gemm_fused");
+  Buf* B = as_buf(b, "gemm_fused");
+  if (!C || !A || !B) return -cleave_cuda_last_error();
+  Buf* opt[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  cleave_buf given[5] = {bias, y, a_lo, b_lo, c_lo};
+  for (int i = 0; i < 5; ++i)
+    if (given[i]) {
+      opt[i] = as_buf(given[i], "gemm_fused");
+      if (!opt[i]) return -cleave_cuda_last_error();
+    }
+  if (opt[0] && opt[1])
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "gemm_fused: bias + activation and the backward form exclude each other");
+  if (opt[1] && act != CLEAVE_ACT_IDENTITY)
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "gemm_fused: the backward form takes no forward activation");
+  int r = gemm_into(C, A, B, batch, m, n, k, trans_a, trans_b, algo, opt[0], act, opt[1], opt[1] ? dact : CLEAVE_ACT_IDENTITY,
+                    opt[2], opt[3], opt[4]);
+  return r == CLEAVE_CUDA_OK ? CLEAVE_CUDA_OK : -r;
+}
+
+cleave_buf cleave_cuda_split_lo_f32(cleave_buf x) {
+  ApiLock lock;
+  Buf* a = as_buf(x, "split_lo");
+  if (!a) return nullptr;
+  Trace tr("split_lo", "n=%lld", (long long)a->len);
+  Buf* o = new_buf(a->len);
+  if (!o) return nullptr;
+  if (!split_lo_plane(a->ptr, o->ptr, a->len)) { release_buf(o); return nullptr; }
+  return (cleave_buf)o;
 }
 
 }  // extern "C"

@@ -508,7 +508,32 @@ __global__ void __launch_bounds__(256, 4) split_lo_kernel(const float4* __restri
   }
 }
 
+__global__ void split_lo_scalar_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = split_lo(src[i]);
+}
+
 // ---- host side ---------------------------------------------------------------------------------
+bool split_lo_plane(const float* src, float* dst, int64_t n) {
+  cudaStream_t s = ctx().stream;
+  if (aligned16(src) && aligned16(dst)) {
+    const int64_t n4 = n / 4;
+    if (n4 > 0) {
+      split_lo_kernel<<<stream_grid(n4, 256, 4), 256, 0, s>>>(reinterpret_cast<const float4*>(src),
+                                                              reinterpret_cast<float4*>(dst), n4);
+      count_launch();
+    }
+    if (n % 4) {
+      split_lo_scalar_kernel<<<1, 32, 0, s>>>(src + 4 * n4, dst + 4 * n4, n % 4);
+      count_launch();
+    }
+  } else {
+    split_lo_scalar_kernel<<<stream_grid(n, 256, 4), 256, 0, s>>>(src, dst, n);
+    count_launch();
+  }
+  return cuda_ok(cudaGetLastError(), "lo-plane split launch");
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -739,6 +764,7 @@ static bool launch_direct(const GemmArgs& g) {
   p.b_sliced = 0;
   p.b_box_rows = b_box_rows;
   p.c = g.c;
+  p.c_lo = g.c_lo;
   p.bias = g.bias;
   p.dact_y = g.dact_y;
   p.dact = g.dact;
@@ -864,30 +890,34 @@ static bool launch_narrow_transposed(const GemmArgs& g, int slices) {
 static bool launch_lo_plane(const GemmArgs& g) {
   const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
   const int64_t a_elems = (int64_t)g.m * g.k, b_elems = (int64_t)g.n * g.k;
-  const int chunk = gemm_batch_chunk((a_elems + b_elems) * 4, g.batch);
-  float* wa = scratch_alloc(chunk * a_elems * 4);
-  if (!wa) return false;
-  float* wb = scratch_alloc(chunk * b_elems * 4);
-  if (!wb) { scratch_free(wa); return false; }
+  // planes the caller holds are used as they are; a missing one is written here, in chunks of the batch
+  const int64_t scratch_per_entry = ((g.a_lo ? 0 : a_elems) + (g.b_lo ? 0 : b_elems)) * 4;
+  const int chunk = scratch_per_entry ? gemm_batch_chunk(scratch_per_entry, g.batch) : (g.batch < 65535 ? g.batch : 65535);
+  float* wa = nullptr;
+  float* wb = nullptr;
+  if (!g.a_lo) {
+    wa = scratch_alloc(chunk * a_elems * 4);
+    if (!wa) return false;
+  }
+  if (!g.b_lo) {
+    wb = scratch_alloc(chunk * b_elems * 4);
+    if (!wb) { scratch_free(wa); return false; }
+  }
   bool ok = true;
   for (int b0 = 0; ok && b0 < g.batch; b0 += chunk) {
     const int nb = (g.batch - b0) < chunk ? (g.batch - b0) : chunk;
     const float* a = g.a + b0 * a_elems;
     const float* b = g.b + b0 * b_elems;
-    const int64_t a4 = nb * a_elems / 4, b4 = nb * b_elems / 4;
-    split_lo_kernel<<<stream_grid(a4, 256, 4), 256, 0, ctx().stream>>>(reinterpret_cast<const float4*>(a),
-                                                                        reinterpret_cast<float4*>(wa), a4);
-    count_launch();
-    split_lo_kernel<<<stream_grid(b4, 256, 4), 256, 0, ctx().stream>>>(reinterpret_cast<const float4*>(b),
-                                                                        reinterpret_cast<float4*>(wb), b4);
-    count_launch();
-    ok = cuda_ok(cudaGetLastError(), "lo-plane split launch");
+    const float* a_lo = g.a_lo ? g.a_lo + b0 * a_elems : wa;
+    const float* b_lo = g.b_lo ? g.b_lo + b0 * b_elems : wb;
+    if (!g.a_lo) ok = split_lo_plane(a, wa, nb * a_elems);
+    if (ok && !g.b_lo) ok = split_lo_plane(b, wb, nb * b_elems);
     if (!ok) break;
     CUtensorMap maps[4];
     ok = make_direct_map(&maps[0], a, g.m, g.k, nb, !a_mn, BM, a_mn) &&
          make_direct_map(&maps[1], b, g.n, g.k, nb, !b_mn, BN, b_mn) &&
-         make_direct_map(&maps[2], wa, g.m, g.k, nb, !a_mn, BM, a_mn) &&
-         make_direct_map(&maps[3], wb, g.n, g.k, nb, !b_mn, BN, b_mn);
+         make_direct_map(&maps[2], a_lo, g.m, g.k, nb, !a_mn, BM, a_mn) &&
+         make_direct_map(&maps[3], b_lo, g.n, g.k, nb, !b_mn, BN, b_mn);
     if (!ok) break;
     TcParams p;
     p.a_blocked = a_mn;
@@ -896,6 +926,7 @@ static bool launch_lo_plane(const GemmArgs& g) {
     p.b_sliced = 0;
     p.b_box_rows = BN;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
+    p.c_lo = g.c_lo ? g.c_lo + (int64_t)b0 * g.m * g.n : nullptr;
     p.bias = g.bias;
     p.dact_y = g.dact_y ? g.dact_y + (int64_t)b0 * g.m * g.n : nullptr;
     p.dact = g.dact;
@@ -936,13 +967,19 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     return false;
   }
   read_options();
+  // Lo planes handed in by the caller (an earlier GEMM's epilogue wrote them, or they are reused across calls):
+  // the lo-plane route then needs no pre-pass at all, which beats every other route where it applies.
+  if ((g.a_lo || g.b_lo) && g_direct == 1 && lo_plane_eligible(g) && aligned16(g.a_lo) && aligned16(g.b_lo))
+    return launch_lo_plane(g);
+  // The narrow transposed route adds partial results in a pass of its own and cannot write C's low part.
+  const bool narrow_ok = g.c_lo == nullptr;
   // Measured choice.  Small / narrow problems: split in the kernel.  Up to 4096^2 outputs: lo planes (the
   // pre-pass moves 2/3 of the bytes of the padded one: 183 vs 300 us at 8192^3, 50 vs 80 us at 4096^3).
   // Beyond that the padded [hi | lo] planes win although their pre-pass is longer: the kernel runs
   // 3-5 % slower when its hi operand is the raw tensor (low mantissa bits that the tensor pipe ignores
   // still travel through shared memory; the kernel runs under the power cap).
   if (g_direct == 2 || (g_direct == 1 && prefer_direct(g))) {
-    if (g_direct == 1 && g_narrow) {
+    if (g_direct == 1 && g_narrow && narrow_ok) {
       const int slices = narrow_slices(g);
       if (slices > 0) return launch_narrow_transposed(g, slices);
     }
@@ -990,6 +1027,7 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     maps[3] = maps[1];
     TcParams p;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
+    p.c_lo = g.c_lo ? g.c_lo + (int64_t)b0 * g.m * g.n : nullptr;
     p.bias = g.bias;
     p.dact_y = g.dact_y ? g.dact_y + (int64_t)b0 * g.m * g.n : nullptr;
     p.dact = g.dact;

@@ -254,10 +254,17 @@ __device__ __forceinline__ float mse_grad(float p, float e, float fn, int bwd_ac
   return d;
 }
 
+// Low split part of a value (the lo plane a following tensor-core GEMM needs; same function as split_lo in
+// tc_common.cuh, repeated here because this file does not include the GEMM headers).
+__device__ __forceinline__ float lo_part(float x) {
+  const float d = __fsub_rn(x, __uint_as_float(__float_as_uint(x) & 0xFFFFE000u));
+  return __uint_as_float(__float_as_uint(d) + 0x1000u);
+}
+
 __global__ void __launch_bounds__(kRThreads) mse_stage1(const float* __restrict__ p, const float* __restrict__ t,
-                                                        float* __restrict__ dp, int64_t n, int64_t slab, float fn,
-                                                        float* __restrict__ partials, int vec, int bwd_act,
-                                                        Finish fin) {
+                                                        float* __restrict__ dp, float* __restrict__ dlo, int64_t n,
+                                                        int64_t slab, float fn, float* __restrict__ partials, int vec,
+                                                        int bwd_act, Finish fin) {
   const int64_t lo = (int64_t)blockIdx.x * slab;
   int64_t hi = lo + slab;
   if (hi > n) hi = n;
@@ -277,18 +284,27 @@ __global__ void __launch_bounds__(kRThreads) mse_stage1(const float* __restrict_
         d.x = mse_grad(a.x, e0, fn, bwd_act); d.y = mse_grad(a.y, e1, fn, bwd_act);
         d.z = mse_grad(a.z, e2, fn, bwd_act); d.w = mse_grad(a.w, e3, fn, bwd_act);
         __stcs(d4 + i, d);
+        if (dlo) __stcs(reinterpret_cast<float4*>(dlo) + i, make_float4(lo_part(d.x), lo_part(d.y), lo_part(d.z), lo_part(d.w)));
       }
     }
     for (int64_t i = (hi4 << 2) + threadIdx.x; i < hi; i += kRThreads) {
       float e = __fsub_rn(p[i], t[i]);
       acc = __fadd_rn(acc, __fmul_rn(e, e));
-      if (dp) dp[i] = mse_grad(p[i], e, fn, bwd_act);
+      if (dp) {
+        const float d = mse_grad(p[i], e, fn, bwd_act);
+        dp[i] = d;
+        if (dlo) dlo[i] = lo_part(d);
+      }
     }
   } else {
     for (int64_t i = lo + threadIdx.x; i < hi; i += kRThreads) {
       float e = __fsub_rn(p[i], t[i]);
       acc = __fadd_rn(acc, __fmul_rn(e, e));
-      if (dp) dp[i] = mse_grad(p[i], e, fn, bwd_act);
+      if (dp) {
+        const float d = mse_grad(p[i], e, fn, bwd_act);
+        dp[i] = d;
+        if (dlo) dlo[i] = lo_part(d);
+      }
     }
   }
   acc = block_reduce<SumRed>(acc);
@@ -676,8 +692,13 @@ int32_t cleave_cuda_colsum_into_f32(cleave_buf out, cleave_buf x, int32_t rows, 
 // loss_dev == nullptr: the loss is returned (the call waits for it).  Otherwise it is written to
 // that one-element device tensor, nothing is waited for, and 0 is returned on success.
 static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, const char* name,
-                      cleave_buf loss_dev = nullptr) {
+                      cleave_buf loss_dev = nullptr, cleave_buf dp_lo = nullptr) {
   ApiLock lock;
+  Buf* dl = nullptr;
+  if (dp_lo) {
+    dl = as_buf(dp_lo, name);
+    if (!dl) return NAN;
+  }
   Buf* lo = nullptr;
   if (loss_dev) {
     lo = as_buf(loss_dev, name);
@@ -694,6 +715,10 @@ static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, co
   if (dp) {
     d = as_buf(dp, name);
     if (!d) return NAN;
+  }
+  if (dl && (!d || dl->len != d->len || dl->ptr == d->ptr)) {
+    set_error(CLEAVE_CUDA_ERR_SHAPE, "%s: the lo plane needs the gradient output and its length", name);
+    return NAN;
   }
   if (a->len != b->len || (d && d->len != a->len)) {
     set_error(CLEAVE_CUDA_ERR_SHAPE, "%s: prediction, target and gradient tensors must have the same length", name);
@@ -714,12 +739,12 @@ static float mse_impl(cleave_buf p, cleave_buf t, cleave_buf dp, int bwd_act, co
   slab_for(n, max_ctas, &slab, &ctas);
   unsigned int* done = nullptr;
   cudaGetSymbolAddress((void**)&done, g_reduce_done);
-  int vec = (aligned16(a->ptr) && aligned16(b->ptr) && (!d || aligned16(d->ptr))) ? 1 : 0;
+  int vec = (aligned16(a->ptr) && aligned16(b->ptr) && (!d || aligned16(d->ptr)) && (!dl || aligned16(dl->ptr))) ? 1 : 0;
   const float fn = (float)(int32_t)n;
   cudaStream_t s = ctx().stream;
   float* out = lo ? lo->ptr : scalar_slot();
-  mse_stage1<<<ctas, kRThreads, 0, s>>>(a->ptr, b->ptr, d ? d->ptr : nullptr, n, slab, fn, partials, vec, bwd_act,
-                                        Finish{out, fn, 0, nullptr, done});
+  mse_stage1<<<ctas, kRThreads, 0, s>>>(a->ptr, b->ptr, d ? d->ptr : nullptr, dl ? dl->ptr : nullptr, n, slab, fn,
+                                        partials, vec, bwd_act, Finish{out, fn, 0, nullptr, done});
   count_launch();
   float r = NAN;
   if (cuda_ok(cudaGetLastError(), "mse launch")) r = lo ? 0.0f : wait_scalar();
@@ -737,6 +762,16 @@ int32_t cleave_cuda_mse_act_bwd_dev_f32(cleave_buf y, cleave_buf t, cleave_buf d
     return -set_error(CLEAVE_CUDA_ERR_ARG, "mse_act_bwd_dev: the gradient and loss output handles are required");
   }
   float r = mse_impl(y, t, dz, act, "mse_act_bwd_dev", loss_out);
+  return r == 0.0f ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
+}
+
+int32_t cleave_cuda_mse_act_bwd_lo_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act, cleave_buf loss_out,
+                                       cleave_buf dz_lo) {
+  if (!dz || !loss_out || !dz_lo) {
+    ApiLock lock;
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "mse_act_bwd_lo: the gradient, loss and lo-plane output handles are required");
+  }
+  float r = mse_impl(y, t, dz, act, "mse_act_bwd_lo", loss_out, dz_lo);
   return r == 0.0f ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
 }
 

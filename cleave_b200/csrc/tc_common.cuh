@@ -194,6 +194,8 @@ __device__ __forceinline__ float split_lo(float x) {
 
 struct TcParams {
   float* c;             // [batch][m][n]
+  float* c_lo = nullptr;   // [batch][m][n] or null: also store the low split part of every result (see split_lo),
+                           // i.e. the lo plane a following GEMM needs when C is one of its operands
   const float* bias;    // [n] or null
   const float* dact_y;  // [batch][m][n] or null: multiply the product by dact'(y) (backward form)
   int dact;
@@ -234,19 +236,84 @@ __device__ __forceinline__ void report(DeviceStatus* st, int code, int where, in
   __threadfence_system();
 }
 
+// Stores one drain warp's 32 x 128 block (one row per lane in `sum`) into the matrix `cmat` ([batch][m][n]).
+// Ragged tiles: every lane writes its own row.  Full tiles: a thread owns one ROW (what tcgen05.ld hands
+// out), but a store instruction is efficient when the warp covers whole 128-byte lines, so, 32 columns at a
+// time, every thread parks its 8 16-byte words in the warp-private shared tile `stage` (word j of row r at
+// slot j ^ (r & 7): conflict free both ways) and the warp then writes 4 rows x 128 bytes per instruction --
+// or, with `map_c` (tensor map over cmat {n, m, batch}, box 32 x 32, 128-byte swizzle, which is exactly the
+// layout of that shared tile), one lane hands each 32 x 32 block to TMA as a bulk tensor store.
+__device__ __forceinline__ void store_block(const float (&sum)[BN / 2], float* cmat, const TcParams& p, int b,
+                                            int tile_row0, int nb, int q, int half, int lane, bool vec_ok, float4* stage,
+                                            const CUtensorMap* map_c) {
+  const int row = tile_row0 + q * 32 + lane;
+  const int col0 = nb * BN + half * (BN / 2);
+  const bool full_tile = (tile_row0 + BM <= p.m) && (nb * BN + BN <= p.n);   // uniform over the warps of a tile
+  if (!(full_tile && vec_ok)) {
+    if (row < p.m) {
+      float* crow = cmat + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
+      if (vec_ok && col0 + BN / 2 <= p.n) {
+        float4* dst = reinterpret_cast<float4*>(crow);
+#pragma unroll
+        for (int j = 0; j < BN / 8; ++j) dst[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < BN / 2; ++j)
+          if (col0 + j < p.n) crow[j] = sum[j];
+      }
+    }
+    return;
+  }
+  if (map_c != nullptr) {
+    const uint32_t stage_addr = smem_u32(stage);
+#pragma unroll
+    for (int pass = 0; pass < BN / 64; ++pass) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        stage[lane * 8 + (j ^ (lane & 7))] = make_float4(sum[32 * pass + 4 * j], sum[32 * pass + 4 * j + 1],
+                                                         sum[32 * pass + 4 * j + 2], sum[32 * pass + 4 * j + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the copy engine
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile(
+            "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+            ::"l"(map_c), "r"(stage_addr), "r"(col0 + 32 * pass), "r"(tile_row0 + q * 32), "r"(b)
+            : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the tile may be overwritten
+      }
+      __syncwarp();
+    }
+    return;
+  }
+  float* cblock = cmat + ((int64_t)b * p.m + tile_row0 + q * 32) * (int64_t)p.n + col0;
+#pragma unroll
+  for (int pass = 0; pass < BN / 64; ++pass) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      stage[lane * 8 + (j ^ (lane & 7))] = make_float4(sum[32 * pass + 4 * j], sum[32 * pass + 4 * j + 1],
+                                                       sum[32 * pass + 4 * j + 2], sum[32 * pass + 4 * j + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = it * 4 + (lane >> 3), slot = lane & 7;
+      const float4 v = stage[r * 8 + (slot ^ (r & 7))];
+      *reinterpret_cast<float4*>(cblock + (int64_t)r * p.n + 32 * pass + 4 * slot) = v;
+    }
+    __syncwarp();
+  }
+}
+
 // Epilogue of one drain warp: its 32 rows x 128 columns of a tile (rows tile_row0 + 32q .., columns
-// nb*BN + 128*half ..), one row per lane in `sum`: + bias[col], activation, store to C.
-// `stage`: this warp's 4 KiB of shared memory for the coalesced store.
-// `map_c` (may be null): tensor map over C {n, m, batch}, box 32 x 32, 128-byte swizzle; with it a full tile
-// leaves through TMA stores issued by one lane per warp instead of the warp's own loads and stores.
+// nb*BN + 128*half ..), one row per lane in `sum`: + bias[col], activation or activation derivative, store to C
+// (and, when p.c_lo is set, the low split part of the same values to that plane).
+// `stage`: this warp's 4 KiB of shared memory for the coalesced store; `map_c`: see store_block.
 __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcParams& p, int b, int tile_row0, int nb,
                                               int q, int half, int lane, bool vec_ok, float4* stage,
                                               const CUtensorMap* map_c = nullptr) {
   const int row = tile_row0 + q * 32 + lane;
   const int col0 = nb * BN + half * (BN / 2);
-  const bool full_tile = (tile_row0 + BM <= p.m) && (nb * BN + BN <= p.n);   // uniform over the warps of a tile
   if (row < p.m) {
-    float* crow = p.c + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
     if (p.bias != nullptr) {
       if (vec_ok && col0 + BN / 2 <= p.n && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) {
         const float4* b4 = reinterpret_cast<const float4*>(p.bias + col0);
@@ -303,64 +370,14 @@ __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcPara
       }
 #undef CLEAVE_DACT_LOOP
     }
-    if (!(full_tile && vec_ok)) {
-      if (vec_ok && col0 + BN / 2 <= p.n) {
-        float4* dst = reinterpret_cast<float4*>(crow);
-#pragma unroll
-        for (int j = 0; j < BN / 8; ++j) dst[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < BN / 2; ++j)
-          if (col0 + j < p.n) crow[j] = sum[j];
-      }
-    }
   }
-  if (full_tile && vec_ok) {
-    // Coalesced store of the warp's 32 x 128 block.  A thread owns one ROW (what tcgen05.ld
-    // hands out), but a store instruction is efficient when the warp covers whole 128-byte
-    // lines.  So, 32 columns at a time, every thread parks its 8 16-byte words in a
-    // warp-private shared tile (word j of row r at slot j ^ (r & 7): conflict free both ways)
-    // and the warp then writes 4 rows x 128 bytes per instruction.
-    if (map_c != nullptr) {
-      // The shared tile (word j of row r at slot j ^ (r & 7), rows of 128 bytes, 1024-byte aligned) is exactly
-      // TMA's 128-byte swizzle, so each 32 x 32 block goes out as one bulk tensor store.
-      const uint32_t stage_addr = smem_u32(stage);
+  store_block(sum, p.c, p, b, tile_row0, nb, q, half, lane, vec_ok, stage, map_c);
+  if (p.c_lo != nullptr) {
+    // the same block once more, as the low part of the split-precision representation of what was just stored
 #pragma unroll
-      for (int pass = 0; pass < BN / 64; ++pass) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          stage[lane * 8 + (j ^ (lane & 7))] = make_float4(sum[32 * pass + 4 * j], sum[32 * pass + 4 * j + 1],
-                                                           sum[32 * pass + 4 * j + 2], sum[32 * pass + 4 * j + 3]);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the copy engine
-        __syncwarp();
-        if (lane == 0) {
-          asm volatile(
-              "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-              ::"l"(map_c), "r"(stage_addr), "r"(col0 + 32 * pass), "r"(tile_row0 + q * 32), "r"(b)
-              : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the tile may be overwritten
-        }
-        __syncwarp();
-      }
-      return;
-    }
-    float* cblock = p.c + ((int64_t)b * p.m + tile_row0 + q * 32) * (int64_t)p.n + col0;
-#pragma unroll
-    for (int pass = 0; pass < BN / 64; ++pass) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        stage[lane * 8 + (j ^ (lane & 7))] = make_float4(sum[32 * pass + 4 * j], sum[32 * pass + 4 * j + 1],
-                                                         sum[32 * pass + 4 * j + 2], sum[32 * pass + 4 * j + 3]);
-      __syncwarp();
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int r = it * 4 + (lane >> 3), slot = lane & 7;
-        const float4 v = stage[r * 8 + (slot ^ (r & 7))];
-        *reinterpret_cast<float4*>(cblock + (int64_t)r * p.n + 32 * pass + 4 * slot) = v;
-      }
-      __syncwarp();
-    }
+    for (int j = 0; j < BN / 2; ++j) sum[j] = split_lo(sum[j]);
+    store_block(sum, p.c_lo, p, b, tile_row0, nb, q, half, lane, vec_ok && ((reinterpret_cast<uintptr_t>(p.c_lo) & 15u) == 0),
+                stage, nullptr);
   }
 }
 

@@ -147,13 +147,14 @@ class FusedDataParallel:
         self.params = Tensor.from_device_ptr(self._bufs[0].data_ptr(), n_params)
         self.grads = Tensor.from_device_ptr(self._bufs[1].data_ptr(), n_params)
         self.net = make_net(self.params, self.grads)
-        # Buckets in the order the backward pass completes them: [W2 | b2] first, then [W1 | b1].
+        # Buckets in the replica's numbering: 0 = [W2 | b2], 1 = [W1 | b1]; the backward pass completes bucket 1 first.
         o = [int(x) for x in self.net._offsets]
         self._buckets = [(o[2], o[4] - o[2]), (o[0], o[2] - o[0])]
         if any(off % 4 or n % 4 for off, n in self._buckets):
             self._buckets = [(0, n_params)]          # ragged layer sizes: exchange everything at the end
-        # Each bucket has its own signal words (32 apart) and epoch counter; the first bucket is
-        # exchanged on a side stream while the backward pass continues on the main one.
+        # Each bucket has its own signal words (32 apart), epoch counter and completion event.  Exchanges run
+        # on a side stream: layer 1's beside the rest of the backward pass, layer 2's beside the next step's
+        # first forward product; the main stream waits for a layer's exchange only where it next reads that layer.
         self._flag_tables = [arr(*[int(f.buffer_ptrs[r]) + 128 * b for r in range(self.world)])
                              for b in range(len(self._buckets))]
         self._epochs = [1] * len(self._buckets)
@@ -162,8 +163,9 @@ class FusedDataParallel:
         if (lib().cleave_cuda_get_stream() or 0) != self._main.cuda_stream:
             raise RuntimeError("the library must run on torch's current stream: call dp.use_torch_stream() first")
         self._side = torch.cuda.Stream()
-        self._ready = torch.cuda.Event()
-        self._done = torch.cuda.Event()
+        self._ready = [torch.cuda.Event() for _ in self._buckets]
+        self._done = [torch.cuda.Event() for _ in self._buckets]
+        self._in_flight = [False] * len(self._buckets)
         self._torch = torch
 
     def _exchange(self, b: int, lr: float, stream) -> None:
@@ -176,23 +178,47 @@ class FusedDataParallel:
             raise_last_error("dp_sgd_allreduce")
         self._epochs[b] += 2
 
+    def _settle(self, b: int) -> None:
+        """The main stream continues only after bucket b's exchange in flight, if any."""
+        if self._in_flight[b]:
+            self._main.wait_event(self._done[b])
+            self._in_flight[b] = False
+
+    def flush(self) -> None:
+        """Orders the main stream after every exchange still in flight (call before reading the parameters,
+        timing the end of a run, or switching streams)."""
+        for b in range(len(self._buckets)):
+            self._settle(b)
+
     def step(self, X, T, lr: float, loss_out=None):
-        """``loss_out``: optional one-element device tensor; with it the step never waits for the GPU."""
-        early = len(self._buckets) == 2
+        """``loss_out``: optional one-element device tensor; with it the step never waits for the GPU.
+        When the step returns, the exchange of the last bucket(s) may still be running on the side stream; the
+        next ``step`` (or ``flush``) orders itself after it."""
+        split = len(self._buckets) == 2
 
-        def on_ready(i: int) -> None:
-            if i == 0 and early:
-                # [dW2 | db2] are final and W2 has been consumed: exchange them beside the rest of the pass
-                self._ready.record(self._main)
-                self._side.wait_event(self._ready)
-                self._exchange(0, lr, self._side)
-                self._done.record(self._side)
+        def before_layer(i: int) -> None:
+            # layer i's weights are about to be read: the previous step's exchange of them must have landed
+            if split:
+                self._settle(2 - i)       # layer 1 -> bucket 1, layer 2 -> bucket 0
+            elif i == 1:
+                self._settle(0)
 
-        loss = self.net.forward_backward(X, T, on_grads_ready=on_ready, loss_out=loss_out)
-        self._exchange(len(self._buckets) - 1, lr, self._main)
-        if early:
-            self._main.wait_event(self._done)
+        def on_ready(b: int) -> None:
+            if not split:
+                if b == 0:                # everything is final
+                    self._launch(0, lr)
+                return
+            self._launch(b, lr)
+
+        loss = self.net.forward_backward(X, T, on_grads_ready=on_ready, loss_out=loss_out, before_layer=before_layer)
         return loss
+
+    def _launch(self, b: int, lr: float) -> None:
+        self._ready[b].record(self._main)
+        self._side.wait_event(self._ready[b])
+        self._exchange(b, lr, self._side)
+        self._done[b].record(self._side)
+        self._in_flight[b] = True
 
 
 class MLP2Replica:
@@ -201,7 +227,7 @@ class MLP2Replica:
     def __init__(self, net):
         self.net = net
         o = [int(x) for x in net._offsets]
-        # backward completes [W2 | b2] first, then [W1 | b1]
+        # bucket 0 = [W2 | b2], bucket 1 = [W1 | b1]; the backward pass completes bucket 1 first
         self._buckets = [as_torch(net.grads, o[2], o[4] - o[2]), as_torch(net.grads, o[0], o[2] - o[0])]
 
     def grad_buckets(self):

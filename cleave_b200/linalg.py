@@ -188,15 +188,24 @@ GEMM_AUTO, GEMM_EXACT, GEMM_3XTF32 = 0, 1, 2
 ACT = {"identity": 0, "relu": 1, "sigmoid": 2, "tanh": 3}
 
 
+def split_lo(x: Tensor) -> Tensor:
+    """The lo plane of ``x`` (``cleave_cuda_split_lo_f32``): what the tensor-core path needs beside ``x`` itself."""
+    return Tensor._wrap(lib().cleave_cuda_split_lo_f32(x._h), x.dims, "split_lo")
+
+
 def gemm_into(c: Tensor, a: Tensor, b: Tensor, *, trans_a=False, trans_b=False, algo=GEMM_AUTO,
               bias: Tensor | None = None, act: str = "identity", dact_of: Tensor | None = None,
-              dact: str = "identity") -> Tensor:
+              dact: str = "identity", a_lo: Tensor | None = None, b_lo: Tensor | None = None,
+              c_lo: Tensor | None = None) -> Tensor:
     """General product written into ``c`` (``cleave_cuda_gemm_ex_f32``).  Shapes follow the stored
     layouts: a is [m,k] ([k,m] if trans_a), b is [k,n] ([n,k] if trans_b); a leading batch
     dimension on all three runs independent products.
 
     ``dact_of=y, dact=name`` selects the backward form ``c = name'(y) * (a @ b)`` elementwise, the
-    derivative taken from the activation's forward output ``y`` (``cleave_cuda_gemm_dact_f32``)."""
+    derivative taken from the activation's forward output ``y`` (``cleave_cuda_gemm_dact_f32``).
+
+    ``a_lo`` / ``b_lo``: lo planes of the operands the caller already holds; ``c_lo``: tensor that receives the lo
+    plane of the result (``cleave_cuda_gemm_fused_f32``), so a chain of products runs without operand pre-passes."""
     batched = len(c.dims) == 3
     batch = c.dims[0] if batched else 1
     ad, bd, cd = (t.dims[1:] if batched else t.dims for t in (a, b, c))
@@ -209,6 +218,17 @@ def gemm_into(c: Tensor, a: Tensor, b: Tensor, *, trans_a=False, trans_b=False, 
             raise TypeError("gemm_into: the backward form takes no bias and no forward activation")
         if dact_of.dims != c.dims:
             raise TypeError(f"gemm_into: dact_of has shape {dact_of.dims}, the product {c.dims}")
+    if a_lo is not None or b_lo is not None or c_lo is not None:
+        for t, lo, what in ((a, a_lo, "a_lo"), (b, b_lo, "b_lo"), (c, c_lo, "c_lo")):
+            if lo is not None and lo.numel != t.numel:
+                raise TypeError(f"gemm_into: {what} has {lo.numel} elements, its tensor {t.numel}")
+        h = lambda t: t._h if t is not None else None  # noqa: E731
+        r = lib().cleave_cuda_gemm_fused_f32(c._h, a._h, b._h, batch, m, n, k, int(trans_a), int(trans_b), algo, h(bias),
+                                             ACT[act], h(dact_of), ACT[dact], h(a_lo), h(b_lo), h(c_lo))
+        if r != 0:
+            raise_last_error("gemm_into")
+        return c
+    if dact_of is not None:
         r = lib().cleave_cuda_gemm_dact_f32(c._h, a._h, b._h, batch, m, n, k, int(trans_a), int(trans_b), algo,
                                             dact_of._h, ACT[dact])
         if r != 0:

@@ -105,6 +105,17 @@ def mse_act_bwd(y: Tensor, target: Tensor, act: str, loss_out: Tensor | None = N
     return loss, dz
 
 
+def mse_act_bwd_lo(y: Tensor, target: Tensor, act: str, loss_out: Tensor):
+    """``mse_act_bwd`` with the loss left in ``loss_out`` that also returns the lo plane of the gradient
+    (``cleave_cuda_mse_act_bwd_lo_f32``): ``(dz, dz_lo)``."""
+    if y.dims != target.dims:
+        raise TypeError(f"mse_act_bwd_lo: mismatched types {y!r} and {target!r}")
+    dz, dz_lo = Tensor.empty(*y.dims), Tensor.empty(*y.dims)
+    if lib().cleave_cuda_mse_act_bwd_lo_f32(y._h, target._h, dz._h, ACT[act], loss_out._h, dz_lo._h) != 0:
+        raise_last_error("mse_act_bwd_lo")
+    return dz, dz_lo
+
+
 def sgd_step(w: Tensor, g: Tensor, lr: float, gscale: float = 1.0) -> None:
     """``w = w - lr * (gscale * g)`` in place (examples/xor.cleave:67-70)."""
     if w.dims != g.dims:

@@ -209,6 +209,24 @@ int32_t cleave_cuda_gemm_dact_f32(cleave_buf c, cleave_buf a, cleave_buf b, int3
                                   int32_t n, int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo,
                                   cleave_buf y, int32_t act);
 
+/* Chained form for graphs in which one product feeds the next (the lowered perceptron: H = act(X W1 + b1) feeds
+ * H W2 and H^T dZ2; dZ1 feeds X^T dZ1).  The tensor-core path multiplies x as hi + lo; with the lo parts handed
+ * over between calls no operand pre-pass runs at all:
+ *   a_lo / b_lo  (may be NULL) lo planes of the operands, same shape as a / b, obtained from an earlier call's
+ *                c_lo, from cleave_cuda_split_lo_f32, or from cleave_cuda_mse_act_bwd_lo_f32; a plane must belong
+ *                to the CURRENT contents of its tensor -- the library cannot check that;
+ *   c_lo         (may be NULL) receives the lo plane of the values stored to c, written by the same epilogue.
+ * bias + act, or y + dact (the backward form), as in the two entry points above; not both.  The result is
+ * bit-identical to cleave_cuda_gemm_ex_f32 / cleave_cuda_gemm_dact_f32 on the same tensor-core route.
+ * No counterpart in the reference (its matmul is one linalg op, stdlib/linalg/matrix.cleave:59-60). */
+int32_t cleave_cuda_gemm_fused_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n,
+                                   int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo, cleave_buf bias,
+                                   int32_t act, cleave_buf y, int32_t dact, cleave_buf a_lo, cleave_buf b_lo,
+                                   cleave_buf c_lo);
+/* The lo plane of a tensor in one streaming pass: lo[i] = tf32-rounded (x[i] - x[i] with its 13 low mantissa
+ * bits cleared), the part of x the tensor pipe drops when it reads x as tf32. */
+cleave_buf cleave_cuda_split_lo_f32(cleave_buf x);
+
 /* ------------------------------------------------------------------ compositions the programs spell out
  * bias add: a rows x cols tensor plus a tensor whose rows all equal `bias`
  * (arith.addf does not broadcast: stdlib/nn/nn.cleave:72-74), then an activation. */
@@ -223,6 +241,9 @@ float cleave_cuda_mse_act_bwd_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int
 /* Same, but the loss goes to the one-element tensor loss_out and the call does not wait: a
  * training loop can queue many steps and read the loss only when it wants to log it. */
 int32_t cleave_cuda_mse_act_bwd_dev_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act, cleave_buf loss_out);
+/* cleave_cuda_mse_act_bwd_dev_f32 that also writes the lo plane of dz (see cleave_cuda_gemm_fused_f32). */
+int32_t cleave_cuda_mse_act_bwd_lo_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int32_t act, cleave_buf loss_out,
+                                       cleave_buf dz_lo);
 /* w = w - lr * (gscale * g) in place (examples/xor.cleave:67-70); gscale folds the 1/G of a
  * gradient mean over G data-parallel ranks into the same pass. */
 int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale);

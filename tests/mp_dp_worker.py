@@ -45,6 +45,8 @@ def main():
         for step in range(steps):
             X, T = dp.dp_batch_inputs(gb, rank, world, d_in, d_out, step)
             trainer.step(linalg.Tensor(X), linalg.Tensor(T), lr)
+        if hasattr(trainer, "flush"):
+            trainer.flush()          # the last exchanges run on a side stream
         cb.sync()
         mine = dp.as_torch(net.params).clone()
         gathered = [torch.empty_like(mine) for _ in range(world)]
