@@ -106,6 +106,15 @@ SIGNATURES = {
     "cleave_cuda_mean_f64": (f64, [c_buf]),
     "cleave_cuda_max_f64": (f64, [c_buf]),
     "cleave_cuda_gemm_f64": (c_buf, [c_buf, c_buf, i32, i32, i32]),
+    "cleave_cuda_gemm_nt_f64": (c_buf, [c_buf, c_buf, i32, i32, i32]),
+    "cleave_cuda_gemm_tn_f64": (c_buf, [c_buf, c_buf, i32, i32, i32]),
+    "cleave_cuda_gemm_batched_f64": (c_buf, [c_buf, c_buf, i32, i32, i32, i32]),
+    "cleave_cuda_tanh_bwd_f64": (c_buf, [c_buf, c_buf]),
+    "cleave_cuda_sigmoid_bwd_f64": (c_buf, [c_buf, c_buf]),
+    "cleave_cuda_relu_bwd_f64": (c_buf, [c_buf, c_buf]),
+    "cleave_cuda_colsum_f64": (c_buf, [c_buf, i32, i32]),
+    "cleave_cuda_mse_f64": (f64, [c_buf, c_buf, c_buf]),
+    "cleave_cuda_sgd_f64": (i32, [c_buf, c_buf, f64, f64]),
     "cleave_cuda_dp_sgd_allreduce_f32": (i32, [ctypes.POINTER(ctypes.c_void_p)] * 3 + [ctypes.c_void_p, ctypes.c_void_p,
                                                 i64, i64, i32, i32, f32, ctypes.c_uint32, ctypes.c_void_p]),
     "cleave_cuda_linreg_step_f32": (f32, [c_buf, c_buf, c_buf, c_buf, c_buf, i32, i32]),

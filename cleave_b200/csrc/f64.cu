@@ -25,6 +25,18 @@ struct DRelu { __device__ double operator()(double x) const { return x != x ? x 
 struct DExp { __device__ double operator()(double x) const { return exp(x); } };
 struct DSigmoid { __device__ double operator()(double x) const { return __ddiv_rn(1.0, __dadd_rn(1.0, exp(-x))); } };
 struct DTanh { __device__ double operator()(double x) const { return tanh(x); } };
+// Derivative rules times the upstream factor, each step rounded like the separate arith ops
+// (stdlib/num/num.cleave:222-223; sigmoid through the chain of :123-136): y = forward output, x = forward input.
+struct DTanhBwd { __device__ double operator()(double y, double g) const { return __dmul_rn(__dsub_rn(1.0, __dmul_rn(y, y)), g); } };
+struct DSigmoidBwd { __device__ double operator()(double y, double g) const { return __dmul_rn(__dmul_rn(y, __dsub_rn(1.0, y)), g); } };
+struct DReluBwd { __device__ double operator()(double x, double g) const { return x > 0.0 ? g : 0.0; } };
+struct DSgd {   // w - lr * (gscale * g)
+  double lr, gscale;
+  __device__ double operator()(double w, double g) const {
+    const double gg = gscale == 1.0 ? g : __dmul_rn(gscale, g);
+    return __dsub_rn(w, __dmul_rn(lr, gg));
+  }
+};
 
 template <class Op>
 __global__ void __launch_bounds__(kT, kCtas) unary_f64_kernel(const double* __restrict__ a, double* __restrict__ o,
@@ -163,10 +175,14 @@ __global__ void __launch_bounds__(kT) reduce_f64_kernel(const double* __restrict
 // ---- exact matmul ----------------------------------------------------------------------------------
 constexpr int kDM = 64, kDN = 64, kDK = 16;
 
+// A is [m,k] (or [k,m] when ta), B is [k,n] (or [n,k] when tb); blockIdx.z walks the batch.
 __global__ void __launch_bounds__(256) gemm_exact_f64_kernel(const double* __restrict__ A, const double* __restrict__ B,
-                                                             double* __restrict__ C, int m, int n, int k) {
+                                                             double* __restrict__ C, int m, int n, int k, int ta, int tb) {
   __shared__ double As[kDK][kDM + 2];
   __shared__ double Bs[kDK][kDN + 2];
+  A += (int64_t)blockIdx.z * m * k;
+  B += (int64_t)blockIdx.z * k * n;
+  C += (int64_t)blockIdx.z * m * n;
   const int m0 = blockIdx.y * kDM, n0 = blockIdx.x * kDN;
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
   double acc[4][4];
@@ -178,12 +194,12 @@ __global__ void __launch_bounds__(256) gemm_exact_f64_kernel(const double* __res
     for (int e = threadIdx.x; e < kDM * kDK; e += 256) {
       const int c = e % kDK, r = e / kDK;
       const int gm = m0 + r, gk = k0 + c;
-      As[c][r] = (gm < m && gk < k) ? A[(int64_t)gm * k + gk] : 0.0;
+      As[c][r] = (gm < m && gk < k) ? (ta ? A[(int64_t)gk * m + gm] : A[(int64_t)gm * k + gk]) : 0.0;
     }
     for (int e = threadIdx.x; e < kDN * kDK; e += 256) {
       const int c = e % kDN, r = e / kDN;
       const int gk = k0 + r, gn = n0 + c;
-      Bs[r][c] = (gk < k && gn < n) ? B[(int64_t)gk * n + gn] : 0.0;
+      Bs[r][c] = (gk < k && gn < n) ? (tb ? B[(int64_t)gn * k + gk] : B[(int64_t)gk * n + gn]) : 0.0;
     }
     __syncthreads();
     const int kmax = (k - k0) < kDK ? (k - k0) : kDK;
@@ -212,6 +228,39 @@ __global__ void __launch_bounds__(256) gemm_exact_f64_kernel(const double* __res
   }
 }
 
+// ---- column sums and the squared-error loss ---------------------------------------------------------------
+// Column sums in two deterministic stages: stage 1 adds the rows of one split (rows r0, r0 + 1, ... in order)
+// for one column per thread, stage 2 adds the splits in order.
+__global__ void __launch_bounds__(256) colsum_f64_stage1(const double* __restrict__ x, int rows, int cols, int rows_per_split,
+                                                         double* __restrict__ partials) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const int r0 = blockIdx.y * rows_per_split;
+  const int r1 = (r0 + rows_per_split) < rows ? (r0 + rows_per_split) : rows;
+  double acc = 0.0;
+  for (int r = r0; r < r1; ++r) acc = __dadd_rn(acc, x[(int64_t)r * cols + c]);
+  partials[(int64_t)blockIdx.y * cols + c] = acc;
+}
+__global__ void __launch_bounds__(256) colsum_f64_stage2(const double* __restrict__ partials, int splits, int cols,
+                                                         double* __restrict__ out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  double acc = partials[c];
+  for (int sp = 1; sp < splits; ++sp) acc = __dadd_rn(acc, partials[(int64_t)sp * cols + c]);
+  out[c] = acc;
+}
+// e = p - t; sq = e * e; dp = (2 e) / n  -- the separate arith ops of the lowered program, one pass
+__global__ void __launch_bounds__(kT, kCtas) mse_f64_kernel(const double* __restrict__ p, const double* __restrict__ t,
+                                                            double* __restrict__ sq, double* __restrict__ dp, int64_t n,
+                                                            double fn) {
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nthreads) {
+    const double e = __dsub_rn(p[i], t[i]);
+    sq[i] = __dmul_rn(e, e);
+    if (dp) dp[i] = __ddiv_rn(__dmul_rn(2.0, e), fn);
+  }
+}
+
 // ---- host side --------------------------------------------------------------------------------------
 static inline double* dp(Buf* b) { return reinterpret_cast<double*>(b->ptr); }
 
@@ -225,6 +274,7 @@ static cleave_buf unary_f64_api(cleave_buf x, const char* name, Op op) {
   ApiLock lock;
   Buf* a = as_buf(x, name, DT_F64);
   if (!a) return nullptr;
+  Trace tr(name, "f64 n=%lld", (long long)a->len);
   Buf* o = new_buf(a->len, DT_F64);
   if (!o) return nullptr;
   const bool vec = aligned16(a->ptr) && aligned16(o->ptr) && a->len >= 2;
@@ -245,6 +295,7 @@ static cleave_buf binary_f64_api(cleave_buf x, cleave_buf y, const char* name, O
               name, (long long)a->len, (long long)b->len);
     return nullptr;
   }
+  Trace tr(name, "f64 n=%lld", (long long)a->len);
   Buf* o = new_buf(a->len, DT_F64);
   if (!o) return nullptr;
   const bool vec = aligned16(a->ptr) && aligned16(b->ptr) && aligned16(o->ptr) && a->len >= 2;
@@ -255,11 +306,19 @@ static cleave_buf binary_f64_api(cleave_buf x, cleave_buf y, const char* name, O
 }
 
 template <class R>
+static double reduce_f64_ptr(const double* data, int64_t n, double divisor_or_zero_for_len, int mode);
+
+template <class R>
 static double reduce_f64(cleave_buf v, const char* name, double divisor_or_zero_for_len, int mode) {
   ApiLock lock;
   Buf* a = as_buf(v, name, DT_F64);
   if (!a) return NAN;
-  const int64_t n = a->len;
+  Trace tr(name, "f64 n=%lld", (long long)a->len);
+  return reduce_f64_ptr<R>(dp(a), a->len, divisor_or_zero_for_len, mode);
+}
+
+template <class R>
+static double reduce_f64_ptr(const double* data, int64_t n, double divisor_or_zero_for_len, int mode) {
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, reduce_f64_kernel<R>, kT, 0) != cudaSuccess || per_sm < 1) {
     cudaGetLastError();
@@ -276,7 +335,7 @@ static double reduce_f64(cleave_buf v, const char* name, double divisor_or_zero_
   unsigned int* done = nullptr;
   cudaGetSymbolAddress((void**)&done, g_reduce_f64_done);
   const double divisor = divisor_or_zero_for_len == 0.0 ? (double)(int32_t)n : divisor_or_zero_for_len;
-  reduce_f64_kernel<R><<<ctas, kT, 0, ctx().stream>>>(dp(a), n, slab, partials, scalar_slot_f64(), divisor, mode, done);
+  reduce_f64_kernel<R><<<ctas, kT, 0, ctx().stream>>>(data, n, slab, partials, scalar_slot_f64(), divisor, mode, done);
   count_launch();
   double r = NAN;
   if (cuda_ok(cudaGetLastError(), "f64 reduction launch")) r = wait_scalar_f64();
@@ -368,22 +427,125 @@ double cleave_cuda_sum_f64(cleave_buf v) { return reduce_f64<DSum>(v, "sum", 1.0
 double cleave_cuda_mean_f64(cleave_buf v) { return reduce_f64<DSum>(v, "mean", 0.0, 0); }
 double cleave_cuda_max_f64(cleave_buf v) { return reduce_f64<DMax>(v, "max_of", 1.0, 1); }
 
-cleave_buf cleave_cuda_gemm_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k) {
+static int gemm_f64_into(Buf* C, Buf* A, Buf* B, int batch, int m, int n, int k, int ta, int tb) {
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0)
+    return set_error(CLEAVE_CUDA_ERR_ARG, "gemm_f64: batch, m, n, k must be positive (got %d, %d, %d, %d)", batch, m, n, k);
+  if (A->len != (int64_t)batch * m * k || B->len != (int64_t)batch * k * n || C->len != (int64_t)batch * m * n)
+    return set_error(CLEAVE_CUDA_ERR_SHAPE,
+                     "gemm_f64: operand lengths %lld, %lld, %lld do not match batch %d of [%d x %d] * [%d x %d]",
+                     (long long)A->len, (long long)B->len, (long long)C->len, batch, m, k, k, n);
+  if (C->ptr == A->ptr || C->ptr == B->ptr)
+    return set_error(CLEAVE_CUDA_ERR_ARG, "gemm_f64: the output must not alias an operand");
+  if (batch > 65535 || ceil_div(m, kDM) > 65535)
+    return set_error(CLEAVE_CUDA_ERR_UNSUPPORTED, "gemm_f64: batch %d / %d rows exceed the grid range", batch, m);
+  Trace tr("gemm", "f64 batch=%d m=%d n=%d k=%d ta=%d tb=%d", batch, m, n, k, ta, tb);
+  gemm_exact_f64_kernel<<<dim3(ceil_div(n, kDN), ceil_div(m, kDM), batch), 256, 0, ctx().stream>>>(dp(A), dp(B), dp(C), m, n,
+                                                                                                  k, ta ? 1 : 0, tb ? 1 : 0);
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "f64 GEMM launch") ? CLEAVE_CUDA_OK : cleave_cuda_last_error();
+}
+
+static cleave_buf gemm_f64_new(cleave_buf a, cleave_buf b, int batch, int m, int n, int k, int ta, int tb) {
   ApiLock lock;
   Buf* A = as_buf(a, "gemm_f64", DT_F64);
   Buf* B = as_buf(b, "gemm_f64", DT_F64);
   if (!A || !B) return nullptr;
-  if (m <= 0 || n <= 0 || k <= 0 || A->len != (int64_t)m * k || B->len != (int64_t)k * n) {
-    set_error(CLEAVE_CUDA_ERR_SHAPE, "gemm_f64: operand lengths %lld, %lld do not match [%d x %d] * [%d x %d]",
-              (long long)A->len, (long long)B->len, m, k, k, n);
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "gemm_f64: batch, m, n, k must be positive (got %d, %d, %d, %d)", batch, m, n, k);
     return nullptr;
   }
-  Buf* C = new_buf((int64_t)m * n, DT_F64);
+  Buf* C = new_buf((int64_t)batch * m * n, DT_F64);
   if (!C) return nullptr;
-  gemm_exact_f64_kernel<<<dim3(ceil_div(n, kDN), ceil_div(m, kDM)), 256, 0, ctx().stream>>>(dp(A), dp(B), dp(C), m, n, k);
-  count_launch();
-  if (!cuda_ok(cudaGetLastError(), "f64 GEMM launch")) { release_buf(C); return nullptr; }
+  if (gemm_f64_into(C, A, B, batch, m, n, k, ta, tb) != CLEAVE_CUDA_OK) { release_buf(C); return nullptr; }
   return (cleave_buf)C;
+}
+
+cleave_buf cleave_cuda_gemm_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k) {
+  return gemm_f64_new(a, b, 1, m, n, k, 0, 0);
+}
+cleave_buf cleave_cuda_gemm_nt_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k) {
+  return gemm_f64_new(a, b, 1, m, n, k, 0, 1);
+}
+cleave_buf cleave_cuda_gemm_tn_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k) {
+  return gemm_f64_new(a, b, 1, m, n, k, 1, 0);
+}
+cleave_buf cleave_cuda_gemm_batched_f64(cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n, int32_t k) {
+  return gemm_f64_new(a, b, batch, m, n, k, 0, 0);
+}
+
+cleave_buf cleave_cuda_tanh_bwd_f64(cleave_buf y, cleave_buf g) { return binary_f64_api(y, g, "tanh_bwd", DTanhBwd{}); }
+cleave_buf cleave_cuda_sigmoid_bwd_f64(cleave_buf y, cleave_buf g) {
+  return binary_f64_api(y, g, "sigmoid_bwd", DSigmoidBwd{});
+}
+cleave_buf cleave_cuda_relu_bwd_f64(cleave_buf x, cleave_buf g) { return binary_f64_api(x, g, "relu_bwd", DReluBwd{}); }
+
+int32_t cleave_cuda_sgd_f64(cleave_buf w, cleave_buf g, double lr, double gscale) {
+  ApiLock lock;
+  Buf* a = as_buf(w, "sgd", DT_F64);
+  Buf* b = as_buf(g, "sgd", DT_F64);
+  if (!a || !b) return -cleave_cuda_last_error();
+  if (a->len != b->len)
+    return -set_error(CLEAVE_CUDA_ERR_SHAPE, "sgd: weights have %lld elements, gradient %lld", (long long)a->len,
+                      (long long)b->len);
+  Trace tr("sgd", "f64 n=%lld", (long long)a->len);
+  const bool vec = aligned16(a->ptr) && aligned16(b->ptr) && a->len >= 2;
+  binary_f64_kernel<DSgd><<<grid_f64(a->len, vec), kT, 0, ctx().stream>>>(dp(a), dp(b), dp(a), a->len, vec ? 1 : 0,
+                                                                          DSgd{lr, gscale});
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "f64 sgd launch") ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
+}
+
+cleave_buf cleave_cuda_colsum_f64(cleave_buf x, int32_t rows, int32_t cols) {
+  ApiLock lock;
+  Buf* a = as_buf(x, "colsum", DT_F64);
+  if (!a) return nullptr;
+  if (rows <= 0 || cols <= 0 || a->len != (int64_t)rows * cols) {
+    set_error(CLEAVE_CUDA_ERR_SHAPE, "colsum: tensor has %lld elements, not %d x %d", (long long)a->len, rows, cols);
+    return nullptr;
+  }
+  Trace tr("colsum", "f64 rows=%d cols=%d", rows, cols);
+  int splits = ceil_div(rows, 64);
+  if (splits > 64) splits = 64;
+  const int rows_per_split = ceil_div(rows, splits);
+  splits = ceil_div(rows, rows_per_split);
+  double* partials = reinterpret_cast<double*>(scratch_alloc((int64_t)splits * cols * sizeof(double)));
+  if (!partials) return nullptr;
+  Buf* o = new_buf(cols, DT_F64);
+  if (!o) { scratch_free(reinterpret_cast<float*>(partials)); return nullptr; }
+  colsum_f64_stage1<<<dim3(ceil_div(cols, 256), splits), 256, 0, ctx().stream>>>(dp(a), rows, cols, rows_per_split, partials);
+  colsum_f64_stage2<<<ceil_div(cols, 256), 256, 0, ctx().stream>>>(partials, splits, cols, dp(o));
+  count_launch(2);
+  const bool ok = cuda_ok(cudaGetLastError(), "f64 colsum launch");
+  scratch_free(reinterpret_cast<float*>(partials));
+  if (!ok) { release_buf(o); return nullptr; }
+  return (cleave_buf)o;
+}
+
+double cleave_cuda_mse_f64(cleave_buf p, cleave_buf t, cleave_buf dpred) {
+  ApiLock lock;
+  Buf* a = as_buf(p, "mse", DT_F64);
+  Buf* b = as_buf(t, "mse", DT_F64);
+  if (!a || !b) return NAN;
+  Buf* d = nullptr;
+  if (dpred) {
+    d = as_buf(dpred, "mse", DT_F64);
+    if (!d) return NAN;
+  }
+  if (a->len != b->len || (d && d->len != a->len)) {
+    set_error(CLEAVE_CUDA_ERR_SHAPE, "mse: prediction, target and gradient tensors must have the same length");
+    return NAN;
+  }
+  const int64_t n = a->len;
+  Trace tr("mse", "f64 n=%lld", (long long)n);
+  double* sq = reinterpret_cast<double*>(scratch_alloc(n * (int64_t)sizeof(double)));
+  if (!sq) return NAN;
+  const double fn = (double)(int32_t)n;
+  mse_f64_kernel<<<stream_grid(n, kT, kCtas), kT, 0, ctx().stream>>>(dp(a), dp(b), sq, d ? dp(d) : nullptr, n, fn);
+  count_launch();
+  double r = NAN;
+  if (cuda_ok(cudaGetLastError(), "f64 mse launch")) r = reduce_f64_ptr<DSum>(sq, n, fn, 0);
+  scratch_free(reinterpret_cast<float*>(sq));
+  return r;
 }
 
 }  // extern "C"

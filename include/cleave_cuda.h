@@ -297,6 +297,18 @@ double cleave_cuda_sum_f64(cleave_buf v);
 double cleave_cuda_mean_f64(cleave_buf v);
 double cleave_cuda_max_f64(cleave_buf v);
 cleave_buf cleave_cuda_gemm_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k);
+/* What derive() over f64 tensors emits beyond the above (the algebras and their derivative rules are declared for
+ * every T: Float, stdlib/num/num.cleave:189-196, :222-223, :231-234; stdlib/linalg/matrix.cleave:24): transposed
+ * and batched products (exact kernel), the derivative forms, column sums, the squared-error loss, the SGD update. */
+cleave_buf cleave_cuda_gemm_nt_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k);
+cleave_buf cleave_cuda_gemm_tn_f64(cleave_buf a, cleave_buf b, int32_t m, int32_t n, int32_t k);
+cleave_buf cleave_cuda_gemm_batched_f64(cleave_buf a, cleave_buf b, int32_t batch, int32_t m, int32_t n, int32_t k);
+cleave_buf cleave_cuda_tanh_bwd_f64(cleave_buf y, cleave_buf g);
+cleave_buf cleave_cuda_sigmoid_bwd_f64(cleave_buf y, cleave_buf g);
+cleave_buf cleave_cuda_relu_bwd_f64(cleave_buf x, cleave_buf g);
+cleave_buf cleave_cuda_colsum_f64(cleave_buf x, int32_t rows, int32_t cols);
+double cleave_cuda_mse_f64(cleave_buf p, cleave_buf t, cleave_buf dp);      /* dp may be NULL */
+int32_t cleave_cuda_sgd_f64(cleave_buf w, cleave_buf g, double lr, double gscale);
 
 /* ------------------------------------------------------------------ data-parallel step over peer memory
  * No counterpart in the reference (distribution is "named as a goal but not designed",

@@ -79,3 +79,62 @@ def test_element_types_do_not_mix():
     assert L.cleave_cuda_add_f32(a32._h, a64._h) is None and L.cleave_cuda_last_error() == 4
     assert b"f64" in L.cleave_cuda_last_error_message()
     L.cleave_cuda_clear_error()
+
+
+def _wrap(handle, *dims):
+    assert handle, cb.lib().cleave_cuda_last_error_message()
+    return linalg.Tensor._wrap(handle, dims, "f64 op", "f64")
+
+
+def test_derivative_forms_and_sgd_are_bit_exact():
+    # (1 - y*y) * g, y*(1 - y) * g, x > 0 ? g : 0, w - lr*(gscale*g): one rounded operation per step, as the
+    # separate arith ops of the lowered program (stdlib/num/num.cleave:123-136, :222-223)
+    L = cb.lib()
+    rng = np.random.default_rng(3)
+    n = 100003
+    y, g = rng.uniform(-1, 1, n), rng.standard_normal(n)
+    ty, tg = T(y), T(g)
+    one = np.ones(n)
+    want = ref.binary64("mul", ref.binary64("sub", one, ref.binary64("mul", y, y)), g)
+    assert np.array_equal(_wrap(L.cleave_cuda_tanh_bwd_f64(ty._h, tg._h), n).numpy(), want)
+    want = ref.binary64("mul", ref.binary64("mul", y, ref.binary64("sub", one, y)), g)
+    assert np.array_equal(_wrap(L.cleave_cuda_sigmoid_bwd_f64(ty._h, tg._h), n).numpy(), want)
+    assert np.array_equal(_wrap(L.cleave_cuda_relu_bwd_f64(ty._h, tg._h), n).numpy(), np.where(y > 0, g, 0.0))
+    w = rng.standard_normal(n)
+    tw = T(w)
+    assert L.cleave_cuda_sgd_f64(tw._h, tg._h, 0.1, 0.25) == 0
+    want = ref.binary64("sub", w, ref.binary64("mul", np.full(n, 0.1), ref.binary64("mul", np.full(n, 0.25), g)))
+    assert np.array_equal(tw.numpy(), want)
+
+
+@pytest.mark.parametrize("m,n,k", [(33, 65, 17), (100, 130, 77), (128, 64, 256)])
+def test_transposed_and_batched_matmul_are_bit_identical_to_the_reference_loop(m, n, k):
+    L = cb.lib()
+    rng = np.random.default_rng(m + n + k)
+    a, b = rng.uniform(-1, 1, (m, k)), rng.uniform(-1, 1, (k, n))
+    want = ref.matmul64(a, b)
+    at, bt = T(np.ascontiguousarray(a.T)), T(np.ascontiguousarray(b.T))
+    assert np.array_equal(_wrap(L.cleave_cuda_gemm_tn_f64(at._h, T(b)._h, m, n, k), m, n).numpy(), want)
+    assert np.array_equal(_wrap(L.cleave_cuda_gemm_nt_f64(T(a)._h, bt._h, m, n, k), m, n).numpy(), want)
+    A, B = rng.uniform(-1, 1, (3, m, k)), rng.uniform(-1, 1, (3, k, n))
+    got = _wrap(L.cleave_cuda_gemm_batched_f64(T(A)._h, T(B)._h, 3, m, n, k), 3, m, n).numpy()
+    for i in range(3):
+        assert np.array_equal(got[i], ref.matmul64(A[i], B[i]))
+
+
+def test_colsum_and_mse():
+    L = cb.lib()
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((1000, 333))
+    got = _wrap(L.cleave_cuda_colsum_f64(T(x)._h, 1000, 333), 333).numpy()
+    assert np.max(np.abs(got - x.sum(axis=0)) / np.abs(x).sum(axis=0)) <= 1e-14
+    p, t = rng.uniform(0, 1, 100003), rng.uniform(0, 1, 100003)
+    d = linalg.Tensor.zero(100003, dtype="f64")
+    loss = L.cleave_cuda_mse_f64(T(p)._h, T(t)._h, d._h)
+    e = ref.binary64("sub", p, t)
+    assert abs(loss - np.mean(e * e)) <= 1e-14 * np.mean(e * e)
+    want_d = ref.binary64("div", ref.binary64("mul", np.full(p.size, 2.0), e), np.full(p.size, float(p.size)))
+    assert np.array_equal(d.numpy(), want_d)
+    assert L.cleave_cuda_mse_f64(T(p)._h, T(t[:5])._h, None) != L.cleave_cuda_mse_f64(T(p)._h, T(t[:5])._h, None)  # NaN
+    assert L.cleave_cuda_last_error() == 3
+    L.cleave_cuda_clear_error()
