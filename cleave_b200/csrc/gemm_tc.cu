@@ -162,6 +162,8 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 for (int j = 0; j < BM / 32; ++j)
                   tma_load_3d(sa + j * (BK * 128), &map_a, full, mb * BM + j * 32, kb * BK, b);
               }
+            } else if (p.a_sliced) {
+              tma_load_3d(sa, &map_a, full, kb * BK, b, mb * BM);   // K-sliced view: {k in slice, slice, row}
             } else {
               tma_load_3d(sa, &map_a, full, kb * BK, mb * BM, b);
             }
@@ -613,6 +615,7 @@ int gemm_batch_chunk(int64_t bytes_per_entry, int batch) {
 static bool g_mn_major = true;
 static int g_direct = 1;
 static bool g_narrow = true;   // CLEAVE_CUDA_GEMM_NARROW=0: no transposed split-K route for narrow outputs
+static bool g_splitk = true;   // CLEAVE_CUDA_GEMM_SPLITK=0: no split-K route for products with few tiles
 static int g_pair = -1;   // CLEAVE_CUDA_GEMM_PAIR: 1 / 0 = always / never run the padded-planes path on CTA pairs
 static void read_options() {
   static bool done = false;
@@ -624,6 +627,8 @@ static void read_options() {
   if (d && (d[0] == '0' || d[0] == '2' || d[0] == '3')) g_direct = d[0] - '0';
   const char* nr = getenv("CLEAVE_CUDA_GEMM_NARROW");
   if (nr && nr[0] == '0') g_narrow = false;
+  const char* sk = getenv("CLEAVE_CUDA_GEMM_SPLITK");
+  if (sk && sk[0] == '0') g_splitk = false;
   const char* pr = getenv("CLEAVE_CUDA_GEMM_PAIR");
   if (pr && (pr[0] == '0' || pr[0] == '1')) g_pair = pr[0] - '0';
 }
@@ -886,6 +891,131 @@ static bool launch_narrow_transposed(const GemmArgs& g, int slices) {
   return ok;
 }
 
+// ---- few tiles: split K ------------------------------------------------------------------------------------
+// A product with fewer tiles than half the SMs leaves most of the machine idle for the whole of K.  Here K is cut
+// into S slices that run as the S entries of a batch on the in-kernel-split kernel (a K-slice of a K-major operand
+// is a strided view, which a tensor map expresses; a K-slice of an MN-major operand is a contiguous block), so
+// tiles * S CTAs are busy, and one pass adds the S partial results in slice order -- a fixed order, so the result
+// is reproducible -- and applies bias / activation / derivative exactly as the GEMM epilogue would.
+__global__ void __launch_bounds__(256) sum_slices_kernel(const float4* __restrict__ part, float4* __restrict__ c,
+                                                         float4* __restrict__ c_lo, int slices, int64_t n4, int n,
+                                                         const float* __restrict__ bias, int act,
+                                                         const float* __restrict__ dact_y, int dact) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 acc = __ldcg(part + i);
+    for (int sl = 1; sl < slices; ++sl) {
+      const float4 v = __ldcg(part + (int64_t)sl * n4 + i);
+      acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+    }
+    if (bias != nullptr) {
+      const float4 bv = __ldg(reinterpret_cast<const float4*>(bias + (int)((4 * i) % n)));   // n is a multiple of 4
+      acc.x = __fadd_rn(acc.x, bv.x); acc.y = __fadd_rn(acc.y, bv.y);
+      acc.z = __fadd_rn(acc.z, bv.z); acc.w = __fadd_rn(acc.w, bv.w);
+    }
+    if (act != CLEAVE_ACT_IDENTITY) {
+      acc.x = act_apply(acc.x, act); acc.y = act_apply(acc.y, act);
+      acc.z = act_apply(acc.z, act); acc.w = act_apply(acc.w, act);
+    }
+    if (dact_y != nullptr) {
+      const float4 y = __ldg(reinterpret_cast<const float4*>(dact_y) + i);
+      acc.x = dact_apply(y.x, acc.x, dact); acc.y = dact_apply(y.y, acc.y, dact);
+      acc.z = dact_apply(y.z, acc.z, dact); acc.w = dact_apply(y.w, acc.w, dact);
+    }
+    c[i] = acc;
+    if (c_lo != nullptr) c_lo[i] = make_float4(split_lo(acc.x), split_lo(acc.y), split_lo(acc.z), split_lo(acc.w));
+  }
+}
+
+// Number of K slices for the split-K route, 0 if it does not apply.
+static int splitk_slices(const GemmArgs& g) {
+  if (g.batch != 1 || !addressable(g) || g.n % 4 != 0 || !aligned16(g.c) || g.k < 1024) return 0;
+  if ((g.bias && !aligned16(g.bias)) || (g.dact_y && !aligned16(g.dact_y)) || (g.c_lo && !aligned16(g.c_lo))) return 0;
+  const int tiles = ceil_div(g.m, BM) * ceil_div(g.n, BN);
+  const int sms = ctx().sm_count;
+  if (tiles * 2 > sms) return 0;
+  int s = sms / tiles;
+  if (s > 16) s = 16;
+  while (s > 1 && (g.k % s != 0 || (g.k / s) % 16 != 0 || g.k / s < 256)) --s;
+  return s > 1 ? s : 0;
+}
+
+// Tensor map over the K slices of a K-major operand ([rows][K], K contiguous): dimensions ordered by stride
+// {k within the slice, slice, row}, box {16, 1, tile_rows}.
+static bool make_sliced_map(CUtensorMap* map, const float* base, int rows, int K, int slices, int tile_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  const int ks = K / slices;
+  cuuint64_t dims[3] = {(cuuint64_t)ks, (cuuint64_t)slices, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)ks * 4, (cuuint64_t)K * 4};
+  cuuint32_t box[3] = {16, 1, (cuuint32_t)tile_rows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (K-sliced operand %d x %d / %d)", (int)r,
+              rows, K, slices);
+    return false;
+  }
+  return true;
+}
+
+static bool launch_split_k(const GemmArgs& g, int slices) {
+  const int ks = g.k / slices;
+  const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
+  const bool a_blocked = a_mn && g.m % 32 == 0, b_blocked = b_mn && g.n % 32 == 0;
+  const int b_box_rows = g.n < BN ? round_up(g.n, 32) : BN;
+  const int64_t out = (int64_t)g.m * g.n;
+  float* part = scratch_alloc((int64_t)slices * out * 4);
+  if (!part) return false;
+  CUtensorMap maps[4];
+  // an MN-major operand is stored [K][rows]: its K slices are consecutive blocks, i.e. a batch of [ks][rows] matrices
+  bool ok = (a_mn ? make_direct_map(&maps[0], g.a, g.m, ks, slices, false, BM, a_blocked)
+                  : make_sliced_map(&maps[0], g.a, g.m, g.k, slices, BM)) &&
+            (b_mn ? make_direct_map(&maps[1], g.b, g.n, ks, slices, false, b_box_rows, b_blocked)
+                  : make_sliced_map(&maps[1], g.b, g.n, g.k, slices, b_box_rows));
+  if (ok) {
+    maps[2] = maps[0];
+    maps[3] = maps[1];
+    TcParams p;
+    p.a_blocked = a_blocked;
+    p.b_blocked = b_blocked;
+    p.a_sliced = a_mn ? 0 : 1;
+    p.b_sliced = b_mn ? 0 : 1;
+    p.c_tma = 0;
+    p.b_box_rows = b_box_rows;
+    p.c = part;
+    p.bias = nullptr;
+    p.dact_y = nullptr;
+    p.dact = CLEAVE_ACT_IDENTITY;
+    p.m = g.m;
+    p.n = g.n;
+    p.num_kb = ceil_div(ks, 16);
+    p.chunk_kb = kChunkK / 16;
+    p.batch = slices;
+    p.mblks = ceil_div(g.m, BM);
+    p.nblks = ceil_div(g.n, BN);
+    p.act = CLEAVE_ACT_IDENTITY;
+    p.status = ctx().status_dev;
+    ok = run_tc_layout<kPathDirect>(a_mn, b_mn, maps, p);
+  }
+  if (ok) {
+    const int64_t n4 = out / 4;
+    sum_slices_kernel<<<stream_grid(n4, 256, 4), 256, 0, ctx().stream>>>(
+        reinterpret_cast<const float4*>(part), reinterpret_cast<float4*>(g.c), reinterpret_cast<float4*>(g.c_lo), slices,
+        n4, g.n, g.bias, g.act, g.dact_y, g.dact);
+    count_launch();
+    ok = cuda_ok(cudaGetLastError(), "slice-sum launch");
+  }
+  scratch_free(part);
+  return ok;
+}
+
 // hi planes are the caller's tensors, lo planes come from one streaming pass per operand.
 static bool launch_lo_plane(const GemmArgs& g) {
   const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
@@ -967,22 +1097,28 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     return false;
   }
   read_options();
-  // Lo planes handed in by the caller (an earlier GEMM's epilogue wrote them, or they are reused across calls):
-  // the lo-plane route then needs no pre-pass at all, which beats every other route where it applies.
-  if ((g.a_lo || g.b_lo) && g_direct == 1 && lo_plane_eligible(g) && aligned16(g.a_lo) && aligned16(g.b_lo))
-    return launch_lo_plane(g);
-  // The narrow transposed route adds partial results in a pass of its own and cannot write C's low part.
-  const bool narrow_ok = g.c_lo == nullptr;
+  // Routes chosen by shape alone come first, so that a call gives the same bits whether or not the caller also
+  // hands in lo planes.  (1) A narrow output with long m and k: the transposed split-K route; it adds its partial
+  // results in a pass of its own that cannot write C's lo plane.  (2) Few tiles: split K.
+  if (g_direct == 1) {
+    if (g_narrow && g.c_lo == nullptr) {
+      const int slices = narrow_slices(g);
+      if (slices > 0) return launch_narrow_transposed(g, slices);
+    }
+    if (g_splitk) {
+      const int slices = splitk_slices(g);
+      if (slices > 0) return launch_split_k(g, slices);
+    }
+    // (3) Lo planes handed in by the caller (an earlier GEMM's epilogue wrote them, or they are reused across
+    // calls): the lo-plane route then needs no pre-pass at all, which beats every other route where it applies.
+    if ((g.a_lo || g.b_lo) && lo_plane_eligible(g) && aligned16(g.a_lo) && aligned16(g.b_lo)) return launch_lo_plane(g);
+  }
   // Measured choice.  Small / narrow problems: split in the kernel.  Up to 4096^2 outputs: lo planes (the
   // pre-pass moves 2/3 of the bytes of the padded one: 183 vs 300 us at 8192^3, 50 vs 80 us at 4096^3).
   // Beyond that the padded [hi | lo] planes win although their pre-pass is longer: the kernel runs
   // 3-5 % slower when its hi operand is the raw tensor (low mantissa bits that the tensor pipe ignores
   // still travel through shared memory; the kernel runs under the power cap).
   if (g_direct == 2 || (g_direct == 1 && prefer_direct(g))) {
-    if (g_direct == 1 && g_narrow && narrow_ok) {
-      const int slices = narrow_slices(g);
-      if (slices > 0) return launch_narrow_transposed(g, slices);
-    }
     if (addressable(g)) return launch_direct(g);
   } else if (g_direct == 3 || (g_direct == 1 && (int64_t)g.m * g.n <= (1ll << 24))) {
     if (lo_plane_eligible(g)) return launch_lo_plane(g);

@@ -66,14 +66,23 @@ struct Finish {
   unsigned int ticket = 0;
 };
 
+// Arrival on a completion counter with release + acquire semantics in ONE memory operation: the partial sums this
+// thread stored before it are visible to whoever observes the count, and the CTA that observes the final count sees
+// every other CTA's partials.  Replaces store; fence; atomic; fence -- two L2 round trips less on the kernel's tail.
+__device__ __forceinline__ unsigned int arrive_acq_rel(unsigned int* counter) {
+  unsigned int prev;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(counter) : "memory");
+  return prev;
+}
+
 // Publishes partials[blockIdx.x] = value (thread 0's) and tells, in every thread, whether this CTA
 // is the last of the grid to do so.  The last CTA re-arms the counter for the next launch.
 __device__ __forceinline__ bool publish_and_check_last(float* partials, float value, const Finish& f) {
   __shared__ int s_last;
   if (threadIdx.x == 0) {
     partials[blockIdx.x] = value;
-    __threadfence();
     if (f.ticket_word != nullptr) {
+      __threadfence();
       unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(f.ticket_word);
       unsigned int count;
       for (;;) {   // ends after at most gridDim.x rounds: every failed exchange means another CTA arrived
@@ -84,14 +93,14 @@ __device__ __forceinline__ bool publish_and_check_last(float* partials, float va
         seen = prev;
       }
       s_last = (count == gridDim.x) ? 1 : 0;
+      if (s_last) __threadfence();
     } else {
-      const unsigned int prev = atomicAdd(f.done, 1u);
+      const unsigned int prev = arrive_acq_rel(f.done);
       s_last = (prev == gridDim.x - 1) ? 1 : 0;
       if (s_last) *f.done = 0;
     }
   }
   __syncthreads();
-  if (s_last) __threadfence();
   return s_last != 0;
 }
 
@@ -123,14 +132,27 @@ __global__ void __launch_bounds__(kRThreads) reduce_kernel(const float* __restri
   if (vec) {   // slab is a multiple of 4 and v is 16-byte aligned
     const float4* v4 = reinterpret_cast<const float4*>(v);
     const int64_t lo4 = lo >> 2, hi4 = hi >> 2;
-    for (int64_t i = lo4 + threadIdx.x; i < hi4; i += kRThreads) {
+    int64_t i = lo4 + threadIdx.x;
+    for (; i + 3 * kRThreads < hi4; i += 4 * kRThreads) {   // four independent 16-byte loads in flight
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) x[u] = __ldcs(v4 + i + u * kRThreads);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        acc[0] = R::combine(acc[0], x[u].x);
+        acc[1] = R::combine(acc[1], x[u].y);
+        acc[2] = R::combine(acc[2], x[u].z);
+        acc[3] = R::combine(acc[3], x[u].w);
+      }
+    }
+    for (; i < hi4; i += kRThreads) {
       float4 x = __ldcs(v4 + i);
       acc[0] = R::combine(acc[0], x.x);
       acc[1] = R::combine(acc[1], x.y);
       acc[2] = R::combine(acc[2], x.z);
       acc[3] = R::combine(acc[3], x.w);
     }
-    for (int64_t i = (hi4 << 2) + threadIdx.x; i < hi; i += kRThreads) acc[0] = R::combine(acc[0], v[i]);
+    for (int64_t j = (hi4 << 2) + threadIdx.x; j < hi; j += kRThreads) acc[0] = R::combine(acc[0], v[j]);
   } else {
     for (int64_t i = lo + threadIdx.x; i < hi; i += kRThreads) acc[0] = R::combine(acc[0], v[i]);
   }
@@ -199,12 +221,13 @@ __global__ void __launch_bounds__(kCsTx* kCsTy) colsum_stage1(const float* __res
   }
   if (out == nullptr) return;
   // ---- the strip's last CTA combines the splits
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) is_last = atomicAdd(&g_colsum_done[blockIdx.x], 1u) == gridDim.y - 1 ? 1 : 0;
+  __syncthreads();   // every thread's partial stores are ordered before thread 0's arrival below (CTA scope) ...
+  if (threadIdx.x == 0) {
+    __threadfence();   // ... and made visible device-wide (cumulativity: the fence covers what the barrier ordered)
+    is_last = arrive_acq_rel(&g_colsum_done[blockIdx.x]) == gridDim.y - 1 ? 1 : 0;
+  }
   __syncthreads();
   if (!is_last) return;
-  __threadfence();
   const int splits = gridDim.y;
   float4 part = make_float4(0.f, 0.f, 0.f, 0.f);
   if (c0 < cols) {
@@ -373,15 +396,14 @@ __device__ __forceinline__ void linreg_fold(const float* partials, int pitch, in
 // Publishes this CTA's partials and returns true in exactly one CTA: the last one to arrive.
 __device__ __forceinline__ bool linreg_arrive_last() {
   __shared__ int s_last;
-  __threadfence();
-  __syncthreads();
+  __syncthreads();     // the partial stores of threads 0..feat are ordered before thread 0's arrival (CTA scope)
   if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(&g_linreg_done, 1u);
+    __threadfence();   // cumulative: makes them visible device-wide before the count can be observed
+    const unsigned int prev = arrive_acq_rel(&g_linreg_done);
     s_last = (prev == gridDim.x - 1) ? 1 : 0;
     if (s_last) g_linreg_done = 0;   // ready for the next launch
   }
   __syncthreads();
-  if (s_last) __threadfence();
   return s_last != 0;
 }
 

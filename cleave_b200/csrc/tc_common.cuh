@@ -207,6 +207,7 @@ struct TcParams {
   int a_blocked, b_blocked;   // direct path, MN-major operand: one 4-D box per stage instead of 32-wide boxes
   int b_box_rows;             // direct path: rows of B fetched and split per stage (BN, less when n is small)
   int b_sliced;               // direct path: B is a K-sliced view, map dimensions {k, slice, row}
+  int a_sliced = 0;           // direct path: the same for a K-major A
   int c_tma;                  // pair kernel: a tensor map over C exists (16-byte aligned, n a multiple of 4): TMA stores
   DeviceStatus* status;
 };

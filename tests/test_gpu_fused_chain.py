@@ -41,7 +41,7 @@ def test_split_lo_matches_its_definition():
 ROUTES = [(1024, 1024, 512, False, False, GEMM_AUTO), (4096, 1024, 256, False, True, GEMM_AUTO),
           (512, 2048, 384, True, False, GEMM_AUTO), (300, 200, 100, False, False, GEMM_3XTF32),
           (4352, 4096, 160, False, False, GEMM_3XTF32), (96, 80, 40, False, False, GEMM_EXACT),
-          (4096, 64, 2048, False, False, GEMM_3XTF32)]
+          (4096, 64, 2048, False, False, GEMM_3XTF32), (1024, 512, 2048, False, False, GEMM_AUTO)]   # last: split-K
 
 
 @pytest.mark.parametrize("m,n,k,ta,tb,algo", ROUTES)
@@ -60,7 +60,7 @@ def test_output_lo_plane_equals_a_split_of_the_result_and_changes_nothing(m, n, 
     assert np.array_equal(c_lo.numpy().view(np.uint32), host_split_lo(fused.numpy()).view(np.uint32))
 
 
-@pytest.mark.parametrize("m,n,k,ta,tb", [(1024, 1024, 512, False, False), (2048, 512, 1024, True, False),
+@pytest.mark.parametrize("m,n,k,ta,tb", [(1024, 1024, 512, False, False), (2048, 2048, 1024, True, False),
                                          (512, 4096, 256, False, True), (4096, 1024, 4096, True, False)])
 def test_operand_lo_planes_from_the_caller_change_no_bit(m, n, k, ta, tb):
     a, b = workloads.gemm_inputs(m, n, k)

@@ -259,3 +259,27 @@ def test_narrow_output_takes_the_transposed_split_k_route(m, n, k):
     got = gemm(a, b, GEMM_3XTF32)
     assert L.cleave_cuda_kernel_launches() - before == 2          # the GEMM kernel and the sum-transpose pass
     assert_gemm_close(got, a, b, what=("narrow", m, n, k))
+
+
+@pytest.mark.parametrize("m,n,k,ta,tb", [(1024, 1024, 1024, False, False), (512, 768, 4096, False, False),
+                                         (1024, 512, 2048, True, False), (640, 1024, 1536, False, True),
+                                         (256, 256, 8192, True, True), (1000, 520, 2048, False, False)])
+def test_few_tiles_take_the_split_k_route(m, n, k, ta, tb):
+    # Fewer tiles than half the SMs: K is cut into slices that run side by side, then one pass adds the partial
+    # results in slice order and applies bias + activation.  Same tolerance as every other route.
+    a, b = workloads.gemm_inputs(m, n, k)
+    a *= f32(0.25)
+    A = np.ascontiguousarray(a.T) if ta else a
+    B = np.ascontiguousarray(b.T) if tb else b
+    L = cb.lib()
+    before = L.cleave_cuda_kernel_launches()
+    got = gemm(A, B, linalg.GEMM_AUTO, trans_a=ta, trans_b=tb)
+    assert L.cleave_cuda_kernel_launches() - before == 2          # the sliced GEMM kernel and the slice-sum pass
+    assert_gemm_close(got, a, b, what=("split-K", m, n, k, ta, tb))
+    bias = workloads.uniform_pm1(7, n)
+    got = gemm(A, B, linalg.GEMM_AUTO, trans_a=ta, trans_b=tb, bias=bias, act="tanh")
+    z = ref.bias_add(ref.matmul(a, b), bias)
+    s = ref.matmul_absdot(a, b) + np.abs(bias)
+    assert np.max(np.abs(got.astype(np.float64) - ref.tanh(z)) / s) <= TOL
+    # run to run the same bits (fixed slice order)
+    assert np.array_equal(got, gemm(A, B, linalg.GEMM_AUTO, trans_a=ta, trans_b=tb, bias=bias, act="tanh"))
