@@ -33,6 +33,7 @@ SIGNATURES = {
     "cleave_cuda_live_bytes": (i64, []),
     "cleave_cuda_kernel_launches": (i64, []),
     "cleave_cuda_test_hook": (i64, [i32, i64]),
+    "cleave_cuda_gemm_batch_chunk": (i32, [i64, i32]),
     "cleave_cuda_profile_begin": (None, []),
     "cleave_cuda_profile_end": (ctypes.c_double, [ctypes.POINTER(i32)]),
     "cleave_cuda_host_alloc": (ctypes.c_void_p, [i64]),
@@ -78,6 +79,7 @@ SIGNATURES = {
     "cleave_cuda_gemm_fused_f32": (i32, [c_buf, c_buf, c_buf, i32, i32, i32, i32, i32, i32, i32, c_buf, i32, c_buf, i32,
                                          c_buf, c_buf, c_buf]),
     "cleave_cuda_split_lo_f32": (c_buf, [c_buf]),
+    "cleave_cuda_split_lo_into_f32": (i32, [c_buf, c_buf, ctypes.c_void_p]),
     "cleave_cuda_bias_act_f32": (c_buf, [c_buf, c_buf, i32, i32, i32]),
     "cleave_cuda_mse_f32": (f32, [c_buf, c_buf, c_buf]),
     "cleave_cuda_mse_act_bwd_f32": (f32, [c_buf, c_buf, c_buf, i32]),

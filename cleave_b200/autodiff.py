@@ -46,6 +46,7 @@ class MLP2:
             raise ValueError("activations with a declared derivative rule: tanh, sigmoid")
         self.d_in, self.d_hid, self.d_out, self.act1, self.act2 = d_in, d_hid, d_out, act1, act2
         self.chain_lo = all(d % 32 == 0 for d in (d_in, d_hid, d_out)) if chain_lo is None else bool(chain_lo)
+        self.weights_version = 0   # bumped by every method of this class that rewrites the weights (load, sgd)
         sizes = [d_in * d_hid, d_hid, d_hid * d_out, d_out]
         shapes = [(d_in, d_hid), (d_hid,), (d_hid, d_out), (d_out,)]
         self.n_params = sum(sizes)
@@ -71,6 +72,7 @@ class MLP2:
     def load(self, W1, b1, W2, b2) -> None:
         flat = np.concatenate([np.asarray(a, np.float32).ravel() for a in (W1, b1, W2, b2)])
         assert flat.size == self.n_params
+        self.weights_version += 1
         from ._lib import c_f32p
         if lib().cleave_cuda_upload_into_f32(self.params._h, flat.ctypes.data_as(c_f32p), flat.size) != 0:
             raise_last_error("MLP2.load")
@@ -83,13 +85,15 @@ class MLP2:
         return H, Y
 
     def forward_backward(self, X: Tensor, T: Tensor, keep: bool = False, on_grads_ready=None,
-                         loss_out: Tensor | None = None, before_layer=None):
+                         loss_out: Tensor | None = None, before_layer=None, weight_planes=None):
         """One forward + backward pass; gradients land in ``self.grads``.  Returns the loss
         (and, with ``keep``, the intermediates for inspection).  ``on_grads_ready(i)`` is called
         when a gradient bucket is final and its weights are no longer read in this pass:
         1 = [dW1 | db1] first, then 0 = [dW2 | db2].  ``before_layer(i)`` is called just before the
         first kernel that reads layer i's weights (1: W1, b1; 2: W2, b2), so a data-parallel driver can
         let the previous step's exchange of that layer run beside the kernels queued before it.
+        ``weight_planes = (W1_lo, W2_lo)``: lo planes of the CURRENT weights that the caller maintains (either
+        may be ``None``); without them the step splits the weights itself when it chains planes.
         With ``loss_out`` (a one-element tensor) the loss is left on the device, nothing waits and
         ``None`` is returned."""
         if before_layer:
@@ -97,16 +101,18 @@ class MLP2:
         batch = X.dims[0]
         # Lo planes travel with their tensors through the chain when the products are large enough for the
         # tensor cores (each plane is one extra store in a producer's epilogue, or one streaming pass).
-        chain = self.chain_lo and batch % 32 == 0 and batch * self.d_in * self.d_hid >= (1 << 24)
+        chain = self.chains_planes(batch)
         lo = (lambda t: split_lo(t)) if chain else (lambda t: None)
         new = (lambda *dims: Tensor.empty(*dims)) if chain else (lambda *dims: None)
-        X_lo, W1_lo = lo(X), lo(self.W1)
+        given1, given2 = weight_planes if weight_planes else (None, None)
+        X_lo = lo(X)
+        W1_lo = given1 if (chain and given1 is not None) else lo(self.W1)
         H_lo = new(batch, self.d_hid)
         H = gemm_into(Tensor.empty(batch, self.d_hid), X, self.W1, bias=self.b1, act=self.act1,
                       a_lo=X_lo, b_lo=W1_lo, c_lo=H_lo)
         if before_layer:
             before_layer(2)
-        W2_lo = lo(self.W2)
+        W2_lo = given2 if (chain and given2 is not None) else lo(self.W2)
         Y = gemm_into(Tensor.empty(batch, self.d_out), H, self.W2, bias=self.b2, act=self.act2, a_lo=H_lo, b_lo=W2_lo)
         if chain:
             dev_loss = loss_out if loss_out is not None else Tensor.empty(1)
@@ -142,12 +148,18 @@ class MLP2:
         return loss
 
     @staticmethod
+    def chains_planes(self, batch: int) -> bool:
+        """Whether a step at this batch size hands lo planes from product to product."""
+        return bool(self.chain_lo and batch % 32 == 0 and batch * self.d_in * self.d_hid >= (1 << 24))
+
+    @staticmethod
     def _colsum_into(out: Tensor, x: Tensor) -> None:
         if lib().cleave_cuda_colsum_into_f32(out._h, x._h, x.dims[0], x.dims[1]) != 0:
             raise_last_error("colsum_into")
 
     def sgd(self, lr: float, gscale: float = 1.0) -> None:
         """``p = p - lr * gscale * g`` over the whole parameter buffer in one pass."""
+        self.weights_version += 1
         nn.sgd_step(self.params, self.grads, lr, gscale)
 
 

@@ -41,7 +41,8 @@ __device__ __forceinline__ float dact_apply(float y, float g, int dact) {
 }
 
 bool launch_gemm_exact(const GemmArgs& g);
-bool split_lo_plane(const float* src, float* dst, int64_t n);   // dst[i] = low split part of src[i]
+// dst[i] = low split part of src[i]; on_stream = nullptr: the library's stream
+bool split_lo_plane(const float* src, float* dst, int64_t n, cudaStream_t on_stream = nullptr);
 bool launch_gemm_3xtf32(const GemmArgs& g);   // false + error if the problem cannot use this path
 bool gemm_3xtf32_supported(const GemmArgs& g);
 int gemm_batch_chunk(int64_t bytes_per_entry, int batch);   // batch entries per pass (workspace and grid limits)

@@ -167,4 +167,18 @@ cleave_buf cleave_cuda_split_lo_f32(cleave_buf x) {
   return (cleave_buf)o;
 }
 
+int32_t cleave_cuda_gemm_batch_chunk(int64_t workspace_bytes_per_entry, int32_t batch) {
+  return gemm_batch_chunk(workspace_bytes_per_entry, batch);
+}
+
+int32_t cleave_cuda_split_lo_into_f32(cleave_buf lo, cleave_buf x, void* cuda_stream) {
+  ApiLock lock;
+  Buf* a = as_buf(x, "split_lo_into");
+  Buf* o = as_buf(lo, "split_lo_into");
+  if (!a || !o) return -cleave_cuda_last_error();
+  if (a->len != o->len || a->ptr == o->ptr)
+    return -set_error(CLEAVE_CUDA_ERR_SHAPE, "split_lo_into: the plane must be a distinct tensor of the same length");
+  return split_lo_plane(a->ptr, o->ptr, a->len, (cudaStream_t)cuda_stream) ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
+}
+
 }  // extern "C"

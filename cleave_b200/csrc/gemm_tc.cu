@@ -516,8 +516,8 @@ __global__ void split_lo_scalar_kernel(const float* __restrict__ src, float* __r
 }
 
 // ---- host side ---------------------------------------------------------------------------------
-bool split_lo_plane(const float* src, float* dst, int64_t n) {
-  cudaStream_t s = ctx().stream;
+bool split_lo_plane(const float* src, float* dst, int64_t n, cudaStream_t on_stream) {
+  cudaStream_t s = on_stream ? on_stream : ctx().stream;
   if (aligned16(src) && aligned16(dst)) {
     const int64_t n4 = n / 4;
     if (n4 > 0) {
@@ -1076,17 +1076,18 @@ static bool launch_lo_plane(const GemmArgs& g) {
   return ok;
 }
 
-// Tensor map over the output for TMA stores: dims {n, m, batch}, box 32 x 32 floats, 128-byte swizzle (the layout
-// of the drain warps' shared staging tile).  Needs a 16-byte aligned C and n a multiple of 4.
-static bool make_c_map(CUtensorMap* map, float* c, int m, int n, int batch) {
+// Tensor map over the output for TMA stores: dims {n, m, batch}; box 32 x 32 floats with the 128-byte swizzle
+// (mode 1: the layout of a drain warp's shared staging tile) or 16 columns x 32 rows with the 64-byte swizzle
+// (mode 2: the layout of its halves).  Needs a 16-byte aligned C and n a multiple of 4.
+static bool make_c_map(CUtensorMap* map, float* c, int m, int n, int batch, int mode) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return false;
   cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)batch};
   cuuint64_t strides[2] = {(cuuint64_t)n * 4, (cuuint64_t)m * n * 4};
-  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t box[3] = {mode == 2 ? 16u : 32u, 32, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+             mode == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
          CUDA_SUCCESS;
 }
 
@@ -1183,8 +1184,14 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     if (pair) {
       p.mblks = Mp / 256;
       // full tiles leave through TMA stores when a tensor map can describe C
-      static const bool tma_store = !(getenv("CLEAVE_CUDA_GEMM_TMA_STORE") && getenv("CLEAVE_CUDA_GEMM_TMA_STORE")[0] == '0');
-      p.c_tma = (tma_store && aligned16(p.c) && g.n % 4 == 0 && make_c_map(&maps[2], p.c, g.m, g.n, nb)) ? 1 : 0;
+      // CLEAVE_CUDA_GEMM_TMA_STORE: 0 = the warps' own stores, 1 = 32 x 32 bulk stores one at a time, 2 = 32 x 16
+      // bulk stores, two in flight
+      static const int tma_store = [] {
+        const char* e = getenv("CLEAVE_CUDA_GEMM_TMA_STORE");
+        return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
+      }();
+      p.c_tma = (tma_store && aligned16(p.c) && g.n % 4 == 0 && make_c_map(&maps[2], p.c, g.m, g.n, nb, tma_store))
+                    ? tma_store : 0;
       ok = run_tc_pair(a_mn, b_mn, maps, p, bk);
     } else {
       ok = run_tc_layout<kPathPlanes>(a_mn, b_mn, maps, p);

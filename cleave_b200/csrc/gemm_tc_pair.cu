@@ -4,7 +4,7 @@
 // operand traffic into shared memory and out of it to the tensor pipe is 2/3 of the one-CTA kernel's
 // (A 128 + B 128 rows per K-block instead of 128 + 256).  Each CTA keeps the accumulator of its own
 // 128 rows in its own TMEM and drains it exactly as the one-CTA kernel does; full tiles are stored with TMA
-// (32 x 32 bulk tensor stores from the drain warps' swizzled staging tiles), ragged ones with plain stores.
+// (32-row x 16-column bulk tensor stores from the drain warps' swizzled staging tiles, two in flight), ragged ones with plain stores.
 //
 // Operands: the padded [hi | lo] planes of the pre-pass (both operands padded to 256 rows).  The K-block is a
 // template parameter: 32 (three stages of 64 KiB, K-major rows of 128 bytes in the 128-byte swizzle; the default,

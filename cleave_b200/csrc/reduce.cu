@@ -59,11 +59,6 @@ struct Finish {
   int mode;
   const float* first;
   unsigned int* done;   // completion counter of this launch family: zero between launches
-  // Ticketed completion word (used instead of `done` when non-null): high half = ticket of the launch that
-  // is counting, low half = CTAs arrived.  A launch whose ticket differs from the stored one restarts the
-  // count, so a word left non-zero by a launch that never finished cannot stall later launches.
-  unsigned long long* ticket_word = nullptr;
-  unsigned int ticket = 0;
 };
 
 // Arrival on a completion counter with release + acquire semantics in ONE memory operation: the partial sums this
@@ -81,24 +76,9 @@ __device__ __forceinline__ bool publish_and_check_last(float* partials, float va
   __shared__ int s_last;
   if (threadIdx.x == 0) {
     partials[blockIdx.x] = value;
-    if (f.ticket_word != nullptr) {
-      __threadfence();
-      unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(f.ticket_word);
-      unsigned int count;
-      for (;;) {   // ends after at most gridDim.x rounds: every failed exchange means another CTA arrived
-        count = ((unsigned int)(seen >> 32) == f.ticket) ? (unsigned int)seen + 1u : 1u;
-        const unsigned long long want = ((unsigned long long)f.ticket << 32) | count;
-        const unsigned long long prev = atomicCAS(f.ticket_word, seen, want);
-        if (prev == seen) break;
-        seen = prev;
-      }
-      s_last = (count == gridDim.x) ? 1 : 0;
-      if (s_last) __threadfence();
-    } else {
-      const unsigned int prev = arrive_acq_rel(f.done);
-      s_last = (prev == gridDim.x - 1) ? 1 : 0;
-      if (s_last) *f.done = 0;
-    }
+    const unsigned int prev = arrive_acq_rel(f.done);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) *f.done = 0;
   }
   __syncthreads();
   return s_last != 0;
@@ -894,9 +874,9 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
 // ------------------------------------------------------------------------------------------------
 namespace cleave {
 
-constexpr int kNoAllocScratchFloats = kMaxPartials + 4;     // 1188 floats, 4752 bytes: partials, then the 8-byte
-                                                            // completion word (byte offset 4736)
-static_assert((kMaxPartials * sizeof(float)) % 8 == 0, "the completion word must be 8-byte aligned");
+constexpr int kNoAllocScratchFloats = kMaxPartials + 4;     // 1188 floats, 4752 bytes: partials, then the
+                                                            // completion counter (byte offset 4736)
+
 constexpr int64_t kNoAllocMaxLen = 2147483647ll;             // largest tensor an i32 shape can describe
 constexpr int kNoAllocMaxDevices = 64;
 
@@ -926,7 +906,7 @@ bool noalloc_poke_completion_word(unsigned long long value) {
   float* scratch = noalloc_scratch_for_current_device();
   if (!scratch) return false;
   return cuda_ok(cudaMemcpy(scratch + kMaxPartials, &value, sizeof(value), cudaMemcpyHostToDevice),
-                 "cudaMemcpy(completion word)");
+                 "cudaMemcpy(completion counter)");
 }
 
 }  // namespace cleave
@@ -949,22 +929,20 @@ extern "C" int32_t cleave_cuda_sum_noalloc_f32(const float* x_dev, int64_t len, 
   // Same slab rule and the same kernel as cleave_cuda_sum_f32, so the summation tree and
   // therefore the result are identical.  The CTAs write partials [0, ctas) and the last one to
   // finish reads exactly those, so no value left in the array by an earlier call is ever read.
-  // Nothing in the array has to start at zero: the completion word behind the partials carries the
-  // ticket of the call that is counting in it (tickets start at 1 and grow with every call of this
-  // process), and a call that finds another ticket there restarts the count.  So a word left behind by
-  // a call whose kernel never finished -- or by two calls that overlapped, which is a caller error --
-  // cannot make a later, correctly ordered call skip its final step.
+  // The one word that must start at zero is the completion counter behind the partials.  It is cleared
+  // on the caller's stream right before the kernel (a memset node: no allocation, ordered like the kernel
+  // itself), so a value left behind by a call whose kernel never finished -- or by two calls that
+  // overlapped, which is a caller error -- cannot make this call skip its final step.
   int64_t slab;
   int ctas;
   // The occupancy query reads kernel attributes only; it allocates nothing.
   static const int max_ctas = resident_ctas(reduce_kernel<SumRed>);
   slab_for(len, max_ctas, &slab, &ctas);
-  static unsigned int next_ticket = 0;   // guarded by the API lock
-  if (++next_ticket == 0) ++next_ticket;
-  Finish fin{out_dev, 1.0f, 0, nullptr, nullptr};
-  fin.ticket_word = reinterpret_cast<unsigned long long*>(scratch + kMaxPartials);
-  fin.ticket = next_ticket;
-  reduce_kernel<SumRed><<<ctas, kRThreads, 0, s>>>(x_dev, len, slab, scratch, aligned16(x_dev) ? 1 : 0, fin);
+  unsigned int* done = reinterpret_cast<unsigned int*>(scratch + kMaxPartials);
+  if (!cuda_ok(cudaMemsetAsync(done, 0, 2 * sizeof(unsigned int), s), "cudaMemsetAsync(completion counter)"))
+    return -cleave_cuda_last_error();
+  reduce_kernel<SumRed><<<ctas, kRThreads, 0, s>>>(x_dev, len, slab, scratch, aligned16(x_dev) ? 1 : 0,
+                                                   Finish{out_dev, 1.0f, 0, nullptr, done});
   count_launch();
   if (!cuda_ok(cudaGetLastError(), "sum_noalloc launch")) return -cleave_cuda_last_error();
   return CLEAVE_CUDA_OK;

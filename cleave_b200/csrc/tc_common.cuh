@@ -209,6 +209,7 @@ struct TcParams {
   int b_sliced;               // direct path: B is a K-sliced view, map dimensions {k, slice, row}
   int a_sliced = 0;           // direct path: the same for a K-major A
   int c_tma;                  // pair kernel: a tensor map over C exists (16-byte aligned, n a multiple of 4): TMA stores
+                              // of 32 x 32 blocks (1) or of 32 x 16 blocks, two in flight (2)
   DeviceStatus* status;
 };
 
@@ -242,8 +243,9 @@ __device__ __forceinline__ void report(DeviceStatus* st, int code, int where, in
 // out), but a store instruction is efficient when the warp covers whole 128-byte lines, so, 32 columns at a
 // time, every thread parks its 8 16-byte words in the warp-private shared tile `stage` (word j of row r at
 // slot j ^ (r & 7): conflict free both ways) and the warp then writes 4 rows x 128 bytes per instruction --
-// or, with `map_c` (tensor map over cmat {n, m, batch}, box 32 x 32, 128-byte swizzle, which is exactly the
-// layout of that shared tile), one lane hands each 32 x 32 block to TMA as a bulk tensor store.
+// or, with `map_c` (tensor map over cmat {n, m, batch}), one lane hands blocks to TMA as bulk tensor stores:
+// p.c_tma == 1: 32 x 32 blocks (box 32 x 32, 128-byte swizzle), one at a time; p.c_tma == 2: 32-row x 16-column
+// blocks (box 16 x 32, 64-byte swizzle), two in flight.
 __device__ __forceinline__ void store_block(const float (&sum)[BN / 2], float* cmat, const TcParams& p, int b,
                                             int tile_row0, int nb, int q, int half, int lane, bool vec_ok, float4* stage,
                                             const CUtensorMap* map_c) {
@@ -265,7 +267,9 @@ __device__ __forceinline__ void store_block(const float (&sum)[BN / 2], float* c
     }
     return;
   }
-  if (map_c != nullptr) {
+  if (map_c != nullptr && p.c_tma == 1) {
+    // One 32 x 32 block per bulk store: the shared tile (word j of row r at slot j ^ (r & 7), rows of 128 bytes) is
+    // exactly TMA's 128-byte swizzle.  The warp waits for the copy engine to have read the tile before repacking it.
     const uint32_t stage_addr = smem_u32(stage);
 #pragma unroll
     for (int pass = 0; pass < BN / 64; ++pass) {
@@ -285,6 +289,39 @@ __device__ __forceinline__ void store_block(const float (&sum)[BN / 2], float* c
       }
       __syncwarp();
     }
+    return;
+  }
+  if (map_c != nullptr) {
+    // p.c_tma == 2: two 2 KiB halves of the warp's staging tile alternate, each a 32-row x 16-column block (rows of
+    // 64 bytes in TMA's 64-byte swizzle: 16-byte word j of row r at slot j ^ ((r >> 1) & 3), conflict free for the
+    // row-per-lane writes).  While the copy engine reads one half the warp already packs the other, so the latency
+    // of a bulk store is hidden behind the next one.
+    const uint32_t stage_addr = smem_u32(stage);
+    constexpr int kPasses = BN / 2 / 16;
+#pragma unroll
+    for (int pass = 0; pass < kPasses; ++pass) {
+      const int half_buf = pass & 1;
+      if (pass >= 2) {
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // this half has been read
+        __syncwarp();
+      }
+      float4* buf = stage + half_buf * 128;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        buf[lane * 4 + (j ^ ((lane >> 1) & 3))] = make_float4(sum[16 * pass + 4 * j], sum[16 * pass + 4 * j + 1],
+                                                              sum[16 * pass + 4 * j + 2], sum[16 * pass + 4 * j + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the copy engine
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile(
+            "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+            ::"l"(map_c), "r"(stage_addr + half_buf * 2048), "r"(col0 + 16 * pass), "r"(tile_row0 + q * 32), "r"(b)
+            : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the staging tile may be reused
+    __syncwarp();
     return;
   }
   float* cblock = cmat + ((int64_t)b * p.m + tile_row0 + q * 32) * (int64_t)p.n + col0;
@@ -384,7 +421,7 @@ __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcPara
 
 // Pair kernel (gemm_tc_pair.cu): two CTAs of a cluster share one 256 x 256 tile (tcgen05 cta_group::2).
 // `maps` = {A planes, B planes, C}; the planes must be padded to 256 rows for both operands; the map over C
-// ({n, m, batch}, box 32 x 32, 128-byte swizzle) is read only when p.c_tma is set.
+// ({n, m, batch}; box and swizzle as p.c_tma says, see store_block) is read only when p.c_tma is set.
 bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk);
 
 }  // namespace cleave

@@ -167,6 +167,13 @@ class FusedDataParallel:
         self._done = [torch.cuda.Event() for _ in self._buckets]
         self._in_flight = [False] * len(self._buckets)
         self._torch = torch
+        # Lo planes of the weights (what the tensor-core products read beside W itself), refreshed on the side stream
+        # right after the exchange that rewrote the layer: the split of W1 / W2 leaves the step's critical path.
+        # _planes[b] belongs to bucket b's weight matrix; valid only after that bucket's first exchange.
+        self._planes = None
+        if len(self._buckets) == 2:
+            self._planes = [Tensor.empty(*self.net.W2.dims), Tensor.empty(*self.net.W1.dims)]
+        self._planes_version = [-1, -1]   # net.weights_version at the refresh; a load() or sgd() since makes a plane stale
 
     def _exchange(self, b: int, lr: float, stream) -> None:
         from ._lib import lib, raise_last_error
@@ -210,13 +217,26 @@ class FusedDataParallel:
                 return
             self._launch(b, lr)
 
-        loss = self.net.forward_backward(X, T, on_grads_ready=on_ready, loss_out=loss_out, before_layer=before_layer)
+        planes = None
+        self._refresh_planes = self._planes is not None and self.net.chains_planes(X.dims[0])
+        if self._refresh_planes:
+            v = self.net.weights_version
+            planes = (self._planes[1] if self._planes_version[1] == v else None,
+                      self._planes[0] if self._planes_version[0] == v else None)
+        loss = self.net.forward_backward(X, T, on_grads_ready=on_ready, loss_out=loss_out, before_layer=before_layer,
+                                         weight_planes=planes)
         return loss
 
     def _launch(self, b: int, lr: float) -> None:
+        from ._lib import lib, raise_last_error
         self._ready[b].record(self._main)
         self._side.wait_event(self._ready[b])
         self._exchange(b, lr, self._side)
+        if self._planes is not None and getattr(self, "_refresh_planes", False):
+            w = self.net.W2 if b == 0 else self.net.W1
+            if lib().cleave_cuda_split_lo_into_f32(self._planes[b]._h, w._h, ctypes.c_void_p(self._side.cuda_stream)) != 0:
+                raise_last_error("split_lo_into")
+            self._planes_version[b] = self.net.weights_version
         self._done[b].record(self._side)
         self._in_flight[b] = True
 

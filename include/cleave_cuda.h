@@ -92,10 +92,14 @@ double cleave_cuda_profile_end(int32_t* launches);
  * launches anything.  Selectors: */
 enum {
   CLEAVE_HOOK_SET_DEVICE_STATUS = 1,   /* arg = status code: as if a kernel's bounded wait had run out */
-  CLEAVE_HOOK_POISON_NOALLOC_WORD = 2, /* arg = 64-bit value stored into cleave_cuda_sum_noalloc_f32's completion word */
+  CLEAVE_HOOK_POISON_NOALLOC_WORD = 2, /* arg = 64-bit value stored over cleave_cuda_sum_noalloc_f32's completion counter */
   CLEAVE_HOOK_GUARD_FAILURES = 3       /* returns the number of guard-byte mismatches seen so far (debug mode) */
 };
 int64_t cleave_cuda_test_hook(int32_t what, int64_t arg);
+/* Host arithmetic of the batched GEMM paths, exposed so that it can be checked without a device: how many batch
+ * entries one pass processes given the operand workspace one entry needs (bounded by the workspace limit, by
+ * `batch`, and by the 65535 entries a grid's z dimension can index). */
+int32_t cleave_cuda_gemm_batch_chunk(int64_t workspace_bytes_per_entry, int32_t batch);
 void* cleave_cuda_host_alloc(int64_t bytes);         /* pinned host memory for fast transfers */
 void cleave_cuda_host_free(void* p);
 
@@ -168,9 +172,10 @@ float cleave_cuda_max_f32(cleave_buf v);
  * CLEAVE_CUDA_ERR_UNSUPPORTED).  The first call on each device looks up the array's device
  * address, so make that first call outside any stream capture.  All calls on one device share
  * the array: calls whose kernels may overlap on the GPU (different streams) race on it and their
- * results are undefined; calls on one stream do not.  The completion word is keyed by a per-call ticket,
- * so a call that was cut short (or an overlapped pair) leaves nothing behind that a later, properly
- * ordered call could trip over.  The value equals cleave_cuda_sum_f32 of the same data bit for bit.
+ * results are undefined; calls on one stream do not.  Every call clears its completion counter on its own
+ * stream before the kernel (a memset node, no allocation), so a call that was cut short (or an overlapped
+ * pair) leaves nothing behind that a later, properly ordered call could trip over.  The value equals
+ * cleave_cuda_sum_f32 of the same data bit for bit.
  * It uses no handle and no pool, never calls cudaMalloc or cudaFree, and takes from the library context
  * only the SM count.  x_dev must stay valid until the kernel has run: when it comes from
  * cleave_cuda_data_ptr and the call is on a stream other than the library's, do not free the handle
@@ -226,6 +231,11 @@ int32_t cleave_cuda_gemm_fused_f32(cleave_buf c, cleave_buf a, cleave_buf b, int
 /* The lo plane of a tensor in one streaming pass: lo[i] = tf32-rounded (x[i] - x[i] with its 13 low mantissa
  * bits cleared), the part of x the tensor pipe drops when it reads x as tf32. */
 cleave_buf cleave_cuda_split_lo_f32(cleave_buf x);
+/* The same into a plane the caller owns, queued on cuda_stream (NULL = the library's stream): a data-parallel
+ * driver refreshes the weights' planes on the stream of its exchange kernel, off the training step's critical
+ * path.  On a foreign stream the caller orders the call against the library's work (events), as for
+ * cleave_cuda_dp_sgd_allreduce_f32. */
+int32_t cleave_cuda_split_lo_into_f32(cleave_buf lo, cleave_buf x, void* cuda_stream);
 
 /* ------------------------------------------------------------------ compositions the programs spell out
  * bias add: a rows x cols tensor plus a tensor whose rows all equal `bias`

@@ -13,20 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
-def main():
-    import torch
-    import torch.distributed as dist
-
-    import cleave_b200 as cb
-    from cleave_b200 import autodiff, dp, linalg, workloads
-    from oracle import ref
-
-    rank, world, local = (int(os.environ[k]) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    assert cb.lib().cleave_cuda_init(local) == 0
-    dp.use_torch_stream()
-    d_in, d_hid, d_out, gb, steps, lr = 64, 256, 32, 512, 6, 0.5
+def train_and_check(torch, dist, cb, autodiff, dp, linalg, workloads, ref, rank, world, d_in, d_hid, d_out, gb, steps, lr):
     _, W1, b1, W2, b2, _ = workloads.mlp_inputs(1, d_in, d_hid, d_out)
     n_params = d_in * d_hid + d_hid + d_hid * d_out + d_out
     for overlap in ("nccl", "nccl-overlap", "fused-p2p", "fused-multimem"):
@@ -65,6 +52,25 @@ def main():
         assert err <= 1e-5, f"mode={overlap}: parameters differ from whole-batch training by {err}"
         if rank == 0:
             print(f"{overlap}: ok, max deviation from whole-batch training {err:.2e}", flush=True)
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+
+    import cleave_b200 as cb
+    from cleave_b200 import autodiff, dp, linalg, workloads
+    from oracle import ref
+
+    rank, world, local = (int(os.environ[k]) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    assert cb.lib().cleave_cuda_init(local) == 0
+    dp.use_torch_stream()
+    # a small network (exact GEMM path) and one large enough for the tensor-core path with lo planes handed from
+    # product to product and the weights' planes refreshed on the exchange stream
+    for (d_in, d_hid, d_out, gb, steps, lr) in ((64, 256, 32, 512, 6, 0.5), (256, 512, 128, 512 * world, 5, 0.5)):
+        train_and_check(torch, dist, cb, autodiff, dp, linalg, workloads, ref, rank, world, d_in, d_hid, d_out, gb, steps, lr)
     # row-block sharded GEMM with B broadcast into local HBM
     m, n, k = 1024, 512, 256
     a, b = workloads.gemm_inputs(m, n, k)

@@ -113,11 +113,12 @@ def test_transposed_and_batched_matmul_are_bit_identical_to_the_reference_loop(m
     rng = np.random.default_rng(m + n + k)
     a, b = rng.uniform(-1, 1, (m, k)), rng.uniform(-1, 1, (k, n))
     want = ref.matmul64(a, b)
-    at, bt = T(np.ascontiguousarray(a.T)), T(np.ascontiguousarray(b.T))
-    assert np.array_equal(_wrap(L.cleave_cuda_gemm_tn_f64(at._h, T(b)._h, m, n, k), m, n).numpy(), want)
-    assert np.array_equal(_wrap(L.cleave_cuda_gemm_nt_f64(T(a)._h, bt._h, m, n, k), m, n).numpy(), want)
+    ta, tb, at, bt = T(a), T(b), T(np.ascontiguousarray(a.T)), T(np.ascontiguousarray(b.T))   # keep the handles alive
+    assert np.array_equal(_wrap(L.cleave_cuda_gemm_tn_f64(at._h, tb._h, m, n, k), m, n).numpy(), want)
+    assert np.array_equal(_wrap(L.cleave_cuda_gemm_nt_f64(ta._h, bt._h, m, n, k), m, n).numpy(), want)
     A, B = rng.uniform(-1, 1, (3, m, k)), rng.uniform(-1, 1, (3, k, n))
-    got = _wrap(L.cleave_cuda_gemm_batched_f64(T(A)._h, T(B)._h, 3, m, n, k), 3, m, n).numpy()
+    tA, tB = T(A), T(B)
+    got = _wrap(L.cleave_cuda_gemm_batched_f64(tA._h, tB._h, 3, m, n, k), 3, m, n).numpy()
     for i in range(3):
         assert np.array_equal(got[i], ref.matmul64(A[i], B[i]))
 
@@ -126,15 +127,17 @@ def test_colsum_and_mse():
     L = cb.lib()
     rng = np.random.default_rng(9)
     x = rng.standard_normal((1000, 333))
-    got = _wrap(L.cleave_cuda_colsum_f64(T(x)._h, 1000, 333), 333).numpy()
+    tx = T(x)
+    got = _wrap(L.cleave_cuda_colsum_f64(tx._h, 1000, 333), 333).numpy()
     assert np.max(np.abs(got - x.sum(axis=0)) / np.abs(x).sum(axis=0)) <= 1e-14
     p, t = rng.uniform(0, 1, 100003), rng.uniform(0, 1, 100003)
     d = linalg.Tensor.zero(100003, dtype="f64")
-    loss = L.cleave_cuda_mse_f64(T(p)._h, T(t)._h, d._h)
+    tp, tt, short = T(p), T(t), T(t[:5])
+    loss = L.cleave_cuda_mse_f64(tp._h, tt._h, d._h)
     e = ref.binary64("sub", p, t)
     assert abs(loss - np.mean(e * e)) <= 1e-14 * np.mean(e * e)
     want_d = ref.binary64("div", ref.binary64("mul", np.full(p.size, 2.0), e), np.full(p.size, float(p.size)))
     assert np.array_equal(d.numpy(), want_d)
-    assert L.cleave_cuda_mse_f64(T(p)._h, T(t[:5])._h, None) != L.cleave_cuda_mse_f64(T(p)._h, T(t[:5])._h, None)  # NaN
+    assert np.isnan(L.cleave_cuda_mse_f64(tp._h, short._h, None))
     assert L.cleave_cuda_last_error() == 3
     L.cleave_cuda_clear_error()

@@ -110,7 +110,8 @@ def test_chained_perceptron_step_is_bit_identical_to_the_unchained_one(batch, d_
         out.append((loss, net.grads.numpy().copy()))
     assert out[0][0] == out[1][0]
     assert np.array_equal(out[0][1], out[1][1])
-    assert launches[1] == 11, launches      # 3 plane passes, 5 products, the loss pass, 2 column sums
+    # the chained step adds at most the three plane passes over X, W1 and W2 (the other planes leave epilogues)
+    assert launches[1] <= launches[0] + 3, launches
     want = ref.mlp2_fwd_bwd(X, W1, b1, W2, b2, T)
     absX = np.abs(X).astype(np.float64)
     adZ1 = np.abs(want["dZ1"]).astype(np.float64)

@@ -89,3 +89,23 @@ def test_shard_properties_hold_for_arbitrary_sizes():
         assert owned == list(range(min(n, 500)))
 
     check()
+
+
+def test_batch_chunking_respects_workspace_batch_and_grid_limits():
+    # entries per pass = min(workspace limit / bytes per entry, batch, 65535), at least 1
+    import os
+
+    import cleave_b200 as cb
+    L = cb.lib()
+    os.environ.pop("CLEAVE_CUDA_GEMM_WORKSPACE_MB", None)
+    gib = 1 << 30
+    assert L.cleave_cuda_gemm_batch_chunk(128 << 20, 64) == 32          # 4 GiB / 128 MiB
+    assert L.cleave_cuda_gemm_batch_chunk(128 << 20, 20) == 20          # never more than the batch
+    assert L.cleave_cuda_gemm_batch_chunk(16 * gib, 7) == 1             # an entry larger than the limit still runs
+    assert L.cleave_cuda_gemm_batch_chunk(1024, 1 << 20) == 65535       # gridDim.z
+    assert L.cleave_cuda_gemm_batch_chunk(0, 5) == 5
+    os.environ["CLEAVE_CUDA_GEMM_WORKSPACE_MB"] = "1"
+    try:
+        assert L.cleave_cuda_gemm_batch_chunk(300 << 10, 64) == 3       # 1 MiB / 300 KiB
+    finally:
+        del os.environ["CLEAVE_CUDA_GEMM_WORKSPACE_MB"]

@@ -48,10 +48,9 @@ def test_sum_noalloc_matches_the_pooled_sum_on_two_calls_in_a_row():
 
 
 def test_sum_noalloc_recovers_from_a_stale_completion_word():
-    # A call whose kernel was cut short would leave its ticket and a partial count in the completion word behind
-    # the partials.  Such words are planted here from the host (the test hook copies 8 bytes into the array; it
-    # launches nothing): an old ticket with a count, all ones, and a count under ticket 0.  Every following call
-    # must still write its output, and the right one.
+    # A call whose kernel was cut short would leave a partial count in the completion counter behind the partials.
+    # Such values are planted here from the host (the test hook copies 8 bytes into the array; it launches
+    # nothing).  Every following call must still write its output, and the right one.
     L = cb.lib()
     rng = np.random.default_rng(11)
     data = rng.standard_normal(5_000_000).astype(np.float32)
