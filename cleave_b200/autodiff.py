@@ -147,7 +147,6 @@ class MLP2:
             return loss, dict(H=H, Y=Y, dZ2=dZ2, dH=dH, dZ1=dZ1)
         return loss
 
-    @staticmethod
     def chains_planes(self, batch: int) -> bool:
         """Whether a step at this batch size hands lo planes from product to product."""
         return bool(self.chain_lo and batch % 32 == 0 and batch * self.d_in * self.d_hid >= (1 << 24))
