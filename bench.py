@@ -51,9 +51,10 @@ FLOPS = 2.0 * M * N * K
 # DRAM traffic of one tcgen05 GEMM kernel launch at 8192^3: not measured by this program (it needs a
 # profiler) but taken from a one-pass ncu capture of it at full size (dram__bytes_read.sum +
 # dram__bytes_write.sum).  The record names the capture, so a value that no longer matches the kernel shows.
-NCU_TRAFFIC = {"bytes_per_launch": 7.599e9 + 277.6e6,
-               "kernel": "gemm_3xtf32_pair_kernel<0, 1, 32> (256x256 tiles on CTA pairs, K-block 32, 3 stages)",
-               "summary": "profiles/gemm_3xtf32_pair_kernel_8192x4096x4096_ncu_full.md"}
+NCU_TRAFFIC = {"bytes_per_launch": 4.633e9 + 268.3e6,
+               "kernel": "gemm_3xtf32_pair_kernel<0, 1, 32> (256x256 tiles on CTA pairs, K-block 32, 3 stages, "
+                         "tile-rows in groups of 8)",
+               "summary": "profiles/gemm_3xtf32_pair_kernel_8192cubed_group_size_and_traffic.md"}
 NCU_TRAFFIC_BYTES_PER_LAUNCH = NCU_TRAFFIC["bytes_per_launch"]
 NOMINAL_TF32_DENSE_TFLOPS = 1125.0   # datasheet, dense (half the 2:4-sparse figure), at the 1965 MHz boost clock
 

@@ -741,9 +741,16 @@ static bool addressable(const GemmArgs& g) {
 
 // Splitting in the kernel costs shared-memory bandwidth that the MMAs also need (measured: the kernel
 // runs ~1.2x longer); a pre-pass costs an HBM round trip over both operands.  The pre-pass is the
-// cheaper of the two once 1/M + 1/N drops below ~1/1300 (large, square-ish outputs).
+// cheaper of the two once 1/M + 1/N drops below ~1/1000 (large, square-ish outputs; CLEAVE_CUDA_GEMM_DIRECT_BELOW
+// moves the threshold for measurements).  At 2048^3 the lo-plane route wins (80 us against 88), at 4096 x 1024 x K4096
+// the two are level (161 / 162 us).
 static bool prefer_direct(const GemmArgs& g) {
-  return (int64_t)g.m * g.n < 1300ll * ((int64_t)g.m + g.n);
+  static const int64_t threshold = [] {
+    const char* e = getenv("CLEAVE_CUDA_GEMM_DIRECT_BELOW");
+    const long v = e ? atol(e) : 0;
+    return (int64_t)(v > 0 ? v : 1000);
+  }();
+  return (int64_t)g.m * g.n < threshold * ((int64_t)g.m + g.n);
 }
 
 // The lo-plane path fetches an MN-major operand as one blocked box, which needs whole 32-wide blocks.
@@ -1183,6 +1190,14 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     p.status = ctx().status_dev;
     if (pair) {
       p.mblks = Mp / 256;
+      // tile-rows per rasterisation group (CLEAVE_CUDA_GEMM_GROUP_M, 1 .. 64): the ~74 tiles in flight span
+      // group x (74 / group) panels of A and B; 8 x 9 is the squarest split
+      static const int group_m = [] {
+        const char* e = getenv("CLEAVE_CUDA_GEMM_GROUP_M");
+        const int v = e ? atoi(e) : 0;
+        return (v >= 1 && v <= 64) ? v : 8;
+      }();
+      p.pair_group_m = group_m;
       // full tiles leave through TMA stores when a tensor map can describe C
       // CLEAVE_CUDA_GEMM_TMA_STORE: 0 = the warps' own stores, 1 = 32 x 32 bulk stores one at a time, 2 = 32 x 16
       // bulk stores, two in flight

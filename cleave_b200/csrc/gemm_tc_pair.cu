@@ -30,7 +30,6 @@ struct PairCfg {
   static constexpr int kStageBytes = 4 * kPlaneBytes;      // [A hi | A lo | B hi | B lo]
   static constexpr int kStages = kRingBytesPair / kStageBytes;   // 6 (BK 16) or 3 (BK 32)
 };
-constexpr int kPairGroupM = 8;                             // 256-row tile-rows per rasterisation group
 constexpr int kPairSmemBytes = kRingBytesPair + kEpiWarps * 32 * 128 + 1024;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -88,15 +87,15 @@ __host__ __device__ constexpr uint32_t instr_desc_pair(bool a_mn, bool b_mn) {
          ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
-// Tile index -> (batch, 256-row tile-row, 256-column tile-column), tile-rows in groups of kPairGroupM.
+// Tile index -> (batch, 256-row tile-row, 256-column tile-column), tile-rows in groups of p.pair_group_m.
 __device__ __forceinline__ void decode_pair_tile(int t, const TcParams& p, int& b, int& mb, int& nb) {
   const int per_batch = p.mblks * p.nblks;
   b = t / per_batch;
   int r = t - b * per_batch;
-  const int group_span = kPairGroupM * p.nblks;
+  const int group_span = p.pair_group_m * p.nblks;
   const int gid = r / group_span;
-  const int first_m = gid * kPairGroupM;
-  const int rows_here = (p.mblks - first_m) < kPairGroupM ? (p.mblks - first_m) : kPairGroupM;
+  const int first_m = gid * p.pair_group_m;
+  const int rows_here = (p.mblks - first_m) < p.pair_group_m ? (p.mblks - first_m) : p.pair_group_m;
   r -= gid * group_span;
   mb = first_m + r % rows_here;
   nb = r / rows_here;

@@ -208,6 +208,7 @@ struct TcParams {
   int b_box_rows;             // direct path: rows of B fetched and split per stage (BN, less when n is small)
   int b_sliced;               // direct path: B is a K-sliced view, map dimensions {k, slice, row}
   int a_sliced = 0;           // direct path: the same for a K-major A
+  int pair_group_m = 8;       // pair kernel: 256-row tile-rows per rasterisation group
   int c_tma;                  // pair kernel: a tensor map over C exists (16-byte aligned, n a multiple of 4): TMA stores
                               // of 32 x 32 blocks (1) or of 32 x 16 blocks, two in flight (2)
   DeviceStatus* status;
