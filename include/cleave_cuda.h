@@ -201,7 +201,9 @@ cleave_buf cleave_cuda_gemm_batched_f32(cleave_buf a, cleave_buf b, int32_t batc
                                         int32_t k);
 /* General form: writes C (caller-owned, batch*m*n elements).  trans_a / trans_b select the
  * stored layout of the operands as above; algo is a CLEAVE_GEMM_* value; bias (may be NULL,
- * n elements) is added to every row and act (CLEAVE_ACT_*) applied before the store. */
+ * n elements) is added to every row and act (CLEAVE_ACT_*) applied before the store.  On the tensor-core path
+ * the sigmoid of the epilogue uses the hardware exponential and reciprocal: within a few ulp (3e-7 relative) of
+ * cleave_cuda_sigmoid_f32 applied to the same sums, not bit-identical to it; tanh and relu are the same functions. */
 int32_t cleave_cuda_gemm_ex_f32(cleave_buf c, cleave_buf a, cleave_buf b, int32_t batch, int32_t m,
                                 int32_t n, int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo,
                                 cleave_buf bias, int32_t act);
