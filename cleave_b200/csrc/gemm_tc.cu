@@ -510,6 +510,30 @@ __global__ void __launch_bounds__(256, 4) split_lo_kernel(const float4* __restri
   }
 }
 
+// The same for the two operands of one product in a single launch (blockIdx.y selects the operand): saves the
+// second launch's ramp, which at 2048^3 is a quarter of the pre-pass.
+__global__ void __launch_bounds__(256, 4) split_lo2_kernel(const float4* __restrict__ src0, float4* __restrict__ dst0,
+                                                           int64_t n0, const float4* __restrict__ src1,
+                                                           float4* __restrict__ dst1, int64_t n1) {
+  const float4* src = blockIdx.y ? src1 : src0;
+  float4* dst = blockIdx.y ? dst1 : dst0;
+  const int64_t n4 = blockIdx.y ? n1 : n0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n4; i += 4 * stride) {
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __ldcs(src + i + j * stride);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      dst[i + j * stride] = make_float4(split_lo(v[j].x), split_lo(v[j].y), split_lo(v[j].z), split_lo(v[j].w));
+  }
+  for (; i < n4; i += stride) {
+    const float4 v = __ldcs(src + i);
+    dst[i] = make_float4(split_lo(v.x), split_lo(v.y), split_lo(v.z), split_lo(v.w));
+  }
+}
+
 __global__ void split_lo_scalar_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t n) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
     dst[i] = split_lo(src[i]);
@@ -1047,8 +1071,21 @@ static bool launch_lo_plane(const GemmArgs& g) {
     const float* b = g.b + b0 * b_elems;
     const float* a_lo = g.a_lo ? g.a_lo + b0 * a_elems : wa;
     const float* b_lo = g.b_lo ? g.b_lo + b0 * b_elems : wb;
-    if (!g.a_lo) ok = split_lo_plane(a, wa, nb * a_elems);
-    if (ok && !g.b_lo) ok = split_lo_plane(b, wb, nb * b_elems);
+    if (!g.a_lo && !g.b_lo) {
+      // both planes in one launch (the operands of this route are 16-byte aligned, their sizes multiples of 4)
+      const int64_t a4 = nb * a_elems / 4, b4 = nb * b_elems / 4;
+      const int64_t per_operand = (a4 > b4 ? a4 : b4);
+      int grid = stream_grid((per_operand + 3) / 4, 256, 2);
+      split_lo2_kernel<<<dim3(grid, 2), 256, 0, ctx().stream>>>(reinterpret_cast<const float4*>(a),
+                                                                 reinterpret_cast<float4*>(wa), a4,
+                                                                 reinterpret_cast<const float4*>(b),
+                                                                 reinterpret_cast<float4*>(wb), b4);
+      count_launch();
+      ok = cuda_ok(cudaGetLastError(), "lo-plane split launch");
+    } else {
+      if (!g.a_lo) ok = split_lo_plane(a, wa, nb * a_elems);
+      if (ok && !g.b_lo) ok = split_lo_plane(b, wb, nb * b_elems);
+    }
     if (!ok) break;
     CUtensorMap maps[4];
     ok = make_direct_map(&maps[0], a, g.m, g.k, nb, !a_mn, BM, a_mn) &&

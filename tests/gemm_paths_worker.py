@@ -2,7 +2,8 @@
 
 Started by test_gpu_gemm_paths.py with CLEAVE_CUDA_GEMM_DIRECT set, because the library reads that
 switch once per process: 0 sends every problem through the padded-planes pre-pass, 2 makes the kernel
-split every operand that TMA can address, 3 uses the lo-plane pre-pass wherever it applies.  Prints one line ``OK <cases> <gemm calls> <calls TMA cannot address> <kernel launches>`` on success.
+split every operand that TMA can address, 3 uses the lo-plane pre-pass wherever it applies.  Prints one line
+``OK <cases> <gemm calls> <calls TMA cannot address> <kernel launches> <calls the lo-plane route can serve>`` on success.
 """
 import os
 import sys
@@ -29,13 +30,18 @@ SHAPES = [(128, 256, 16), (128, 256, 64), (256, 512, 128), (100, 200, 52), (132,
           (129, 257, 33), (5, 300, 7)]
 
 
-CALLS = {"gemms": 0, "unaddressable": 0, "other": 0}
+CALLS = {"gemms": 0, "unaddressable": 0, "other": 0, "lo_eligible": 0}
 
 
 def run(a, b, trans_a=False, trans_b=False, bias=None, act="identity", batch=None):
     CALLS["gemms"] += 1
     # TMA needs every operand's contiguous extent to be a multiple of 4 elements (16 bytes)
     CALLS["unaddressable"] += int(a.shape[-1] % 4 != 0 or b.shape[-1] % 4 != 0)
+    # the lo-plane route also needs whole 32-wide blocks of an operand that is read row-index-contiguous
+    mm = a.shape[-1] if trans_a else a.shape[-2]
+    nn_ = b.shape[-2] if trans_b else b.shape[-1]
+    CALLS["lo_eligible"] += int(a.shape[-1] % 4 == 0 and b.shape[-1] % 4 == 0 and (not trans_a or mm % 32 == 0)
+                                and (trans_b or nn_ % 32 == 0))
     ta, tb = linalg.Tensor(a), linalg.Tensor(b)
     if batch is None:
         m = a.shape[1] if trans_a else a.shape[0]
@@ -85,6 +91,7 @@ def main() -> int:
     fused = linalg.gemm_into(linalg.Tensor.empty(256, 512), ta_, tb_, algo=GEMM_3XTF32, dact_of=ty_, dact="tanh")
     prod = linalg.gemm_into(linalg.Tensor.empty(256, 512), ta_, tb_, algo=GEMM_3XTF32)
     CALLS["gemms"] += 2
+    CALLS["lo_eligible"] += 2
     before = cb.lib().cleave_cuda_kernel_launches()
     two_step = nn.tanh_bwd(ty_, prod)
     CALLS["other"] = cb.lib().cleave_cuda_kernel_launches() - before      # not a GEMM launch
@@ -108,7 +115,8 @@ def main() -> int:
     got = run(a, b)
     assert np.isnan(got[3]).all() and not np.isnan(np.delete(got, 3, axis=0)).any()
     cases += 3
-    print("OK", cases, CALLS["gemms"], CALLS["unaddressable"], cb.lib().cleave_cuda_kernel_launches() - CALLS["other"])
+    print("OK", cases, CALLS["gemms"], CALLS["unaddressable"], cb.lib().cleave_cuda_kernel_launches() - CALLS["other"],
+          CALLS["lo_eligible"])
     return 0
 
 

@@ -22,8 +22,9 @@ def test_forced_operand_path(mode, pair, pair_bk):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     last = r.stdout.strip().splitlines()[-1].split()
     assert last[0] == "OK"
-    gemms, unaddressable, launches = int(last[2]), int(last[3]), int(last[4])
-    # both pre-pass paths (0: padded hi/lo planes, 3: lo planes) launch two split kernels and the
-    # GEMM; the direct path only the GEMM, except for operands that TMA cannot address, which
-    # take the padded planes
-    assert launches == (gemms + 2 * unaddressable if mode == "2" else 3 * gemms)
+    gemms, unaddressable, launches, lo_eligible = int(last[2]), int(last[3]), int(last[4]), int(last[5])
+    # the padded-planes path (0) launches two split kernels and the GEMM; the lo-plane path (3) one kernel that
+    # writes both planes and the GEMM, falling back to the padded planes where it cannot read the operands in
+    # place; the direct path (2) only the GEMM, except for operands that TMA cannot address
+    want = {"0": 3 * gemms, "2": gemms + 2 * unaddressable, "3": 2 * lo_eligible + 3 * (gemms - lo_eligible)}[mode]
+    assert launches == want
