@@ -723,7 +723,7 @@ static bool run_tc_layout(bool a_mn, bool b_mn, const CUtensorMap* maps, const T
 //   plain: dims {rows, K, batch}, box {32, BK, 1}; the kernel issues tile_rows/32 such boxes per stage.
 // Needs a 16-byte aligned base and a contiguous extent that is a multiple of 4 elements.
 static bool make_direct_map(CUtensorMap* map, const float* base, int rows, int K, int batch, bool k_contiguous,
-                            int tile_rows, bool blocked) {
+                            int tile_rows, bool blocked, int bk = 16) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) {
     set_error(CLEAVE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -735,17 +735,19 @@ static bool make_direct_map(CUtensorMap* map, const float* base, int rows, int K
   if (blocked) {
     cuuint64_t dims[4] = {32, (cuuint64_t)K, (cuuint64_t)(rows / 32), (cuuint64_t)batch};
     cuuint64_t strides[3] = {(cuuint64_t)rows * 4, 128, (cuuint64_t)rows * K * 4};
-    cuuint32_t box[4] = {32, 16, (cuuint32_t)(tile_rows / 32), 1};
+    cuuint32_t box[4] = {32, (cuuint32_t)bk, (cuuint32_t)(tile_rows / 32), 1};
     r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   } else {
     cuuint64_t dims[3] = {inner, outer, (cuuint64_t)batch};
     cuuint64_t strides[2] = {inner * 4, inner * outer * 4};
-    cuuint32_t box[3] = {k_contiguous ? 16u : 32u, k_contiguous ? (cuuint32_t)tile_rows : 16u, 1};
+    // K-major rows are bk * 4 bytes: 64-byte swizzle for bk 16, 128-byte swizzle for bk 32
+    cuuint32_t box[3] = {k_contiguous ? (cuuint32_t)bk : 32u, k_contiguous ? (cuuint32_t)tile_rows : (cuuint32_t)bk, 1};
     r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE,
-            k_contiguous ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+            k_contiguous ? (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)
+                         : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   }
   if (r != CUDA_SUCCESS) {
@@ -1047,6 +1049,8 @@ static bool launch_split_k(const GemmArgs& g, int slices) {
   return ok;
 }
 
+static bool make_c_map(CUtensorMap* map, float* c, int m, int n, int batch, int mode);
+
 // hi planes are the caller's tensors, lo planes come from one streaming pass per operand.
 static bool launch_lo_plane(const GemmArgs& g) {
   const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
@@ -1054,6 +1058,16 @@ static bool launch_lo_plane(const GemmArgs& g) {
   // planes the caller holds are used as they are; a missing one is written here, in chunks of the batch
   const int64_t scratch_per_entry = ((g.a_lo ? 0 : a_elems) + (g.b_lo ? 0 : b_elems)) * 4;
   const int chunk = scratch_per_entry ? gemm_batch_chunk(scratch_per_entry, g.batch) : (g.batch < 65535 ? g.batch : 65535);
+  // Larger outputs run their 256 x 256 tiles on CTA pairs (measured at 4096 x 4096 x K1024: 132 us against 144 us on
+  // single CTAs; level at 2048^3), unless padding to 256 would waste more than ~7 % of the tile area.
+  // CLEAVE_CUDA_GEMM_LO_PAIR = 0 / 1 forces the choice.
+  static const int lo_pair = [] {
+    const char* e = getenv("CLEAVE_CUDA_GEMM_LO_PAIR");
+    return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1;
+  }();
+  const int64_t padded = (int64_t)round_up(g.m, 256) * round_up(g.n, 256);
+  const bool pair = lo_pair >= 0 ? lo_pair == 1
+                                 : ((int64_t)g.m * g.n >= (1ll << 22) && padded * 100 <= (int64_t)g.m * g.n * 107);
   float* wa = nullptr;
   float* wb = nullptr;
   if (!g.a_lo) {
@@ -1087,6 +1101,38 @@ static bool launch_lo_plane(const GemmArgs& g) {
       if (ok && !g.b_lo) ok = split_lo_plane(b, wb, nb * b_elems);
     }
     if (!ok) break;
+    if (pair) {
+      // 256 x 256 tiles on CTA pairs: each CTA loads 128 rows of A and 128 of the tile's 256 rows of B, K-block 32
+      CUtensorMap pm[5];
+      ok = make_direct_map(&pm[0], a, g.m, g.k, nb, !a_mn, 128, a_mn, 32) &&
+           make_direct_map(&pm[1], b, g.n, g.k, nb, !b_mn, 128, b_mn, 32) &&
+           make_direct_map(&pm[3], a_lo, g.m, g.k, nb, !a_mn, 128, a_mn, 32) &&
+           make_direct_map(&pm[4], b_lo, g.n, g.k, nb, !b_mn, 128, b_mn, 32);
+      if (!ok) break;
+      TcParams p;
+      p.a_blocked = a_mn;
+      p.b_blocked = b_mn;
+      p.b_sliced = 0;
+      p.b_box_rows = BN;
+      p.c = g.c + (int64_t)b0 * g.m * g.n;
+      p.c_lo = g.c_lo ? g.c_lo + (int64_t)b0 * g.m * g.n : nullptr;
+      p.bias = g.bias;
+      p.dact_y = g.dact_y ? g.dact_y + (int64_t)b0 * g.m * g.n : nullptr;
+      p.dact = g.dact;
+      p.m = g.m;
+      p.n = g.n;
+      p.num_kb = ceil_div(g.k, 32);
+      p.chunk_kb = kChunkK / 32;
+      p.batch = nb;
+      p.mblks = ceil_div(g.m, 256);
+      p.nblks = ceil_div(g.n, 256);
+      p.act = g.act;
+      p.status = ctx().status_dev;
+      p.c_tma = (aligned16(p.c) && g.n % 4 == 0 && make_c_map(&pm[2], p.c, g.m, g.n, nb, 1)) ? 1 : 0;
+      if (!p.c_tma) pm[2] = pm[0];
+      ok = run_tc_pair(a_mn, b_mn, pm, p, 32, true);
+      continue;
+    }
     CUtensorMap maps[4];
     ok = make_direct_map(&maps[0], a, g.m, g.k, nb, !a_mn, BM, a_mn) &&
          make_direct_map(&maps[1], b, g.n, g.k, nb, !b_mn, BN, b_mn) &&
@@ -1200,12 +1246,13 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
     ok = split_operand(a, wa, nb, g.m, g.k, Mp, Kp, g.trans_a == 0, a_mn) &&
          split_operand(b, wb, nb, g.n, g.k, Np, Kp, g.trans_b != 0, b_mn);
     if (!ok) break;
-    CUtensorMap maps[4];
+    CUtensorMap maps[5];
     ok = make_operand_map(&maps[0], wa, Mp, Kp, nb, bk, BM, a_mn) &&
          make_operand_map(&maps[1], wb, Np, Kp, nb, bk, pair ? 128 : BN, b_mn);
     if (!ok) break;
     maps[2] = maps[0];
     maps[3] = maps[1];
+    maps[4] = maps[1];
     TcParams p;
     p.c = g.c + (int64_t)b0 * g.m * g.n;
     p.c_lo = g.c_lo ? g.c_lo + (int64_t)b0 * g.m * g.n : nullptr;
@@ -1244,7 +1291,7 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
       }();
       p.c_tma = (tma_store && aligned16(p.c) && g.n % 4 == 0 && make_c_map(&maps[2], p.c, g.m, g.n, nb, tma_store))
                     ? tma_store : 0;
-      ok = run_tc_pair(a_mn, b_mn, maps, p, bk);
+      ok = run_tc_pair(a_mn, b_mn, maps, p, bk);   // maps[3] (a copy of maps[1]) and maps[4] are not read in this mode
     } else {
       ok = run_tc_layout<kPathPlanes>(a_mn, b_mn, maps, p);
     }

@@ -6,9 +6,14 @@
 // 128 rows in its own TMEM and drains it exactly as the one-CTA kernel does; full tiles are stored with TMA
 // (32-row x 16-column bulk tensor stores from the drain warps' swizzled staging tiles, two in flight), ragged ones with plain stores.
 //
-// Operands: the padded [hi | lo] planes of the pre-pass (both operands padded to 256 rows).  The K-block is a
-// template parameter: 32 (three stages of 64 KiB, K-major rows of 128 bytes in the 128-byte swizzle; the default,
-// ~3 % faster) or 16 (six stages of 32 KiB, 64-byte rows).
+// Operands, template parameter LO_PLANE:
+//   false  the padded [hi | lo] planes of the pre-pass (both operands padded to 256 rows): one TMA box per operand
+//          brings both planes
+//   true   hi = the caller's tensor read in place (out-of-range parts of a box read as zero, so nothing is padded),
+//          lo = a plane of the same layout (written by a one-pass pre-pass, by an earlier product's epilogue, or
+//          handed in by the caller): two boxes per operand, same shared-memory layout
+// The K-block is a template parameter: 32 (three stages of 64 KiB, K-major rows of 128 bytes in the 128-byte
+// swizzle; the default, ~3 % faster) or 16 (six stages of 32 KiB, 64-byte rows; padded planes only).
 //
 // Roles per CTA (320 threads): warp 0 producer, warp 1 MMA issuer (only in the cluster's CTA 0),
 // warps 2-9 drain + epilogue.  Signals:
@@ -101,10 +106,11 @@ __device__ __forceinline__ void decode_pair_tile(int t, const TcParams& p, int& 
   nb = r / rows_here;
 }
 
-template <bool A_MN, bool B_MN, int BK>
+template <bool A_MN, bool B_MN, int BK, bool LO_PLANE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        const __grid_constant__ CUtensorMap map_c, TcParams p) {
+                        const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_a_lo,
+                        const __grid_constant__ CUtensorMap map_b_lo, TcParams p) {
   constexpr int kPairStages = PairCfg<BK>::kStages;
   constexpr int kPairPlaneBytes = PairCfg<BK>::kPlaneBytes;
   constexpr int kPairStageBytes = PairCfg<BK>::kStageBytes;
@@ -155,6 +161,10 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      if constexpr (LO_PLANE) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a_lo) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b_lo) : "memory");
+      }
       int stage = 0;
       uint32_t phase = 0;
       uint32_t armed[kPairStages];
@@ -175,10 +185,28 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           const uint32_t full0 = map_to_cta(full_own, 0);
           if (rank == 0) mbar_arrive_expect_tx(full_own, 2 * kPairStageBytes);
           const uint32_t sa = ring + stage * kPairStageBytes, sb = sa + 2 * kPairPlaneBytes;
-          if (A_MN) tma_pair_load_4d(sa, &map_a, full0, 0, kb * BK, a_row0 / 32, b * 2);
-          else tma_pair_load_3d(sa, &map_a, full0, kb * BK, a_row0, b * 2);
-          if (B_MN) tma_pair_load_4d(sb, &map_b, full0, 0, kb * BK, b_row0 / 32, b * 2);
-          else tma_pair_load_3d(sb, &map_b, full0, kb * BK, b_row0, b * 2);
+          if constexpr (LO_PLANE) {
+            // hi from the caller's tensor, lo from the plane: same geometry, same coordinates, one plane each
+            if (A_MN) {
+              tma_pair_load_4d(sa, &map_a, full0, 0, kb * BK, a_row0 / 32, b);
+              tma_pair_load_4d(sa + kPairPlaneBytes, &map_a_lo, full0, 0, kb * BK, a_row0 / 32, b);
+            } else {
+              tma_pair_load_3d(sa, &map_a, full0, kb * BK, a_row0, b);
+              tma_pair_load_3d(sa + kPairPlaneBytes, &map_a_lo, full0, kb * BK, a_row0, b);
+            }
+            if (B_MN) {
+              tma_pair_load_4d(sb, &map_b, full0, 0, kb * BK, b_row0 / 32, b);
+              tma_pair_load_4d(sb + kPairPlaneBytes, &map_b_lo, full0, 0, kb * BK, b_row0 / 32, b);
+            } else {
+              tma_pair_load_3d(sb, &map_b, full0, kb * BK, b_row0, b);
+              tma_pair_load_3d(sb + kPairPlaneBytes, &map_b_lo, full0, kb * BK, b_row0, b);
+            }
+          } else {
+            if (A_MN) tma_pair_load_4d(sa, &map_a, full0, 0, kb * BK, a_row0 / 32, b * 2);
+            else tma_pair_load_3d(sa, &map_a, full0, kb * BK, a_row0, b * 2);
+            if (B_MN) tma_pair_load_4d(sb, &map_b, full0, 0, kb * BK, b_row0 / 32, b * 2);
+            else tma_pair_load_3d(sb, &map_b, full0, kb * BK, b_row0, b * 2);
+          }
 #pragma unroll
           for (int s = 0; s < kPairStages; ++s)
             if (s == stage) armed[s]++;
@@ -312,11 +340,11 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   }
 }
 
-template <bool A_MN, bool B_MN, int BK>
+template <bool A_MN, bool B_MN, int BK, bool LO_PLANE>
 static bool run_pair(const CUtensorMap* maps, const TcParams& p) {
   static bool attr_set = false;
   if (!attr_set) {
-    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_pair_kernel<A_MN, B_MN, BK>,
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_pair_kernel<A_MN, B_MN, BK, LO_PLANE>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes),
                  "cudaFuncSetAttribute(pair gemm)"))
       return false;
@@ -326,21 +354,23 @@ static bool run_pair(const CUtensorMap* maps, const TcParams& p) {
   int clusters = ctx().sm_count / 2;
   if (tiles < clusters) clusters = tiles;
   profile_mark(true);
-  gemm_3xtf32_pair_kernel<A_MN, B_MN, BK>
-      <<<2 * clusters, kGemmThreads, kPairSmemBytes, ctx().stream>>>(maps[0], maps[1], maps[2], p);
+  gemm_3xtf32_pair_kernel<A_MN, B_MN, BK, LO_PLANE>
+      <<<2 * clusters, kGemmThreads, kPairSmemBytes, ctx().stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   profile_mark(false);
   count_launch();
   return cuda_ok(cudaGetLastError(), "tcgen05 pair GEMM launch");
 }
 
-template <int BK>
+template <int BK, bool LO_PLANE>
 static bool run_pair_bk(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p) {
-  return a_mn ? (b_mn ? run_pair<true, true, BK>(maps, p) : run_pair<true, false, BK>(maps, p))
-              : (b_mn ? run_pair<false, true, BK>(maps, p) : run_pair<false, false, BK>(maps, p));
+  return a_mn ? (b_mn ? run_pair<true, true, BK, LO_PLANE>(maps, p) : run_pair<true, false, BK, LO_PLANE>(maps, p))
+              : (b_mn ? run_pair<false, true, BK, LO_PLANE>(maps, p) : run_pair<false, false, BK, LO_PLANE>(maps, p));
 }
 
-bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk) {
-  return bk == 32 ? run_pair_bk<32>(a_mn, b_mn, maps, p) : run_pair_bk<16>(a_mn, b_mn, maps, p);
+// maps = {A, B, C, A lo, B lo}; the last two are read in lo-plane mode only.
+bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk, bool lo_plane) {
+  if (lo_plane) return run_pair_bk<32, true>(a_mn, b_mn, maps, p);
+  return bk == 32 ? run_pair_bk<32, false>(a_mn, b_mn, maps, p) : run_pair_bk<16, false>(a_mn, b_mn, maps, p);
 }
 
 }  // namespace cleave

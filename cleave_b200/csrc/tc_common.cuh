@@ -460,6 +460,7 @@ __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcPara
 // Pair kernel (gemm_tc_pair.cu): two CTAs of a cluster share one 256 x 256 tile (tcgen05 cta_group::2).
 // `maps` = {A planes, B planes, C}; the planes must be padded to 256 rows for both operands; the map over C
 // ({n, m, batch}; box and swizzle as p.c_tma says, see store_block) is read only when p.c_tma is set.
-bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk);
+// In lo-plane mode `maps` = {A, B, C, A lo, B lo} over the caller's tensors and their lo planes (K-block 32).
+bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk, bool lo_plane = false);
 
 }  // namespace cleave

@@ -11,12 +11,13 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("mode,pair,pair_bk", [("0", "0", "32"), ("2", "0", "32"), ("3", "0", "32"), ("0", "1", "32"),
-                                                ("0", "1", "16")])
-def test_forced_operand_path(mode, pair, pair_bk):
+@pytest.mark.parametrize("mode,pair,pair_bk,lo_pair", [("0", "0", "32", "0"), ("2", "0", "32", "0"), ("3", "0", "32", "0"),
+                                                        ("0", "1", "32", "0"), ("0", "1", "16", "0"), ("3", "0", "32", "1")])
+def test_forced_operand_path(mode, pair, pair_bk, lo_pair):
     # pair = "1": the padded-planes path runs its 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2), with a
-    # K-block of 32 or 16
-    env = dict(os.environ, CLEAVE_CUDA_GEMM_DIRECT=mode, CLEAVE_CUDA_GEMM_PAIR=pair, CLEAVE_CUDA_GEMM_PAIR_BK=pair_bk)
+    # K-block of 32 or 16; lo_pair = "1": so does the lo-plane path, reading the caller's tensors in place
+    env = dict(os.environ, CLEAVE_CUDA_GEMM_DIRECT=mode, CLEAVE_CUDA_GEMM_PAIR=pair, CLEAVE_CUDA_GEMM_PAIR_BK=pair_bk,
+               CLEAVE_CUDA_GEMM_LO_PAIR=lo_pair)
     r = subprocess.run([sys.executable, os.path.join(HERE, "gemm_paths_worker.py")], env=env, capture_output=True,
                        text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
