@@ -111,3 +111,22 @@ def test_generated_rust_bindings_are_current_and_complete():
         text = f.read()
     for name in _declared_symbols():
         assert f"pub fn {name}(" in text and f'register_symbol("{name}"' in text, name
+
+
+def test_cleave_files_keep_const_generics_out_of_parameter_lists():
+    # cleave/src/grammar.pest:116 allows `const` only in generic_params (`impl<const N: i32> ...`, `fn f<const N: i32>`),
+    # never inside a parameter list; a top-level extern fn cannot be generic at all (cleave/tests/callgraph.rs:227-233).
+    base = os.path.join(ROOT, "cleave_b200", "cleave")
+    seen = 0
+    for dirpath, _, files in os.walk(base):
+        for fn in files:
+            if not fn.endswith(".cleave"):
+                continue
+            with open(os.path.join(dirpath, fn)) as f:
+                text = re.sub(r"//[^\n]*", "", f.read())
+            for name, params in re.findall(r"\bfn\s+(\w+)\s*(?:<[^>]*>)?\s*\(([^)]*)\)", text):
+                seen += 1
+                assert "const " not in params, f"{fn}: fn {name}({params.strip()})"
+            for decl in re.findall(r"^\s*extern\s+fn\s+\w+\s*<", text, flags=re.M):
+                raise AssertionError(f"{fn}: generic top-level extern fn: {decl.strip()}")
+    assert seen > 60
