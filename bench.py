@@ -393,6 +393,9 @@ def run_ops(args):
                                          stream) != 0:
             cb._lib.raise_last_error("sum_noalloc")
     cases["sum_device_result"] = (sum_dev, 4 * n)
+    loss_dev = linalg.Tensor.zero(1)
+    # the loss kernel with its result left on the device: loss + gradient with respect to the pre-activation
+    cases["mse_sigmoid_bwd_device_result"] = (lambda i: nn.mse_act_bwd(Y[i], B[i], "sigmoid", loss_out=loss_dev), 12 * n)
     out = {}
     for name, (fn, nbytes) in cases.items():
         def rotation():

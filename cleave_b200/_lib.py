@@ -38,6 +38,7 @@ SIGNATURES = {
     "cleave_cuda_profile_end": (ctypes.c_double, [ctypes.POINTER(i32)]),
     "cleave_cuda_host_alloc": (ctypes.c_void_p, [i64]),
     "cleave_cuda_host_free": (None, [ctypes.c_void_p]),
+    "cleave_cuda_none": (c_buf, []),
     "cleave_cuda_alloc_f32": (c_buf, [i64]),
     "cleave_cuda_upload_f32": (c_buf, [c_f32p, i64]),
     "cleave_cuda_download_f32": (i64, [c_buf, c_f32p, i64]),

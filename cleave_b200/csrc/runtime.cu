@@ -522,6 +522,8 @@ void cleave_cuda_host_free(void* p) {
   if (p && g_ctx.ready) cudaFreeHost(p);
 }
 
+cleave_buf cleave_cuda_none(void) { return nullptr; }
+
 cleave_buf cleave_cuda_alloc_f32(int64_t len) {
   ApiLock lock;
   return (cleave_buf)new_buf(len);

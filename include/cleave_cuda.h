@@ -107,6 +107,8 @@ void cleave_cuda_host_free(void* p);
  * Replaces tensor.from_elements (mlir_lower.rs:1447-1476), the array-repeat fill behind
  * Ring::zero (stdlib/linalg/tensor.cleave:79, mlir_lower.rs:1176-1272) and tensor.extract
  * (stdlib/linalg/tensor.cleave:129-133, mlir_lower.rs:1972-2002). */
+cleave_buf cleave_cuda_none(void);   /* the absent operand: NULL.  cleave has no null literal for an opaque struct, so
+                                        optional handles (a bias, a lo plane) are spelled with this call */
 cleave_buf cleave_cuda_alloc_f32(int64_t len);                              /* uninitialised */
 cleave_buf cleave_cuda_upload_f32(const float* host, int64_t len);          /* [f32; len] -> device */
 int64_t cleave_cuda_download_f32(cleave_buf t, float* host, int64_t len);   /* returns len or <0 */
