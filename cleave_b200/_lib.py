@@ -121,6 +121,7 @@ SIGNATURES = {
     "cleave_cuda_dp_sgd_allreduce_f32": (i32, [ctypes.POINTER(ctypes.c_void_p)] * 3 + [ctypes.c_void_p, ctypes.c_void_p,
                                                 i64, i64, i32, i32, f32, ctypes.c_uint32, ctypes.c_void_p]),
     "cleave_cuda_linreg_step_f32": (f32, [c_buf, c_buf, c_buf, c_buf, c_buf, i32, i32]),
+    "cleave_cuda_linreg_step_dev_f32": (i32, [c_buf, c_buf, c_buf, c_buf, c_buf, i32, i32, c_buf]),
 }
 
 _lib = None

@@ -162,15 +162,23 @@ class MLP2:
         nn.sgd_step(self.params, self.grads, lr, gscale)
 
 
-def linreg_step(X: Tensor, y: Tensor, w: Tensor, want_pred: bool = True):
+def linreg_step(X: Tensor, y: Tensor, w: Tensor, want_pred: bool = True, loss_out: Tensor | None = None,
+                grad_out: Tensor | None = None, pred_out: Tensor | None = None):
     """Linear-regression batch gradient step in one sweep over ``X`` [rows, feat]:
     returns ``(loss, grad, pred)`` with loss = mean((X w - y)^2) and grad = dloss/dw
-    (examples/linear_regression.cleave:15-33 scaled to a real batch)."""
+    (examples/linear_regression.cleave:15-33 scaled to a real batch).  With ``loss_out`` (a one-element tensor)
+    the loss stays on the device, the call does not wait and the returned loss is ``None``; ``grad_out`` /
+    ``pred_out`` reuse the caller's tensors instead of allocating."""
     rows, feat = X.dims
     if y.dims != (rows,) or w.dims != (feat,):
         raise TypeError(f"linreg_step: X {X.dims}, y {y.dims}, w {w.dims}")
-    grad = Tensor.empty(feat)
-    pred = Tensor.empty(rows) if want_pred else None
+    grad = grad_out if grad_out is not None else Tensor.empty(feat)
+    pred = pred_out if pred_out is not None else (Tensor.empty(rows) if want_pred else None)
+    if loss_out is not None:
+        if lib().cleave_cuda_linreg_step_dev_f32(X._h, y._h, w._h, pred._h if pred is not None else None, grad._h,
+                                                 rows, feat, loss_out._h) != 0:
+            raise_last_error("linreg_step_dev")
+        return None, grad, pred
     loss = lib().cleave_cuda_linreg_step_f32(X._h, y._h, w._h, pred._h if pred is not None else None, grad._h,
                                              rows, feat)
     if math.isnan(loss) and lib().cleave_cuda_last_error():

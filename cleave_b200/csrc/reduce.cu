@@ -786,9 +786,20 @@ float cleave_cuda_mse_act_bwd_f32(cleave_buf y, cleave_buf t, cleave_buf dz, int
   return mse_impl(y, t, dz, act, "mse_act_bwd");
 }
 
-float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out, cleave_buf grad_out,
-                                  int32_t rows, int32_t feat) {
+// loss_dev == nullptr: the loss is returned (the call waits for it).  Otherwise it is written to that one-element
+// device tensor, nothing is waited for, and 0 is returned on success.
+static float linreg_impl(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out, cleave_buf grad_out, int32_t rows,
+                         int32_t feat, cleave_buf loss_dev) {
   ApiLock lock;
+  Buf* LO = nullptr;
+  if (loss_dev) {
+    LO = as_buf(loss_dev, "linreg_step");
+    if (!LO) return NAN;
+    if (LO->len != 1) {
+      set_error(CLEAVE_CUDA_ERR_SHAPE, "linreg_step: the loss output must be a one-element tensor");
+      return NAN;
+    }
+  }
   Buf* X = as_buf(x, "linreg_step");
   Buf* Y = as_buf(y, "linreg_step");
   Buf* W = as_buf(w, "linreg_step");
@@ -834,7 +845,7 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
   int ctas = (int)(((int64_t)rows + slab - 1) / slab);
   float* partials = scratch_alloc(((int64_t)((ctas + 3) & ~3) * (feat + 1) + 4) * sizeof(float));
   if (!partials) return NAN;
-  float* out = scalar_slot();
+  float* out = LO ? LO->ptr : scalar_slot();
   const float fn = (float)rows;
   cudaStream_t s = ctx().stream;
   float* pp = P ? P->ptr : nullptr;
@@ -853,9 +864,24 @@ float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, clea
   profile_mark(false);
   count_launch(1);
   float r = NAN;
-  if (cuda_ok(cudaGetLastError(), "linreg launch")) r = wait_scalar();
+  if (cuda_ok(cudaGetLastError(), "linreg launch")) r = LO ? 0.0f : wait_scalar();
   scratch_free(partials);
   return r;
+}
+
+float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out, cleave_buf grad_out,
+                                  int32_t rows, int32_t feat) {
+  return linreg_impl(x, y, w, pred_out, grad_out, rows, feat, nullptr);
+}
+
+int32_t cleave_cuda_linreg_step_dev_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out, cleave_buf grad_out,
+                                        int32_t rows, int32_t feat, cleave_buf loss_out) {
+  if (!loss_out) {
+    ApiLock lock;
+    return -set_error(CLEAVE_CUDA_ERR_ARG, "linreg_step_dev: the loss output handle is required");
+  }
+  const float r = linreg_impl(x, y, w, pred_out, grad_out, rows, feat, loss_out);
+  return r == 0.0f ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
 }
 
 }  // extern "C"

@@ -266,6 +266,10 @@ int32_t cleave_cuda_sgd_f32(cleave_buf w, cleave_buf g, float lr, float gscale);
  * (feat) are caller-owned handles; pred_out may be NULL.  feat <= 32.  Returns the loss. */
 float cleave_cuda_linreg_step_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out,
                                   cleave_buf grad_out, int32_t rows, int32_t feat);
+/* Same, but the loss goes to the one-element tensor loss_out and the call does not wait: gradient-descent loops
+ * queue step after step (grad_out feeds cleave_cuda_sgd_f32) and read the loss only when they log it. */
+int32_t cleave_cuda_linreg_step_dev_f32(cleave_buf x, cleave_buf y, cleave_buf w, cleave_buf pred_out,
+                                        cleave_buf grad_out, int32_t rows, int32_t feat, cleave_buf loss_out);
 
 /* ------------------------------------------------------------------ host-array forms (the lowering hook's targets)
  * What a name-based exception in lower_raw_mlir_op (cleave/src/mlir_lower.rs:2004-2068; the two existing ones

@@ -89,3 +89,16 @@ def test_linreg_step(rows, feat):
         # from the exact sum (3e-5 of the scale at a million rows), not by more
         drift = np.abs(want_grad - grad64) / scale
         assert np.all(np.abs(g - want_grad) / scale <= drift + TOL)
+
+
+def test_linreg_step_with_the_loss_left_on_the_device():
+    X = workloads.normal(31, 100003, 16)
+    y = workloads.normal(33, 100003)
+    w = workloads.normal(32, 16)
+    tX, ty, tw = linalg.Tensor(X), linalg.Tensor(y), linalg.Tensor(w)
+    loss, grad, pred = autodiff.linreg_step(tX, ty, tw)
+    loss_dev, g2, p2 = linalg.Tensor.zero(1), linalg.Tensor.empty(16), linalg.Tensor.empty(100003)
+    none, g, p = autodiff.linreg_step(tX, ty, tw, loss_out=loss_dev, grad_out=g2, pred_out=p2)
+    assert none is None and g is g2 and p is p2
+    assert loss_dev[0] == loss
+    assert np.array_equal(g2.numpy(), grad.numpy()) and np.array_equal(p2.numpy(), pred.numpy())
