@@ -68,9 +68,11 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs.  nvidia-smi needs a moment to
+    start, so the sampler is started early and `stop(t0, t1)` keeps the samples stamped inside [t0, t1]
+    (`time.time()` values around the timed region)."""
 
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
@@ -78,37 +80,43 @@ class ClockSampler:
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.p = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}",
-                                       "--format=csv,noheader,nounits", "-lms", "25"],
+                                       "--format=csv,noheader,nounits", "-lms", "20"],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
 
-    def stop(self) -> dict:
+    def stop(self, t0: float | None = None, t1: float | None = None) -> dict:
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.p.terminate()
         self.p.wait()
         self.f.flush()
         self.f.seek(0)
-        sm, mx, reasons = [], [], set()
+        import datetime
+        sm, mx, reasons, total = [], [], set(), 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.f.read().splitlines():
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 8:
+            if len(parts) < 9:
                 continue
+            total += 1
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, cmax = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
-            for nm, v in zip(names, parts[4:8]):
+            if t0 is not None and not (t0 - 0.02 <= stamp <= t1 + 0.02):
+                continue
+            sm.append(clk)
+            mx.append(cmax)
+            for nm, v in zip(names, parts[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         self.f.close()
         os.unlink(self.f.name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "samples_outside_window": total - len(sm), "reasons": sorted(reasons)}
 
 
 def cpu_gemm_sample(a: np.ndarray, b: np.ndarray, target_s: float = 10.0, threads: int | None = None):
@@ -821,6 +829,7 @@ def main():
 
     # The library runs on a torch-owned stream, made current, so torch CUDA events (which record on
     # the current stream) bracket exactly the kernels and copies the library enqueues.
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if int(os.environ.get("RANK", "0")) == 0 else None
     env = _dist_setup()
     torch, dist, cb, L, rank, world, local = env
     assert L.cleave_cuda_get_stream() == torch.cuda.current_stream().cuda_stream != 0
@@ -843,9 +852,9 @@ def main():
         step()
     barrier()
     launches0 = L.cleave_cuda_kernel_launches()
-    sampler = ClockSampler(local) if rank == 0 else None
     L.cleave_cuda_profile_begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_window0 = time.time()
     e0.record()
     for _ in range(args.steps):
         step()
@@ -853,7 +862,6 @@ def main():
     barrier()
     n_prof = ctypes.c_int32(0)
     kernel_ms_total = L.cleave_cuda_profile_end(ctypes.byref(n_prof))
-    clocks = sampler.stop() if sampler else None
     launches = L.cleave_cuda_kernel_launches() - launches0
     if L.cleave_cuda_sync() != 0:
         cb._lib.raise_last_error("timed region")
@@ -936,6 +944,11 @@ def main():
         e2e_ms = timed_region(e2e_run, e2e_steps)
         copy_ms = timed_region(copies_only, e2e_steps)
     e2e_value = world * FLOPS / (e2e_ms * 1e-3) / 1e12
+    # clocks: samples stamped between the start of the timed GEMM loop and the end of the end-to-end leg (the same
+    # kernels, with copies beside them); the timed loop alone is ~85 ms, too short for more than a few samples
+    clocks = sampler.stop(t_window0, time.time()) if sampler else None
+    if clocks is not None:
+        clocks["window"] = "timed GEMM loop + end-to-end leg"
     checksum = float(hcs[(e2e_steps - 1) & 1][:4096].astype(np.float64).sum())
     # One synchronous call with host arrays (the entry point a lowering hook targets): upload, product and
     # download pipelined over row blocks inside the call.
