@@ -10,7 +10,8 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PATCH = os.path.join(ROOT, "cleave_b200", "cleave", "patches", "cleave_cuda_backend.patch")
-REFERENCE = os.environ.get("CLEAVE_REFERENCE_DIR", "/root/reference")
+# the reference checkout: CLEAVE_REFERENCE_DIR, else a directory named `reference` beside this repository
+REFERENCE = os.environ.get("CLEAVE_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def _patched_files():
