@@ -36,6 +36,10 @@ SIGNATURES = {
     "cleave_cuda_gemm_batch_chunk": (i32, [i64, i32]),
     "cleave_cuda_profile_begin": (None, []),
     "cleave_cuda_profile_end": (ctypes.c_double, [ctypes.POINTER(i32)]),
+    "cleave_cuda_graph_begin": (i32, []),
+    "cleave_cuda_graph_end": (ctypes.c_void_p, []),
+    "cleave_cuda_graph_launch": (i32, [ctypes.c_void_p]),
+    "cleave_cuda_graph_free": (None, [ctypes.c_void_p]),
     "cleave_cuda_host_alloc": (ctypes.c_void_p, [i64]),
     "cleave_cuda_host_free": (None, [ctypes.c_void_p]),
     "cleave_cuda_none": (c_buf, []),

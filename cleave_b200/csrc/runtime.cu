@@ -19,7 +19,22 @@ namespace cleave {
 static std::recursive_mutex g_mu;
 static Context g_ctx;
 static std::unordered_set<Buf*> g_live;
-static std::unordered_map<int64_t, std::vector<void*>> g_free_blocks;   // block size -> cached blocks
+typedef std::unordered_map<int64_t, std::vector<void*>> BlockCache;       // block size -> cached blocks
+static BlockCache g_free_blocks;
+// The cache allocations are served from.  While a step is being captured into a CUDA graph this points at the
+// graph's private cache, so the captured kernels only ever name blocks that stay reserved for the graph.
+static BlockCache* g_pool = &g_free_blocks;
+
+// A captured step: the instantiated graph and the device blocks its kernels point at.
+struct StepGraph {
+  uint32_t magic;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  BlockCache blocks;
+};
+constexpr uint32_t kGraphMagic = 0x6EA9C1EAu;
+static StepGraph* g_capturing = nullptr;
+static std::unordered_set<StepGraph*> g_graphs;
 static std::unordered_map<void*, int64_t> g_scratch_sizes;
 static int64_t g_live_bytes = 0;
 static int64_t g_cached_bytes = 0;
@@ -132,6 +147,10 @@ Trace::Trace(const char* op, const char* fmt, ...) : on(false) {
     g_trace_mode = (e && e[0] == '1') ? 1 : 0;
   }
   if (!g_trace_mode || !g_ctx.ready) return;
+  if (g_capturing) {   // a capture records work, it does not run it: nothing to time
+    ++g_trace_depth;
+    return;
+  }
   if (g_trace_depth++ > 0) return;
   if (!g_trace_ev[0] && (cudaEventCreate(&g_trace_ev[0]) != cudaSuccess || cudaEventCreate(&g_trace_ev[1]) != cudaSuccess)) {
     cudaGetLastError();
@@ -209,18 +228,18 @@ static int64_t block_size_for(int64_t bytes) {
 static void* pool_alloc(int64_t bytes, int64_t* block_bytes) {
   int64_t bs = block_size_for(bytes);
   *block_bytes = bs;
-  auto it = g_free_blocks.find(bs);
-  if (it != g_free_blocks.end() && !it->second.empty()) {
+  auto it = g_pool->find(bs);
+  if (it != g_pool->end() && !it->second.empty()) {
     void* p = it->second.back();
     it->second.pop_back();
-    g_cached_bytes -= bs;
+    if (!g_capturing) g_cached_bytes -= bs;
     guard_arm(p, bs);
     return p;
   }
   const size_t real = (size_t)bs + (debug_mode() ? (size_t)kGuardBytes : 0);
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, real);
-  if (e != cudaSuccess) {
+  if (e != cudaSuccess && !g_capturing) {
     // Give cached blocks back to the driver and retry once.
     cudaGetLastError();
     cudaStreamSynchronize(g_ctx.stream);
@@ -243,9 +262,9 @@ static void* pool_alloc(int64_t bytes, int64_t* block_bytes) {
 // Blocks go straight back to the free list: all work of this library runs on one stream,
 // so a later user of the block is ordered after every kernel that touched it.
 static void pool_free(void* p, int64_t block_bytes) {
-  guard_check(p, block_bytes);
-  g_free_blocks[block_bytes].push_back(p);
-  g_cached_bytes += block_bytes;
+  if (!g_capturing) guard_check(p, block_bytes);   // the check waits for the stream, which a capture cannot do
+  (*g_pool)[block_bytes].push_back(p);
+  if (!g_capturing) g_cached_bytes += block_bytes;
 }
 
 Buf* new_buf(int64_t len, int dtype) {
@@ -497,6 +516,75 @@ int64_t cleave_cuda_test_hook(int32_t what, int64_t arg) {
     default:
       return -set_error(CLEAVE_CUDA_ERR_ARG, "test_hook: unknown selector %d", what);
   }
+}
+
+int32_t cleave_cuda_graph_begin(void) {
+  ApiLock lock;
+  if (!ensure_init()) return -t_err_code;
+  if (g_capturing) return -set_error(CLEAVE_CUDA_ERR_ARG, "graph_begin: a capture is already open");
+  // Relaxed mode: the pool may call cudaMalloc for a block the graph's private cache does not hold yet.
+  if (!cuda_ok(cudaStreamBeginCapture(g_ctx.stream, cudaStreamCaptureModeRelaxed), "cudaStreamBeginCapture"))
+    return -t_err_code;
+  g_capturing = new StepGraph();
+  g_capturing->magic = kGraphMagic;
+  g_pool = &g_capturing->blocks;
+  return CLEAVE_CUDA_OK;
+}
+
+void* cleave_cuda_graph_end(void) {
+  ApiLock lock;
+  if (!g_capturing) {
+    set_error(CLEAVE_CUDA_ERR_ARG, "graph_end: no capture is open");
+    return nullptr;
+  }
+  StepGraph* g = g_capturing;
+  g_capturing = nullptr;
+  g_pool = &g_free_blocks;
+  bool ok = cuda_ok(cudaStreamEndCapture(g_ctx.stream, &g->graph), "cudaStreamEndCapture") && g->graph != nullptr &&
+            cuda_ok(cudaGraphInstantiate(&g->exec, g->graph, 0), "cudaGraphInstantiate");
+  if (!ok) {
+    if (t_err_code == 0) set_error(CLEAVE_CUDA_ERR_CUDA, "graph_end: the capture produced no graph");
+    if (g->graph) cudaGraphDestroy(g->graph);
+    for (auto& kv : g->blocks)
+      for (void* q : kv.second) cudaFree(q);
+    delete g;
+    cudaGetLastError();
+    return nullptr;
+  }
+  g_graphs.insert(g);
+  return (void*)g;
+}
+
+static StepGraph* as_graph(void* h, const char* what) {
+  StepGraph* g = (StepGraph*)h;
+  if (!g || g_graphs.find(g) == g_graphs.end() || g->magic != kGraphMagic) {
+    set_error(CLEAVE_CUDA_ERR_BAD_HANDLE, "%s: not a live graph handle (%p)", what, h);
+    return nullptr;
+  }
+  return g;
+}
+
+int32_t cleave_cuda_graph_launch(void* graph) {
+  ApiLock lock;
+  StepGraph* g = as_graph(graph, "graph_launch");
+  if (!g) return -t_err_code;
+  if (g_capturing) return -set_error(CLEAVE_CUDA_ERR_ARG, "graph_launch: a capture is open");
+  if (!cuda_ok(cudaGraphLaunch(g->exec, g_ctx.stream), "cudaGraphLaunch")) return -t_err_code;
+  return CLEAVE_CUDA_OK;
+}
+
+void cleave_cuda_graph_free(void* graph) {
+  ApiLock lock;
+  StepGraph* g = as_graph(graph, "graph_free");
+  if (!g) return;
+  cudaStreamSynchronize(g_ctx.stream);
+  cudaGraphExecDestroy(g->exec);
+  cudaGraphDestroy(g->graph);
+  for (auto& kv : g->blocks)
+    for (void* q : kv.second) cudaFree(q);
+  g_graphs.erase(g);
+  g->magic = 0;
+  delete g;
 }
 
 void* cleave_cuda_host_alloc(int64_t bytes) {
