@@ -109,3 +109,8 @@ def test_batch_chunking_respects_workspace_batch_and_grid_limits():
         assert L.cleave_cuda_gemm_batch_chunk(300 << 10, 64) == 3       # 1 MiB / 300 KiB
     finally:
         del os.environ["CLEAVE_CUDA_GEMM_WORKSPACE_MB"]
+
+
+def test_the_absent_operand_is_a_null_handle():
+    import cleave_b200 as cb
+    assert cb.lib().cleave_cuda_none() is None
