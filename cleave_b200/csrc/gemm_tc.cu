@@ -1291,7 +1291,15 @@ bool launch_gemm_3xtf32(const GemmArgs& g) {
       }();
       p.c_tma = (tma_store && aligned16(p.c) && g.n % 4 == 0 && make_c_map(&maps[2], p.c, g.m, g.n, nb, tma_store))
                     ? tma_store : 0;
-      ok = run_tc_pair(a_mn, b_mn, maps, p, bk);   // maps[3] (a copy of maps[1]) and maps[4] are not read in this mode
+      // one accumulation chunk and nothing but the product: the variant with twice the drain warps
+      // (CLEAVE_CUDA_GEMM_SHORTK=0 turns it off)
+      static const bool shortk_on = !(getenv("CLEAVE_CUDA_GEMM_SHORTK") && getenv("CLEAVE_CUDA_GEMM_SHORTK")[0] == '0');
+      if (shortk_on && bk == 32 && Kp <= kChunkK && !g.bias && g.act == CLEAVE_ACT_IDENTITY && !g.dact_y && !g.c_lo) {
+        if (p.c_tma == 2) p.c_tma = make_c_map(&maps[2], p.c, g.m, g.n, nb, 1) ? 1 : 0;   // this variant stores 32 x 32 blocks
+        ok = run_tc_pair_shortk(a_mn, b_mn, maps, p);
+      } else {
+        ok = run_tc_pair(a_mn, b_mn, maps, p, bk);   // maps[3] (a copy of maps[1]) and maps[4] are not read in this mode
+      }
     } else {
       ok = run_tc_layout<kPathPlanes>(a_mn, b_mn, maps, p);
     }

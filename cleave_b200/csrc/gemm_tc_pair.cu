@@ -373,4 +373,274 @@ bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& 
   return bk == 32 ? run_pair_bk<32, false>(a_mn, b_mn, maps, p) : run_pair_bk<16, false>(a_mn, b_mn, maps, p);
 }
 
+// ---- short K ------------------------------------------------------------------------------------------------------
+// With K <= 256 a tile is one accumulation chunk: 2 us of MMAs at K = 64, against ~3.3 us that the memory system
+// needs for a CTA's 128 KiB of the tile when all SMs store at once, and in the kernel above the 8 drain warps
+// cannot start on the next accumulator before their last store has left (measured at 16384 x 16384 x K64: 4.7 us per
+// tile, tensor pipe 33 % busy, DRAM 41 %).  This variant has 16 drain warps in two groups of 8, one group per TMEM
+// accumulator: while one group stores tile t the other drains and stores tile t + 1, so the stores of a CTA never
+// pause.  No running sums (the single chunk goes from TMEM through a staging tile into a bulk store, 32 columns at a
+// time, the next TMEM load in flight meanwhile), hence few registers.  Shared memory: a two-stage ring (128 KiB; a
+// tile is at most 8 K-blocks and the MMAs of one tile overlap the loads of the next) + 64 KiB of staging tiles.
+// Plain products only (no bias, activation, derivative or lo-plane output); padded [hi | lo] planes, K-block 32.
+constexpr int kShortDrainWarps = 16;
+constexpr int kShortThreads = 64 + 32 * kShortDrainWarps;        // producer, issuer, 16 drain warps
+constexpr int kShortStages = 2;
+constexpr int kShortRingBytes = kShortStages * PairCfg<32>::kStageBytes;                    // 128 KiB
+constexpr int kShortSmemBytes = kShortRingBytes + kShortDrainWarps * 32 * 128 + 1024;
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kShortThreads, 1)
+gemm_3xtf32_pair_shortk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                               const __grid_constant__ CUtensorMap map_c, TcParams p) {
+  constexpr int BK = 32;
+  constexpr int kPlaneBytes = PairCfg<BK>::kPlaneBytes;
+  constexpr int kStageBytes = PairCfg<BK>::kStageBytes;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kShortStages];
+  __shared__ __align__(8) uint64_t bar_empty[kShortStages];
+  __shared__ __align__(8) uint64_t bar_tmem_full[kAccStages];
+  __shared__ __align__(8) uint64_t bar_tmem_empty[kAccStages];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int total_tiles = p.batch * p.mblks * p.nblks;
+  const int n_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kShortStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < kAccStages; ++a) {
+      mbar_init(smem_u32(&bar_tmem_full[a]), 1);
+      mbar_init(smem_u32(&bar_tmem_empty[a]), kShortDrainWarps);   // the 8 warps of its drain group, in both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed[kShortStages] = {0, 0};
+      bool ok = true;
+      for (int t = cluster_id; ok && t < total_tiles; t += n_clusters) {
+        int b, mb, nb;
+        decode_pair_tile(t, p, b, mb, nb);
+        const int a_row0 = mb * 256 + (int)rank * 128, b_row0 = nb * 256 + (int)rank * 128;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
+            report(p.status, 1, 100 + stage, kb);
+            ok = false;
+            break;
+          }
+          const uint32_t full_own = smem_u32(&bar_full[stage]);
+          const uint32_t full0 = map_to_cta(full_own, 0);
+          if (rank == 0) mbar_arrive_expect_tx(full_own, 2 * kStageBytes);
+          const uint32_t sa = ring + stage * kStageBytes, sb = sa + 2 * kPlaneBytes;
+          if (A_MN) tma_pair_load_4d(sa, &map_a, full0, 0, kb * BK, a_row0 / 32, b * 2);
+          else tma_pair_load_3d(sa, &map_a, full0, kb * BK, a_row0, b * 2);
+          if (B_MN) tma_pair_load_4d(sb, &map_b, full0, 0, kb * BK, b_row0 / 32, b * 2);
+          else tma_pair_load_3d(sb, &map_b, full0, kb * BK, b_row0, b * 2);
+          armed[stage]++;
+          if (++stage == kShortStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && rank == 0) {
+        for (int s = 0; s < kShortStages; ++s) {
+          if (armed[s] == 0) continue;
+          const uint32_t par = (armed[s] - 1u) & 1u;
+          for (int spin = 0; spin < (1 << 20); ++spin)
+            if (mbar_try_wait(smem_u32(&bar_full[s]), par)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (CTA 0 only): one chunk per tile
+    if (lane == 0 && rank == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      constexpr uint32_t idesc = instr_desc_pair(A_MN, B_MN);
+      for (int t = cluster_id; ok && t < total_tiles; t += n_clusters) {
+        if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
+          report(p.status, 2, 200 + acc, t);
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
+            report(p.status, 3, 300 + stage, kb);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_hi = ring + stage * kStageBytes;
+          const uint32_t a_lo = a_hi + kPlaneBytes;
+          const uint32_t b_hi = a_hi + 2 * kPlaneBytes;
+          const uint32_t b_lo = b_hi + kPlaneBytes;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint32_t off_a = A_MN ? kk * 1024 : kk * UMMA_K * 4;
+            const uint32_t off_b = B_MN ? kk * 1024 : kk * UMMA_K * 4;
+            constexpr uint32_t kmaj_sbo = 8 * BK * 4, kmaj_lay = 2u;
+            constexpr uint32_t sbo_a = A_MN ? 512u : kmaj_sbo, lay_a = A_MN ? 1u : kmaj_lay;
+            constexpr uint32_t sbo_b = B_MN ? 512u : kmaj_sbo, lay_b = B_MN ? 1u : kmaj_lay;
+            constexpr uint32_t lbo_a = A_MN ? BK * 128u : 16u, lbo_b = B_MN ? BK * 128u : 16u;
+            const uint64_t da_hi = make_smem_desc(a_hi + off_a, sbo_a, lay_a, lbo_a);
+            const uint64_t da_lo = make_smem_desc(a_lo + off_a, sbo_a, lay_a, lbo_a);
+            const uint64_t db_hi = make_smem_desc(b_hi + off_b, sbo_b, lay_b, lbo_b);
+            const uint64_t db_lo = make_smem_desc(b_lo + off_b, sbo_b, lay_b, lbo_b);
+            umma_tf32_pair(d_tmem, da_lo, db_hi, idesc, (kb != 0 || kk != 0) ? 1u : 0u);
+            umma_tf32_pair(d_tmem, da_hi, db_lo, idesc, 1u);
+            umma_tf32_pair(d_tmem, da_hi, db_hi, idesc, 1u);
+          }
+          tcgen05_commit_pair(smem_u32(&bar_empty[stage]));
+          if (++stage == kShortStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tcgen05_commit_pair(smem_u32(&bar_tmem_full[acc]));
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ drain + store: two groups of 8 warps
+    // Group g (warps 2 + 8g .. 9 + 8g) owns accumulator g and with it every second tile of the cluster; a warp takes
+    // 32 rows x 128 columns in four 32-column pieces, each from TMEM through its staging tile into a bulk store, and
+    // hands the accumulator back after the last TMEM load.
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int grp = (warp - 2) >> 3;              // accumulator / tile parity
+    const int half = ((warp - 2) >> 2) & 1;       // which 128 of the tile's 256 columns
+    uint32_t acc_phase = 0;
+    const bool vec_ok = (p.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0);
+    float4* stage_tile = reinterpret_cast<float4*>(smem_raw + (ring - smem_u32(smem_raw)) + kShortRingBytes) +
+                         (warp - 2) * (32 * 8);
+    const uint32_t stage_addr = smem_u32(stage_tile);
+    int i = 0;
+    for (int t = cluster_id; t < total_tiles; t += n_clusters, ++i) {
+      if ((i & 1) != grp) continue;
+      int b, mb, nb;
+      decode_pair_tile(t, p, b, mb, nb);
+      bool ok = mbar_wait(smem_u32(&bar_tmem_full[grp]), acc_phase, &abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, 4, 400 + grp, t);
+        break;
+      }
+      acc_phase ^= 1u;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * BN + half * 128);
+      const int tile_row0 = mb * 256 + (int)rank * 128;
+      const int row = tile_row0 + q * 32 + lane;
+      const int col0 = nb * 256 + half * 128;
+      const bool full_tile = (tile_row0 + 128 <= p.m) && (nb * 256 + 256 <= p.n);
+      const bool bulk = full_tile && p.c_tma;
+      float* crow = p.c + ((int64_t)b * p.m + row) * (int64_t)p.n + col0;
+      uint32_t r[2][32];
+      tmem_ld_32x32(taddr, r[0]);
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+        tmem_ld_wait_for(r[piece & 1]);                                   // piece `piece` has arrived
+        if (piece < 3) {
+          tmem_ld_32x32(taddr + (piece + 1) * 32, r[(piece + 1) & 1]);    // in flight while this piece is stored
+        } else {
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_tmem_empty[grp]), 0));
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(0.0f, __uint_as_float(r[piece & 1][j]));   // as the chunked kernels do
+        if (bulk) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            stage_tile[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile(
+                "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                ::"l"(&map_c), "r"(stage_addr), "r"(col0 + 32 * piece), "r"(tile_row0 + q * 32), "r"(b)
+                : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
+          __syncwarp();
+        } else if (row < p.m) {
+          const int c0 = col0 + 32 * piece;
+          if (vec_ok && c0 + 32 <= p.n) {
+            float4* dst = reinterpret_cast<float4*>(crow + 32 * piece);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < p.n) crow[32 * piece + j] = v[j];
+          }
+        }
+      }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static bool run_pair_shortk(const CUtensorMap* maps, const TcParams& p) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_pair_shortk_kernel<A_MN, B_MN>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kShortSmemBytes),
+                 "cudaFuncSetAttribute(short-K pair gemm)"))
+      return false;
+    attr_set = true;
+  }
+  const int tiles = p.batch * p.mblks * p.nblks;
+  int clusters = ctx().sm_count / 2;
+  if (tiles < clusters) clusters = tiles;
+  profile_mark(true);
+  gemm_3xtf32_pair_shortk_kernel<A_MN, B_MN>
+      <<<2 * clusters, kShortThreads, kShortSmemBytes, ctx().stream>>>(maps[0], maps[1], maps[2], p);
+  profile_mark(false);
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "tcgen05 short-K pair GEMM launch");
+}
+
+// Padded planes (K-block 32), one accumulation chunk (K_padded <= 256), plain product.  maps = {A planes, B planes, C}.
+bool run_tc_pair_shortk(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p) {
+  return a_mn ? (b_mn ? run_pair_shortk<true, true>(maps, p) : run_pair_shortk<true, false>(maps, p))
+              : (b_mn ? run_pair_shortk<false, true>(maps, p) : run_pair_shortk<false, false>(maps, p));
+}
+
 }  // namespace cleave

@@ -173,6 +173,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait for a load that was issued further back with other work in between: the registers pass through the
+// statement as in/out operands, so that no use of them can be scheduled above it.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 
 __device__ __forceinline__ float act_apply(float v, int act) {
   switch (act) {
@@ -462,5 +473,7 @@ __device__ __forceinline__ void tile_epilogue(float (&sum)[BN / 2], const TcPara
 // ({n, m, batch}; box and swizzle as p.c_tma says, see store_block) is read only when p.c_tma is set.
 // In lo-plane mode `maps` = {A, B, C, A lo, B lo} over the caller's tensors and their lo planes (K-block 32).
 bool run_tc_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p, int bk, bool lo_plane = false);
+// Short-K variant (K_padded <= 256, plain product, padded planes with K-block 32): 16 drain warps per CTA.
+bool run_tc_pair_shortk(bool a_mn, bool b_mn, const CUtensorMap* maps, const TcParams& p);
 
 }  // namespace cleave

@@ -3,8 +3,10 @@
 Started by test_gpu_gemm_paths.py with CLEAVE_CUDA_GEMM_DIRECT set, because the library reads that
 switch once per process: 0 sends every problem through the padded-planes pre-pass, 2 makes the kernel
 split every operand that TMA can address, 3 uses the lo-plane pre-pass wherever it applies.  Prints one line
-``OK <cases> <gemm calls> <calls TMA cannot address> <kernel launches> <calls the lo-plane route can serve>`` on success.
+``OK <cases> <gemm calls> <calls TMA cannot address> <kernel launches> <calls the lo-plane route can serve>
+<sha256 of every result's bytes>`` on success.
 """
+import hashlib
 import os
 import sys
 
@@ -30,6 +32,7 @@ SHAPES = [(128, 256, 16), (128, 256, 64), (256, 512, 128), (100, 200, 52), (132,
           (129, 257, 33), (5, 300, 7)]
 
 
+DIGEST = hashlib.sha256()
 CALLS = {"gemms": 0, "unaddressable": 0, "other": 0, "lo_eligible": 0}
 
 
@@ -52,7 +55,9 @@ def run(a, b, trans_a=False, trans_b=False, bias=None, act="identity", batch=Non
     linalg.gemm_into(c, ta, tb, trans_a=trans_a, trans_b=trans_b, algo=GEMM_3XTF32,
                      bias=linalg.Tensor(bias) if bias is not None else None, act=act)
     cb.sync()
-    return c.numpy()
+    out = c.numpy()
+    DIGEST.update(out.tobytes())
+    return out
 
 
 def main() -> int:
@@ -116,7 +121,7 @@ def main() -> int:
     assert np.isnan(got[3]).all() and not np.isnan(np.delete(got, 3, axis=0)).any()
     cases += 3
     print("OK", cases, CALLS["gemms"], CALLS["unaddressable"], cb.lib().cleave_cuda_kernel_launches() - CALLS["other"],
-          CALLS["lo_eligible"])
+          CALLS["lo_eligible"], DIGEST.hexdigest())
     return 0
 
 

@@ -29,3 +29,18 @@ def test_forced_operand_path(mode, pair, pair_bk, lo_pair):
     # place; the direct path (2) only the GEMM, except for operands that TMA cannot address
     want = {"0": 3 * gemms, "2": gemms + 2 * unaddressable, "3": 2 * lo_eligible + 3 * (gemms - lo_eligible)}[mode]
     assert launches == want
+
+
+def test_the_short_k_pair_kernel_gives_the_bits_of_the_general_one():
+    # K <= 256 without an epilogue runs on the pair kernel's variant with 16 drain warps; CLEAVE_CUDA_GEMM_SHORTK=0
+    # keeps the general kernel.  Same problems, both ways round: every result byte must agree.
+    digests = []
+    for shortk in ("1", "0"):
+        env = dict(os.environ, CLEAVE_CUDA_GEMM_DIRECT="0", CLEAVE_CUDA_GEMM_PAIR="1", CLEAVE_CUDA_GEMM_SHORTK=shortk)
+        r = subprocess.run([sys.executable, os.path.join(HERE, "gemm_paths_worker.py")], env=env, capture_output=True,
+                           text=True, timeout=900)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+        last = r.stdout.strip().splitlines()[-1].split()
+        assert last[0] == "OK"
+        digests.append(last[6])
+    assert digests[0] == digests[1]
