@@ -106,6 +106,60 @@ __device__ __forceinline__ void decode_pair_tile(int t, const TcParams& p, int& 
   nb = r / rows_here;
 }
 
+// ---- what a cluster works on ------------------------------------------------------------------------------------------
+// Whole tiles first: t = cluster + i * clusters over the tiles below the cut region.  The cut region is the last,
+// partly filled wave of a product whose tile count is not a multiple of the cluster count: each of its sk_tiles tiles
+// is cut along K into sk_slices equal runs of K-blocks and cluster c < sk_tiles * sk_slices takes run c / sk_tiles of
+// tile c % sk_tiles, leaving raw partial sums in slot c of p.sk_part; pair_streamk_fixup_kernel adds a tile's runs in
+// ascending K order.  All clusters walk K at the same pace, as in a full wave, so operand panels are still shared
+// through L2 (handing every cluster an equal share of one long K-block sequence instead -- stream-K proper -- was
+// measured slower: clusters then sit at unrelated K offsets and the panels come from DRAM again and again).  Which
+// cluster adds which K-blocks is a function of the shape alone, so the result is reproducible.
+struct PairItem {
+  int tile, kb0, kb1, slot;   // slot < 0: the whole K, result goes to C through the epilogue
+};
+__device__ __forceinline__ bool pair_item(const TcParams& p, int total_tiles, int cluster_id, int n_clusters, int idx,
+                                          PairItem& w) {
+  const int whole_tiles = total_tiles - p.sk_tiles;
+  const int n_whole = whole_tiles > cluster_id ? (whole_tiles - cluster_id + n_clusters - 1) / n_clusters : 0;
+  if (idx < n_whole) {
+    w.tile = cluster_id + idx * n_clusters;
+    w.kb0 = 0;
+    w.kb1 = p.num_kb;
+    w.slot = -1;
+    return true;
+  }
+  if (idx > n_whole || cluster_id >= p.sk_tiles * p.sk_slices) return false;
+  const int run = cluster_id / p.sk_tiles;
+  w.tile = whole_tiles + cluster_id % p.sk_tiles;
+  w.kb0 = (int)((long long)p.num_kb * run / p.sk_slices);
+  w.kb1 = (int)((long long)p.num_kb * (run + 1) / p.sk_slices);
+  w.slot = cluster_id;
+  return true;
+}
+
+// A drain warp's 32 rows x 128 columns of raw partial sums -> slot `slot` of the partial-sum workspace (a 256 x 256
+// tile; this CTA owns rows 128 * rank ..), through the warp's staging tile so that every store instruction writes
+// whole 128-byte lines.
+__device__ __forceinline__ void store_partial(const float (&sum)[BN / 2], float* ws, int slot, int rank, int q, int half,
+                                              int lane, float4* stage) {
+  float* block = ws + ((int64_t)slot * 256 + rank * 128 + q * 32) * 256 + half * 128;
+#pragma unroll
+  for (int pass = 0; pass < BN / 64; ++pass) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      stage[lane * 8 + (j ^ (lane & 7))] = make_float4(sum[32 * pass + 4 * j], sum[32 * pass + 4 * j + 1],
+                                                       sum[32 * pass + 4 * j + 2], sum[32 * pass + 4 * j + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = it * 4 + (lane >> 3), slot4 = lane & 7;
+      __stcg(reinterpret_cast<float4*>(block + r * 256 + 32 * pass + 4 * slot4), stage[r * 8 + (slot4 ^ (r & 7))]);
+    }
+    __syncwarp();
+  }
+}
+
 template <bool A_MN, bool B_MN, int BK, bool LO_PLANE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -171,11 +225,12 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 #pragma unroll
       for (int s = 0; s < kPairStages; ++s) armed[s] = 0;
       bool ok = true;
-      for (int t = cluster_id; ok && t < total_tiles; t += n_clusters) {
+      PairItem w;
+      for (int idx = 0; ok && pair_item(p, total_tiles, cluster_id, n_clusters, idx, w); ++idx) {
         int b, mb, nb;
-        decode_pair_tile(t, p, b, mb, nb);
+        decode_pair_tile(w.tile, p, b, mb, nb);
         const int a_row0 = mb * 256 + (int)rank * 128, b_row0 = nb * 256 + (int)rank * 128;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
             report(p.status, 1, 100 + stage, kb);
             ok = false;
@@ -233,16 +288,17 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       uint32_t acc_phase = 0;
       bool ok = true;
       constexpr uint32_t idesc = instr_desc_pair(A_MN, B_MN);
-      for (int t = cluster_id; ok && t < total_tiles; t += n_clusters) {
-        for (int kb0 = 0; ok && kb0 < p.num_kb; kb0 += p.chunk_kb) {
+      PairItem w;
+      for (int idx = 0; ok && pair_item(p, total_tiles, cluster_id, n_clusters, idx, w); ++idx) {
+        for (int kb0 = w.kb0; ok && kb0 < w.kb1; kb0 += p.chunk_kb) {
           if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
-            report(p.status, 2, 200 + acc, t);
+            report(p.status, 2, 200 + acc, w.tile);
             ok = false;
             break;
           }
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-          const int kb_end = (kb0 + p.chunk_kb) < p.num_kb ? (kb0 + p.chunk_kb) : p.num_kb;
+          const int kb_end = (kb0 + p.chunk_kb) < w.kb1 ? (kb0 + p.chunk_kb) : w.kb1;
           for (int kb = kb0; kb < kb_end; ++kb) {
             if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
               report(p.status, 3, 300 + stage, kb);
@@ -290,17 +346,18 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     float4* stage_tile = reinterpret_cast<float4*>(smem_raw + (ring - smem_u32(smem_raw)) + kRingBytesPair) +
                          (warp - 2) * (32 * 8);
     bool ok = true;
-    for (int t = cluster_id; ok && t < total_tiles; t += n_clusters) {
+    PairItem w;
+    for (int idx = 0; ok && pair_item(p, total_tiles, cluster_id, n_clusters, idx, w); ++idx) {
       int b, mb, nb;
-      decode_pair_tile(t, p, b, mb, nb);
+      decode_pair_tile(w.tile, p, b, mb, nb);
       float sum[BN / 2];
 #pragma unroll
       for (int j = 0; j < BN / 2; ++j) sum[j] = 0.0f;
-      for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.chunk_kb) {
+      for (int kb0 = w.kb0; kb0 < w.kb1; kb0 += p.chunk_kb) {
         ok = mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
-          if (lane == 0) report(p.status, 4, 400 + acc, t);
+          if (lane == 0) report(p.status, 4, 400 + acc, w.tile);
           break;
         }
         tcgen05_fence_after();
@@ -319,8 +376,11 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) break;
-      tile_epilogue(sum, p, b, mb * 256 + (int)rank * 128, nb, q, half, lane, vec_ok, stage_tile,
-                    p.c_tma ? &map_c : nullptr);
+      if (w.slot < 0)
+        tile_epilogue(sum, p, b, mb * 256 + (int)rank * 128, nb, q, half, lane, vec_ok, stage_tile,
+                      p.c_tma ? &map_c : nullptr);
+      else
+        store_partial(sum, p.sk_part, w.slot, (int)rank, q, half, lane, stage_tile);
     }
     // this warp's bulk stores have reached memory before the CTA may exit
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -340,8 +400,76 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   }
 }
 
+// Second pass of a product with a cut region: adds the K-runs of each cut tile in ascending K order and
+// applies the epilogue exactly as tile_epilogue does (same expressions).  grid = (8 bands of 32 rows, sk_tiles).
+__device__ __forceinline__ float sk_epilogue_value(float v, int act) {
+  if (act == CLEAVE_ACT_TANH) return tanhf(v);
+  if (act == CLEAVE_ACT_SIGMOID) return __fdividef(1.0f, 1.0f + __expf(-v));
+  if (act == CLEAVE_ACT_RELU) return act_apply(v, CLEAVE_ACT_RELU);
+  return v;
+}
+__global__ void __launch_bounds__(256) pair_streamk_fixup_kernel(TcParams p) {
+  const int r = blockIdx.y;
+  const int total_tiles = p.batch * p.mblks * p.nblks;
+  int b, mb, nb;
+  decode_pair_tile(total_tiles - p.sk_tiles + r, p, b, mb, nb);
+  const bool vec = (p.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) &&
+                   (p.c_lo == nullptr || (reinterpret_cast<uintptr_t>(p.c_lo) & 15u) == 0);
+#pragma unroll 2
+  for (int j = 0; j < 8; ++j) {
+    const int idx = threadIdx.x + 256 * j;          // 32 rows x 64 four-column groups
+    const int row_t = blockIdx.x * 32 + (idx >> 6), c4 = idx & 63;
+    const int grow = mb * 256 + row_t, gcol = nb * 256 + 4 * c4;
+    if (grow >= p.m || gcol >= p.n) continue;
+    const float4* part = reinterpret_cast<const float4*>(p.sk_part + ((int64_t)r * 256 + row_t) * 256) + c4;
+    float4 acc = __ldcg(part);
+    for (int run = 1; run < p.sk_slices; ++run) {
+      const float4 v = __ldcg(part + (int64_t)run * p.sk_tiles * (256 * 256 / 4));
+      acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+    }
+    float o[4] = {acc.x, acc.y, acc.z, acc.w};
+    const int64_t at = ((int64_t)b * p.m + grow) * (int64_t)p.n + gcol;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (gcol + e >= p.n) break;
+      if (p.bias != nullptr) o[e] = __fadd_rn(o[e], __ldg(p.bias + gcol + e));
+      o[e] = sk_epilogue_value(o[e], p.act);
+      if (p.dact_y != nullptr) o[e] = dact_apply(__ldg(p.dact_y + at + e), o[e], p.dact);
+    }
+    if (vec && gcol + 4 <= p.n) {
+      *reinterpret_cast<float4*>(p.c + at) = make_float4(o[0], o[1], o[2], o[3]);
+      if (p.c_lo != nullptr)
+        *reinterpret_cast<float4*>(p.c_lo + at) = make_float4(split_lo(o[0]), split_lo(o[1]), split_lo(o[2]), split_lo(o[3]));
+    } else {
+      for (int e = 0; e < 4 && gcol + e < p.n; ++e) {
+        p.c[at + e] = o[e];
+        if (p.c_lo != nullptr) p.c_lo[at + e] = split_lo(o[e]);
+      }
+    }
+  }
+}
+
+// Cut region for this launch: *slices = K-runs per tile (0: none), returns the tiles of the region.  It pays when the
+// last wave fills at most half of the SM pairs (so every tile gets at least two runs) and the K-blocks saved,
+// num_kb * (1 - 1/slices), clearly outweigh the second pass (~16 us, i.e. ~16 K-blocks of 32): at least 48.
+// CLEAVE_CUDA_GEMM_STREAMK=0 turns it off.
+static int cut_region(const TcParams& p, int sm_pairs, int* slices) {
+  static const bool on = !(getenv("CLEAVE_CUDA_GEMM_STREAMK") && getenv("CLEAVE_CUDA_GEMM_STREAMK")[0] == '0');
+  *slices = 0;
+  if (!on) return 0;
+  const int tiles = p.batch * p.mblks * p.nblks;
+  const int rem = tiles % sm_pairs;
+  if (tiles < sm_pairs || rem == 0) return 0;
+  int s = sm_pairs / rem;
+  if (s > 8) s = 8;
+  if (s < 2 || (int64_t)p.num_kb * (s - 1) < 48ll * s || p.num_kb / s < 8) return 0;
+  *slices = s;
+  return rem;
+}
+
 template <bool A_MN, bool B_MN, int BK, bool LO_PLANE>
-static bool run_pair(const CUtensorMap* maps, const TcParams& p) {
+static bool run_pair(const CUtensorMap* maps, const TcParams& p_in) {
   static bool attr_set = false;
   if (!attr_set) {
     if (!cuda_ok(cudaFuncSetAttribute(gemm_3xtf32_pair_kernel<A_MN, B_MN, BK, LO_PLANE>,
@@ -350,15 +478,28 @@ static bool run_pair(const CUtensorMap* maps, const TcParams& p) {
       return false;
     attr_set = true;
   }
+  TcParams p = p_in;
   const int tiles = p.batch * p.mblks * p.nblks;
-  int clusters = ctx().sm_count / 2;
-  if (tiles < clusters) clusters = tiles;
+  const int sm_pairs = ctx().sm_count / 2;
+  p.sk_tiles = cut_region(p, sm_pairs, &p.sk_slices);
+  const int clusters = tiles < sm_pairs ? tiles : sm_pairs;
+  if (p.sk_tiles) {
+    p.sk_part = scratch_alloc((int64_t)p.sk_tiles * p.sk_slices * 256 * 256 * sizeof(float));
+    if (!p.sk_part) return false;
+  }
   profile_mark(true);
   gemm_3xtf32_pair_kernel<A_MN, B_MN, BK, LO_PLANE>
       <<<2 * clusters, kGemmThreads, kPairSmemBytes, ctx().stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
-  profile_mark(false);
   count_launch();
-  return cuda_ok(cudaGetLastError(), "tcgen05 pair GEMM launch");
+  bool ok = cuda_ok(cudaGetLastError(), "tcgen05 pair GEMM launch");
+  if (ok && p.sk_tiles) {
+    pair_streamk_fixup_kernel<<<dim3(8, p.sk_tiles), 256, 0, ctx().stream>>>(p);
+    count_launch();
+    ok = cuda_ok(cudaGetLastError(), "stream-K second pass launch");
+  }
+  profile_mark(false);
+  if (p.sk_part) scratch_free(p.sk_part);
+  return ok;
 }
 
 template <int BK, bool LO_PLANE>

@@ -220,6 +220,10 @@ struct TcParams {
   int b_sliced;               // direct path: B is a K-sliced view, map dimensions {k, slice, row}
   int a_sliced = 0;           // direct path: the same for a K-major A
   int pair_group_m = 8;       // pair kernel: 256-row tile-rows per rasterisation group
+  int sk_tiles = 0;           // pair kernel: the last sk_tiles tiles (a partly filled wave) are each cut along K into
+  int sk_slices = 0;          // sk_slices runs that different clusters add up; their partial sums go to sk_part and a
+                              // second kernel adds them in K order; 0 = off
+  float* sk_part = nullptr;   // [sk_slices][sk_tiles][256][256]: slot = run * sk_tiles + tile of the region
   int c_tma;                  // pair kernel: a tensor map over C exists (16-byte aligned, n a multiple of 4): TMA stores
                               // of 32 x 32 blocks (1) or of 32 x 16 blocks, two in flight (2)
   DeviceStatus* status;
