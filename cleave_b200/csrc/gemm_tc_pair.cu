@@ -452,7 +452,8 @@ __global__ void __launch_bounds__(256) pair_streamk_fixup_kernel(TcParams p) {
 
 // Cut region for this launch: *slices = K-runs per tile (0: none), returns the tiles of the region.  It pays when the
 // last wave fills at most half of the SM pairs (so every tile gets at least two runs) and the K-blocks saved,
-// num_kb * (1 - 1/slices), clearly outweigh the second pass (~16 us, i.e. ~16 K-blocks of 32): at least 48.
+// num_kb * (1 - 1/slices), outweigh the second pass (measured: ~9 us, i.e. ~9 K-blocks of 32): at least 16, or what
+// CLEAVE_CUDA_GEMM_CUT_MIN_KB says (4096 x 4096 x K1024, 34 tiles cut in two: 163 -> 156 us).
 // CLEAVE_CUDA_GEMM_STREAMK=0 turns it off.
 static int cut_region(const TcParams& p, int sm_pairs, int* slices) {
   static const bool on = !(getenv("CLEAVE_CUDA_GEMM_STREAMK") && getenv("CLEAVE_CUDA_GEMM_STREAMK")[0] == '0');
@@ -463,7 +464,12 @@ static int cut_region(const TcParams& p, int sm_pairs, int* slices) {
   if (tiles < sm_pairs || rem == 0) return 0;
   int s = sm_pairs / rem;
   if (s > 8) s = 8;
-  if (s < 2 || (int64_t)p.num_kb * (s - 1) < 48ll * s || p.num_kb / s < 8) return 0;
+  static const int min_saved = [] {
+    const char* e = getenv("CLEAVE_CUDA_GEMM_CUT_MIN_KB");
+    const int v = e ? atoi(e) : 0;
+    return v > 0 ? v : 16;
+  }();
+  if (s < 2 || (int64_t)p.num_kb * (s - 1) < (int64_t)min_saved * s || p.num_kb / s < 8) return 0;
   *slices = s;
   return rem;
 }
