@@ -83,6 +83,7 @@ SIGNATURES = {
     "cleave_cuda_gemm_dact_f32": (i32, [c_buf, c_buf, c_buf, i32, i32, i32, i32, i32, i32, i32, c_buf, i32]),
     "cleave_cuda_gemm_fused_f32": (i32, [c_buf, c_buf, c_buf, i32, i32, i32, i32, i32, i32, i32, c_buf, i32, c_buf, i32,
                                          c_buf, c_buf, c_buf]),
+    "cleave_cuda_dense_grads_f32": (i32, [c_buf, c_buf, c_buf, c_buf, i32, i32, i32, c_buf, c_buf]),
     "cleave_cuda_split_lo_f32": (c_buf, [c_buf]),
     "cleave_cuda_split_lo_into_f32": (i32, [c_buf, c_buf, ctypes.c_void_p]),
     "cleave_cuda_bias_act_f32": (c_buf, [c_buf, c_buf, i32, i32, i32]),

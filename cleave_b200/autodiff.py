@@ -22,7 +22,7 @@ import numpy as np
 
 from . import nn
 from ._lib import lib, raise_last_error
-from .linalg import Tensor, gemm_into, split_lo
+from .linalg import Tensor, dense_grads, gemm_into, split_lo
 
 _ACT_BWD = {"tanh": nn.tanh_bwd, "sigmoid": nn.sigmoid_bwd}
 
@@ -135,12 +135,11 @@ class MLP2:
         # Layer 1's gradients first: W1 was last read by the forward product, so its exchange can run beside
         # the dW2 product, and layer 2's exchange beside the NEXT step's first forward product (which needs
         # only W1).  dZ1 above was the last reader of W2 in this pass.
-        gemm_into(self.dW1, X, dZ1, trans_a=True, a_lo=X_lo, b_lo=dZ1_lo)            # X^T dZ1
-        self._colsum_into(self.db1, dZ1)
+        # Each layer's weight and bias gradient in one call: X^T dZ on the tensor cores, colsum(dZ) beside it.
+        dense_grads(self.dW1, self.db1, X, dZ1, X_lo, dZ1_lo)
         if on_grads_ready:
             on_grads_ready(1)
-        gemm_into(self.dW2, H, dZ2, trans_a=True, a_lo=H_lo, b_lo=dZ2_lo)            # H^T dZ2
-        self._colsum_into(self.db2, dZ2)
+        dense_grads(self.dW2, self.db2, H, dZ2, H_lo, dZ2_lo)
         if on_grads_ready:
             on_grads_ready(0)
         if keep:
@@ -150,11 +149,6 @@ class MLP2:
     def chains_planes(self, batch: int) -> bool:
         """Whether a step at this batch size hands lo planes from product to product."""
         return bool(self.chain_lo and batch % 32 == 0 and batch * self.d_in * self.d_hid >= (1 << 24))
-
-    @staticmethod
-    def _colsum_into(out: Tensor, x: Tensor) -> None:
-        if lib().cleave_cuda_colsum_into_f32(out._h, x._h, x.dims[0], x.dims[1]) != 0:
-            raise_last_error("colsum_into")
 
     def sgd(self, lr: float, gscale: float = 1.0) -> None:
         """``p = p - lr * gscale * g`` over the whole parameter buffer in one pass."""

@@ -47,6 +47,8 @@ struct Context {
   DeviceStatus* status_dev = nullptr;
   float* scalar_host = nullptr;       // pinned, mapped landing area for scalar results (64 floats)
   float* scalar_dev = nullptr;        // device alias of scalar_host: kernels write results straight to the host
+  cudaStream_t side_stream = nullptr; // library-owned; used only between side_fork() and side_join()
+  cudaEvent_t side_fork_ev = nullptr, side_join_ev = nullptr;
 };
 
 Context& ctx();
@@ -84,6 +86,18 @@ float read_scalar(const float* dev_scalar);
 // wait_scalar() synchronises the stream, checks the status word and returns it (NaN on failure).
 float* scalar_slot();
 float wait_scalar();
+
+// ---- a second queue inside one call ---------------------------------------------------------------
+// side_fork() returns a library-owned stream that is ordered after everything queued on ctx().stream so far;
+// side_join() orders ctx().stream after everything queued on that stream.  An entry point that has two
+// independent kernels to run (a product that leaves SMs idle and a streaming pass) queues one on each between the two
+// calls; to its caller all of it is ordered on ctx().stream as usual, so the pool's stream-ordered reuse stays valid:
+// whatever is queued after the call follows the join.  Works while a graph is being captured (the side stream joins
+// the capture through the fork event).  nullptr / false + error on failure.
+cudaStream_t side_fork();
+bool side_join();
+// Column sums x[rows, cols] -> out[cols] on `stream` (reduce.cu).
+bool colsum_launch(const float* x, float* out, int rows, int cols, cudaStream_t stream);
 
 // ---- optional per-kernel timing -------------------------------------------------------------------
 // Between profile_begin() and profile_end() every profile_mark(true) / profile_mark(false) pair

@@ -156,6 +156,35 @@ int32_t cleave_cuda_gemm_fused_f32(cleave_buf c, cleave_buf a, cleave_buf b, int
   return r == CLEAVE_CUDA_OK ? CLEAVE_CUDA_OK : -r;
 }
 
+int32_t cleave_cuda_dense_grads_f32(cleave_buf dw, cleave_buf db, cleave_buf x, cleave_buf dz, int32_t rows, int32_t d_in,
+                                    int32_t d_out, cleave_buf x_lo, cleave_buf dz_lo) {
+  ApiLock lock;
+  Trace tr("dense_grads", "rows=%d d_in=%d d_out=%d", rows, d_in, d_out);
+  Buf* DW = as_buf(dw, "dense_grads");
+  Buf* DB = as_buf(db, "dense_grads");
+  Buf* X = as_buf(x, "dense_grads");
+  Buf* DZ = as_buf(dz, "dense_grads");
+  if (!DW || !DB || !X || !DZ) return -cleave_cuda_last_error();
+  Buf* XL = nullptr;
+  Buf* DZL = nullptr;
+  if (x_lo && !(XL = as_buf(x_lo, "dense_grads"))) return -cleave_cuda_last_error();
+  if (dz_lo && !(DZL = as_buf(dz_lo, "dense_grads"))) return -cleave_cuda_last_error();
+  if (rows <= 0 || d_in <= 0 || d_out <= 0 || DB->len != d_out || DZ->len != (int64_t)rows * d_out)
+    return -set_error(CLEAVE_CUDA_ERR_SHAPE, "dense_grads: db has %lld elements, dz %lld, for rows %d, d_out %d",
+                      (long long)DB->len, (long long)DZ->len, rows, d_out);
+  // The bias gradient only needs dz, which is complete before this call: it runs on the side queue, beside the product
+  // (which is queued first so that its CTAs are placed first; a product with fewer tiles than SMs leaves the rest
+  // to the column sums, otherwise they fill in as the product's CTAs retire).
+  cudaStream_t side = side_fork();
+  if (!side) return -cleave_cuda_last_error();
+  int r = gemm_into(DW, X, DZ, 1, d_in, d_out, rows, 1, 0, CLEAVE_GEMM_AUTO, nullptr, CLEAVE_ACT_IDENTITY, nullptr,
+                    CLEAVE_ACT_IDENTITY, XL, DZL, nullptr);
+  const bool ok = colsum_launch(DZ->ptr, DB->ptr, rows, d_out, side);
+  if (!side_join()) return -cleave_cuda_last_error();   // always rejoin: a captured graph must not end forked
+  if (r != CLEAVE_CUDA_OK) return -r;
+  return ok ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
+}
+
 cleave_buf cleave_cuda_split_lo_f32(cleave_buf x) {
   ApiLock lock;
   Buf* a = as_buf(x, "split_lo");

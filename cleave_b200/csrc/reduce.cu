@@ -638,7 +638,10 @@ float cleave_cuda_max_f32(cleave_buf v) {
   return reduce_scalar<MaxRed>(a->ptr, a->len, 0, 1.0f, 1);
 }
 
-static bool colsum_launch(const float* x, float* out, int rows, int cols) {
+}  // extern "C"
+
+namespace cleave {
+bool colsum_launch(const float* x, float* out, int rows, int cols, cudaStream_t s) {
   Trace tr("colsum", "rows=%d cols=%d", rows, cols);
   const int strips = ceil_div(cols, kCsTx * 4);
   // Row splits: enough CTAs to fill the machine, at least 64 rows each; a function of the shape only.
@@ -651,7 +654,6 @@ static bool colsum_launch(const float* x, float* out, int rows, int cols) {
   float* partials = scratch_alloc((int64_t)splits * cols * sizeof(float));
   if (!partials) return false;
   int vec = (aligned16(x) && cols % 4 == 0) ? 1 : 0;
-  cudaStream_t s = ctx().stream;
   if (strips <= kCsMaxStrips) {
     colsum_stage1<<<dim3(strips, splits), kCsTx * kCsTy, 0, s>>>(x, rows, cols, rows_per_split, partials, vec, out);
     count_launch(1);
@@ -665,6 +667,9 @@ static bool colsum_launch(const float* x, float* out, int rows, int cols) {
   scratch_free(partials);
   return ok;
 }
+}  // namespace cleave
+
+extern "C" {
 
 cleave_buf cleave_cuda_colsum_f32(cleave_buf x, int32_t rows, int32_t cols) {
   ApiLock lock;
@@ -676,7 +681,7 @@ cleave_buf cleave_cuda_colsum_f32(cleave_buf x, int32_t rows, int32_t cols) {
   }
   Buf* o = new_buf(cols);
   if (!o) return nullptr;
-  if (!colsum_launch(a->ptr, o->ptr, rows, cols)) { release_buf(o); return nullptr; }
+  if (!colsum_launch(a->ptr, o->ptr, rows, cols, ctx().stream)) { release_buf(o); return nullptr; }
   return (cleave_buf)o;
 }
 
@@ -688,7 +693,7 @@ int32_t cleave_cuda_colsum_into_f32(cleave_buf out, cleave_buf x, int32_t rows, 
   if (rows <= 0 || cols <= 0 || a->len != (int64_t)rows * cols || o->len != cols)
     return -set_error(CLEAVE_CUDA_ERR_SHAPE, "colsum_into: tensor has %lld elements, output %lld, for %d x %d",
                       (long long)a->len, (long long)o->len, rows, cols);
-  return colsum_launch(a->ptr, o->ptr, rows, cols) ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
+  return colsum_launch(a->ptr, o->ptr, rows, cols, ctx().stream) ? CLEAVE_CUDA_OK : -cleave_cuda_last_error();
 }
 
 // loss_dev == nullptr: the loss is returned (the call waits for it).  Otherwise it is written to

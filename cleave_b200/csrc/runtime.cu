@@ -353,6 +353,26 @@ static bool g_profiling = false;
 static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_prof_events;
 static size_t g_prof_used = 0;
 
+cudaStream_t side_fork() {
+  Context& c = g_ctx;
+  if (!c.side_stream) {
+    if (!cuda_ok(cudaStreamCreateWithFlags(&c.side_stream, cudaStreamNonBlocking), "cudaStreamCreate(side)") ||
+        !cuda_ok(cudaEventCreateWithFlags(&c.side_fork_ev, cudaEventDisableTiming), "cudaEventCreate(fork)") ||
+        !cuda_ok(cudaEventCreateWithFlags(&c.side_join_ev, cudaEventDisableTiming), "cudaEventCreate(join)"))
+      return nullptr;
+  }
+  if (!cuda_ok(cudaEventRecord(c.side_fork_ev, c.stream), "cudaEventRecord(fork)") ||
+      !cuda_ok(cudaStreamWaitEvent(c.side_stream, c.side_fork_ev, 0), "cudaStreamWaitEvent(fork)"))
+    return nullptr;
+  return c.side_stream;
+}
+
+bool side_join() {
+  Context& c = g_ctx;
+  return cuda_ok(cudaEventRecord(c.side_join_ev, c.side_stream), "cudaEventRecord(join)") &&
+         cuda_ok(cudaStreamWaitEvent(c.stream, c.side_join_ev, 0), "cudaStreamWaitEvent(join)");
+}
+
 void profile_mark(bool begin) {
   if (!g_profiling) return;
   if (begin) {

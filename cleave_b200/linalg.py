@@ -188,6 +188,18 @@ GEMM_AUTO, GEMM_EXACT, GEMM_3XTF32 = 0, 1, 2
 ACT = {"identity": 0, "relu": 1, "sigmoid": 2, "tanh": 3}
 
 
+def dense_grads(dw: Tensor, db: Tensor, x: Tensor, dz: Tensor, x_lo: Tensor | None = None,
+                dz_lo: Tensor | None = None) -> None:
+    """Both gradients of a dense layer from the gradient ``dz`` [rows, d_out] of its output: ``dw = x^T dz`` and
+    ``db = colsum(dz)``, the column sums queued beside the product (``cleave_cuda_dense_grads_f32``)."""
+    rows, d_in = x.dims
+    if dz.dims[0] != rows or dw.dims != (d_in, dz.dims[1]) or db.dims != (dz.dims[1],):
+        raise TypeError(f"dense_grads: x {x.dims}, dz {dz.dims} -> dw {dw.dims}, db {db.dims} do not agree")
+    h = lambda t: t._h if t is not None else None  # noqa: E731
+    if lib().cleave_cuda_dense_grads_f32(dw._h, db._h, x._h, dz._h, rows, d_in, dz.dims[1], h(x_lo), h(dz_lo)) != 0:
+        raise_last_error("dense_grads")
+
+
 def split_lo(x: Tensor) -> Tensor:
     """The lo plane of ``x`` (``cleave_cuda_split_lo_f32``): what the tensor-core path needs beside ``x`` itself."""
     return Tensor._wrap(lib().cleave_cuda_split_lo_f32(x._h), x.dims, "split_lo")

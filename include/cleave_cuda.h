@@ -244,6 +244,16 @@ int32_t cleave_cuda_gemm_fused_f32(cleave_buf c, cleave_buf a, cleave_buf b, int
                                    int32_t k, int32_t trans_a, int32_t trans_b, int32_t algo, cleave_buf bias,
                                    int32_t act, cleave_buf y, int32_t dact, cleave_buf a_lo, cleave_buf b_lo,
                                    cleave_buf c_lo);
+/* Both gradients of a dense layer y = x W + b from the gradient dz of its output, in one call (the derivative rule of
+ * MatMul and of the broadcast bias add: stdlib/linalg/matrix.cleave:59-60 reversed, and the column sum that undoes the
+ * row broadcast of stdlib/nn/nn.cleave:72-74):
+ *   dw[d_in, d_out] = x[rows, d_in]^T * dz[rows, d_out],    db[d_out] = sum over rows of dz.
+ * The two are independent, so the library queues the column sums beside the product on a second stream of its own and
+ * rejoins before returning: a product with fewer tiles than SMs leaves the idle SMs to the sums.  Results are bit-identical
+ * to cleave_cuda_gemm_fused_f32(dw, x, dz, trans_a = 1, ...) followed by cleave_cuda_colsum_into_f32(db, dz, ...).
+ * x_lo / dz_lo (may be NULL): lo planes of the operands, as in cleave_cuda_gemm_fused_f32. */
+int32_t cleave_cuda_dense_grads_f32(cleave_buf dw, cleave_buf db, cleave_buf x, cleave_buf dz, int32_t rows, int32_t d_in,
+                                    int32_t d_out, cleave_buf x_lo, cleave_buf dz_lo);
 /* The lo plane of a tensor in one streaming pass: lo[i] = tf32-rounded (x[i] - x[i] with its 13 low mantissa
  * bits cleared), the part of x the tensor pipe drops when it reads x as tf32. */
 cleave_buf cleave_cuda_split_lo_f32(cleave_buf x);

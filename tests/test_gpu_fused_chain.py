@@ -117,3 +117,32 @@ def test_chained_perceptron_step_is_bit_identical_to_the_unchained_one(batch, d_
     adZ1 = np.abs(want["dZ1"]).astype(np.float64)
     err = np.max(np.abs(nets[1].dW1.numpy().astype(np.float64) - want["dW1"]) / (absX.T @ adZ1))
     assert err <= TOL
+
+
+@pytest.mark.parametrize("rows,d_in,d_out", [(64, 32, 48), (300, 100, 52), (4096, 1024, 1024), (2048, 4096, 1024)])
+def test_dense_grads_equals_the_product_followed_by_the_column_sums(rows, d_in, d_out):
+    # dw = x^T dz and db = colsum(dz) in one call, the sums queued beside the product on the library's second
+    # stream: bit for bit the two-call form, with and without the operands' lo planes, and repeatedly (the fork and
+    # join must leave the library's stream ordered: every round reads what the previous one wrote)
+    T = linalg.Tensor
+    x = workloads.uniform_pm1(rows + 1, rows, d_in)
+    dz = workloads.normal(rows + 2, rows, d_out)
+    tx, tdz = T(x), T(dz)
+    want_dw = linalg.gemm_into(T.empty(d_in, d_out), tx, tdz, trans_a=True).numpy()
+    want_db = nn.colsum(tdz).numpy()
+    assert np.max(np.abs(want_db.astype(np.float64) - ref.colsum(dz)) / np.sum(np.abs(dz), axis=0)) <= TOL
+    for planes in (False, True):
+        x_lo = linalg.split_lo(tx) if planes else None
+        dz_lo = linalg.split_lo(tdz) if planes else None
+        for _ in range(3):
+            dw, db = T.filled(7.0, d_in, d_out), T.filled(7.0, d_out)
+            linalg.dense_grads(dw, db, tx, tdz, x_lo, dz_lo)
+            got_db = db.numpy()
+            assert np.array_equal(got_db, want_db)
+            if planes:
+                want_planes = linalg.gemm_into(T.empty(d_in, d_out), tx, tdz, trans_a=True, a_lo=x_lo, b_lo=dz_lo).numpy()
+                assert np.array_equal(dw.numpy(), want_planes)
+            else:
+                assert np.array_equal(dw.numpy(), want_dw)
+    with pytest.raises(Exception):
+        linalg.dense_grads(T.empty(d_in, d_out), T.empty(d_out + 1), tx, tdz)
