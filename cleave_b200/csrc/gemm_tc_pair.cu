@@ -464,6 +464,7 @@ static int cut_region(const TcParams& p, int sm_pairs, int* slices) {
   if (tiles < sm_pairs || rem == 0) return 0;
   int s = sm_pairs / rem;
   if (s > 8) s = 8;
+  while (s > 2 && p.num_kb / s < 8) --s;   // runs of at least 8 K-blocks (one accumulation chunk)
   static const int min_saved = [] {
     const char* e = getenv("CLEAVE_CUDA_GEMM_CUT_MIN_KB");
     const int v = e ? atoi(e) : 0;

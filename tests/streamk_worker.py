@@ -72,6 +72,12 @@ def main() -> int:
     got = linalg.gemm_into(T.empty(2560, 2048), T(ai), T(bi), algo=GEMM_3XTF32).numpy()
     assert np.array_equal(got, ref.matmul(ai, bi))
     cases += 1
+    # K = 1024 (32 K-blocks): the 6 tiles of the second wave are cut into 4 runs of 8 K-blocks
+    m, n, k = 2560, 2048, 1024
+    a, b = workloads.gemm_inputs(m, n, k)
+    got = linalg.gemm_into(T.empty(m, n), T(a), T(b), algo=GEMM_3XTF32).numpy()
+    assert_gemm_close(got, a, b, what=("short runs", m, n, k))
+    cases += 1
     # fewer tiles than SM pairs (8 x 8 = 64): a single, nearly full wave is never cut
     m, n, k = 2048, 2048, 4096
     a, b = workloads.gemm_inputs(m, n, k)
