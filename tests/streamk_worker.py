@@ -78,6 +78,13 @@ def main() -> int:
     got = linalg.gemm_into(T.empty(m, n), T(a), T(b), algo=GEMM_3XTF32).numpy()
     assert_gemm_close(got, a, b, what=("short runs", m, n, k))
     cases += 1
+    # K = 768 (24 K-blocks, three runs of 8), both operands stored the other way round
+    m, n, k = 2560, 2048, 768
+    a, b = workloads.gemm_inputs(m, n, k)
+    got = linalg.gemm_into(T.empty(m, n), T(np.ascontiguousarray(a.T)), T(np.ascontiguousarray(b.T)), trans_a=True,
+                           trans_b=True, algo=GEMM_3XTF32).numpy()
+    assert_gemm_close(got, a, b, what=("tt", m, n, k))
+    cases += 1
     # fewer tiles than SM pairs (8 x 8 = 64): a single, nearly full wave is never cut
     m, n, k = 2048, 2048, 4096
     a, b = workloads.gemm_inputs(m, n, k)

@@ -28,4 +28,4 @@ def test_cut_and_uncut_last_wave_both_match_the_oracle():
     cases_on, launches_on = _run("1")
     assert cases_off == cases_on
     # every product but the last one has a cut region (one more launch each: the second pass)
-    assert launches_on == launches_off + 10
+    assert launches_on == launches_off + 11
