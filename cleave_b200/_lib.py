@@ -34,6 +34,7 @@ SIGNATURES = {
     "cleave_cuda_kernel_launches": (i64, []),
     "cleave_cuda_test_hook": (i64, [i32, i64]),
     "cleave_cuda_gemm_batch_chunk": (i32, [i64, i32]),
+    "cleave_cuda_gemm_cut_plan": (i32, [i32, i32, i32, ctypes.POINTER(ctypes.c_int32)]),
     "cleave_cuda_profile_begin": (None, []),
     "cleave_cuda_profile_end": (ctypes.c_double, [ctypes.POINTER(i32)]),
     "cleave_cuda_graph_begin": (i32, []),

@@ -45,6 +45,9 @@ bool launch_gemm_exact(const GemmArgs& g);
 bool split_lo_plane(const float* src, float* dst, int64_t n, cudaStream_t on_stream = nullptr);
 bool launch_gemm_3xtf32(const GemmArgs& g);   // false + error if the problem cannot use this path
 bool gemm_3xtf32_supported(const GemmArgs& g);
+// Cut of a partly filled last wave of 256 x 256 tiles (gemm_tc_pair.cu): returns the tiles of the wave that are cut along K
+// and stores the K-runs per tile in *slices; 0 / 0 when the wave is left whole.  Host arithmetic only.
+int gemm_cut_plan(int tiles, int num_kb, int sm_pairs, int* slices);
 int gemm_batch_chunk(int64_t bytes_per_entry, int batch);   // batch entries per pass (workspace and grid limits)
 
 }  // namespace cleave

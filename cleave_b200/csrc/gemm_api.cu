@@ -200,6 +200,13 @@ int32_t cleave_cuda_gemm_batch_chunk(int64_t workspace_bytes_per_entry, int32_t 
   return gemm_batch_chunk(workspace_bytes_per_entry, batch);
 }
 
+int32_t cleave_cuda_gemm_cut_plan(int32_t tiles, int32_t k_blocks, int32_t sm_pairs, int32_t* runs_per_tile) {
+  int runs = 0;
+  const int cut = gemm_cut_plan(tiles, k_blocks, sm_pairs, &runs);
+  if (runs_per_tile) *runs_per_tile = runs;
+  return cut;
+}
+
 int32_t cleave_cuda_split_lo_into_f32(cleave_buf lo, cleave_buf x, void* cuda_stream) {
   ApiLock lock;
   Buf* a = as_buf(x, "split_lo_into");

@@ -455,22 +455,21 @@ __global__ void __launch_bounds__(256) pair_streamk_fixup_kernel(TcParams p) {
 // num_kb * (1 - 1/slices), outweigh the second pass (measured: ~9 us, i.e. ~9 K-blocks of 32): at least 16, or what
 // CLEAVE_CUDA_GEMM_CUT_MIN_KB says (4096 x 4096 x K1024, 34 tiles cut in two: 163 -> 156 us).
 // CLEAVE_CUDA_GEMM_STREAMK=0 turns it off.
-static int cut_region(const TcParams& p, int sm_pairs, int* slices) {
+int gemm_cut_plan(int tiles, int num_kb, int sm_pairs, int* slices) {
   static const bool on = !(getenv("CLEAVE_CUDA_GEMM_STREAMK") && getenv("CLEAVE_CUDA_GEMM_STREAMK")[0] == '0');
   *slices = 0;
-  if (!on) return 0;
-  const int tiles = p.batch * p.mblks * p.nblks;
+  if (!on || tiles <= 0 || num_kb <= 0 || sm_pairs <= 0) return 0;
   const int rem = tiles % sm_pairs;
   if (tiles < sm_pairs || rem == 0) return 0;
   int s = sm_pairs / rem;
   if (s > 8) s = 8;
-  while (s > 2 && p.num_kb / s < 8) --s;   // runs of at least 8 K-blocks (one accumulation chunk)
+  while (s > 2 && num_kb / s < 8) --s;   // runs of at least 8 K-blocks (one accumulation chunk)
   static const int min_saved = [] {
     const char* e = getenv("CLEAVE_CUDA_GEMM_CUT_MIN_KB");
     const int v = e ? atoi(e) : 0;
     return v > 0 ? v : 16;
   }();
-  if (s < 2 || (int64_t)p.num_kb * (s - 1) < (int64_t)min_saved * s || p.num_kb / s < 8) return 0;
+  if (s < 2 || (int64_t)num_kb * (s - 1) < (int64_t)min_saved * s || num_kb / s < 8) return 0;
   *slices = s;
   return rem;
 }
@@ -488,7 +487,7 @@ static bool run_pair(const CUtensorMap* maps, const TcParams& p_in) {
   TcParams p = p_in;
   const int tiles = p.batch * p.mblks * p.nblks;
   const int sm_pairs = ctx().sm_count / 2;
-  p.sk_tiles = cut_region(p, sm_pairs, &p.sk_slices);
+  p.sk_tiles = gemm_cut_plan(tiles, p.num_kb, sm_pairs, &p.sk_slices);
   const int clusters = tiles < sm_pairs ? tiles : sm_pairs;
   if (p.sk_tiles) {
     p.sk_part = scratch_alloc((int64_t)p.sk_tiles * p.sk_slices * 256 * 256 * sizeof(float));

@@ -100,6 +100,11 @@ int64_t cleave_cuda_test_hook(int32_t what, int64_t arg);
  * entries one pass processes given the operand workspace one entry needs (bounded by the workspace limit, by
  * `batch`, and by the 65535 entries a grid's z dimension can index). */
 int32_t cleave_cuda_gemm_batch_chunk(int64_t workspace_bytes_per_entry, int32_t batch);
+/* Host arithmetic of the CTA-pair GEMM's last wave, likewise exposed for checking without a device: for a product of
+ * `tiles` 256 x 256 tiles and `k_blocks` K-blocks of 32 on `sm_pairs` SM pairs, returns how many tiles of the last,
+ * partly filled wave are cut along K (0: none) and stores the equal K-runs per cut tile in *runs_per_tile.  The cut
+ * keeps tiles x runs <= sm_pairs and runs of at least 8 K-blocks, and applies only when it saves at least 16 K-blocks. */
+int32_t cleave_cuda_gemm_cut_plan(int32_t tiles, int32_t k_blocks, int32_t sm_pairs, int32_t* runs_per_tile);
 /* A step captured once and replayed (CUDA graph): everything queued between begin and end is recorded instead of
  * run, and cleave_cuda_graph_launch replays it on the library's stream without the per-kernel launch gaps (the
  * 11 kernels of a perceptron step: 0.80 -> 0.76 ms).  Only entry points that do not wait may be called inside a

@@ -114,3 +114,38 @@ def test_batch_chunking_respects_workspace_batch_and_grid_limits():
 def test_the_absent_operand_is_a_null_handle():
     import cleave_b200 as cb
     assert cb.lib().cleave_cuda_none() is None
+
+
+def test_cut_plan_of_a_partly_filled_last_wave():
+    # host arithmetic of the CTA-pair GEMM: which tiles of the last wave are cut along K, and into how many runs
+    import ctypes
+
+    import cleave_b200 as cb
+    L = cb.lib()
+    runs = ctypes.c_int32(-1)
+
+    def plan(tiles, k_blocks, pairs=74):
+        cut = L.cleave_cuda_gemm_cut_plan(tiles, k_blocks, pairs, ctypes.byref(runs))
+        return cut, runs.value
+
+    assert plan(256, 128) == (34, 2)        # 4096^3: three waves + 34 tiles, cut in two
+    assert plan(256, 32) == (34, 2)         # 4096 x 4096 x K1024: saves 16 K-blocks, just enough
+    assert plan(256, 16) == (0, 0)          # K = 512: the second pass would cost what the cut saves
+    assert plan(1024, 256) == (0, 0)        # 8192^3: the last wave has 62 of 74 tiles, nothing to share out
+    assert plan(4096, 512) == (26, 2)       # 16384^3
+    assert plan(80, 64) == (6, 8)           # a nearly empty wave: at most 8 runs
+    assert plan(80, 32) == (6, 4)           # ... of at least 8 K-blocks each
+    assert plan(80, 24) == (6, 3)
+    assert plan(64, 128) == (0, 0)          # fewer tiles than SM pairs: a single wave is never cut
+    assert plan(148, 128) == (0, 0)         # whole waves
+    assert plan(0, 128) == (0, 0) and plan(100, 0) == (0, 0)
+    for tiles in range(75, 400, 7):
+        for kb in (16, 24, 32, 48, 64, 100, 128, 512):
+            cut, r = plan(tiles, kb)
+            if cut:
+                assert cut == tiles % 74 and 2 <= r <= 8 and cut * r <= 74 and kb // r >= 8 and kb * (r - 1) >= 16 * r
+                # the runs floor(kb * j / r) .. floor(kb * (j + 1) / r) partition the K-blocks
+                edges = [kb * j // r for j in range(r + 1)]
+                assert edges[0] == 0 and edges[-1] == kb and all(b > a for a, b in zip(edges, edges[1:]))
+            else:
+                assert r == 0
