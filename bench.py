@@ -530,6 +530,45 @@ def run_gemm_sweep(args):
           flush=True)
 
 
+NUMA_INFO = None   # what bind_to_gpu_numa_node did on this rank (multi-rank runs only)
+
+
+def bind_to_gpu_numa_node(local: int) -> dict:
+    """With several ranks on one host, run this rank's threads on the NUMA node its GPU is attached to, so that the
+    pinned staging buffers it allocates afterwards (placed by first touch) and the copies from them do not cross the
+    socket interconnect.  Reads sysfs only; does nothing when the node is unknown, when there is one node, or when the
+    allowed CPU set leaves no CPU of that node.  Returns what it did, for the bench line."""
+    info = {"node": None}
+    try:
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        if len(nodes) < 2:
+            info["nodes"] = len(nodes)
+            return info
+        import torch
+        pr = torch.cuda.get_device_properties(local)
+        bus = "%04x:%02x:%02x.0" % (getattr(pr, "pci_domain_id", 0), pr.pci_bus_id, pr.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        info.update({"nodes": len(nodes), "gpu_pci": bus})
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        mine = cpus & allowed
+        if mine and mine != allowed:
+            os.sched_setaffinity(0, mine)
+            info.update({"node": node, "cpus": len(mine), "of_allowed": len(allowed)})
+        else:
+            info.update({"node": node, "cpus": len(mine), "of_allowed": len(allowed), "bound": False})
+    except Exception as e:   # noqa: BLE001 - placement is an optimisation; the run goes on unbound
+        info["error"] = f"{type(e).__name__}: {e}"[:160]
+    return info
+
+
 def _dist_setup():
     """torch + process group (NCCL, one rank per GPU) + the library on torch's current stream; idempotent."""
     import torch
@@ -541,6 +580,9 @@ def _dist_setup():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    global NUMA_INFO
+    if world > 1 and NUMA_INFO is None:
+        NUMA_INFO = bind_to_gpu_numa_node(local)
     if world > 1 and not dist.is_initialized():
         import datetime
         # a collective that a failed rank never joins ends with an error after 5 minutes instead of hanging the job
@@ -1086,6 +1128,8 @@ def main():
            "note": "copies on the copy engines, two tensor sets alternating: compute of step i overlaps the upload of "
                    "step i+1 and the download of step i-1; copy_ceiling_ms = the same copies with no product, all "
                    "ranks at once; single_call_ms = one synchronous cleave_cuda_host_gemm_f32 call per step"}
+    if NUMA_INFO is not None:
+        e2e["host_placement_rank0"] = NUMA_INFO   # which NUMA node rank 0's threads and pinned buffers were bound to
     line = {
         "metric": f"f32 GEMM TFLOP/s ({M}^3)", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
