@@ -107,7 +107,7 @@ int32_t cleave_cuda_gemm_batch_chunk(int64_t workspace_bytes_per_entry, int32_t 
 int32_t cleave_cuda_gemm_cut_plan(int32_t tiles, int32_t k_blocks, int32_t sm_pairs, int32_t* runs_per_tile);
 /* A step captured once and replayed (CUDA graph): everything queued between begin and end is recorded instead of
  * run, and cleave_cuda_graph_launch replays it on the library's stream without the per-kernel launch gaps (the
- * 11 kernels of a perceptron step: 0.80 -> 0.76 ms).  Only entry points that do not wait may be called inside a
+ * 13 kernels of a perceptron step: 0.77 -> 0.73 ms).  Only entry points that do not wait may be called inside a
  * capture (no scalar-returning op, no download, no sync); call the step once before capturing it, so that one-time
  * kernel set-up has happened.  Tensors allocated inside the capture come from a cache that belongs to the graph:
  * the replays keep using exactly those blocks, nothing else is handed them, and cleave_cuda_graph_free returns them.
